@@ -1,0 +1,238 @@
+"""Python face of libb200gemm.so, the B200 (sm_100a) asynchronous tensor-core GEMM.
+
+The product is the C-ABI shared library (include/b200_gemm.h); this module only binds it with
+ctypes so that Python harnesses (tests, bench) can call it with device pointers taken from torch
+tensors. There is no CPU or PyTorch fallback: if the library is missing the import fails, and on
+a machine without an sm_100 GPU every compute call raises ``B200Error``.
+
+The directory name contains a hyphen, so import it through ``__graft_entry__.load_package()``
+(which registers it as ``cuda_kernel_opt_b200``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, asdict
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("B200_GEMM_LIB") or os.path.join(_HERE, "libb200gemm.so")
+
+OK, INVALID_CONFIG, INVALID_SHAPE, INVALID_POINTER, CUDA_ERROR, DEVICE_TIMEOUT, WORKSPACE_TOO_SMALL, UNSUPPORTED_DEVICE = range(8)
+F16, BF16 = 0, 1
+UNIFORM, NORMAL = 0, 1
+TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
+
+# every symbol include/b200_gemm.h declares
+EXPORTS = [
+    "b200_gemm_default_params", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
+    "b200_gemm_f16", "b200_gemm_bf16", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
+    "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
+    "b200_fill_u16_device", "b200_fill_f32_device", "b200_fill_u16_host", "b200_fill_f32_host",
+]
+
+
+class Params(C.Structure):
+    """struct b200_gemm_params."""
+    _fields_ = [(n, C.c_int) for n in (
+        "tile_m", "tile_n", "segment_dim_k", "bar_steps_a", "bar_steps_b", "bar_step_rows_a", "bar_step_rows_b",
+        "tile_group_m", "num_stages", "num_producer_warps", "num_consumer_warps", "num_sms", "cta_group", "split_k",
+        "epilogue")] + [("reserved", C.c_int * 3)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
+
+
+class B200Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: status {status} ({status_string(status)}), cuda error {lib().b200_last_cuda_error()}")
+
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library. Raises OSError if it has not been built (no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OSError(f"{LIB_PATH} is missing: build it with cuda-kernel-opt_b200/build.py (there is no fallback path)")
+        L = C.CDLL(LIB_PATH)
+        i64, f32, u64, vp, sz = C.c_int64, C.c_float, C.c_uint64, C.c_void_p, C.c_size_t
+        PP = C.POINTER(Params)
+        L.b200_gemm_default_params.argtypes = [i64, i64, i64, C.c_int, PP]
+        L.b200_gemm_validate.argtypes = [i64, i64, i64, C.c_int, PP]
+        L.b200_gemm_smem_bytes.argtypes = [C.c_int, PP]
+        L.b200_gemm_smem_bytes.restype = i64
+        L.b200_gemm_workspace_bytes.argtypes = [i64, i64, i64, PP]
+        L.b200_gemm_workspace_bytes.restype = i64
+        for fn in (L.b200_gemm_f16, L.b200_gemm_bf16):
+            fn.argtypes = [vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp, sz, vp]
+            fn.restype = C.c_int
+        L.b200_session_create.argtypes = [i64, i64, i64, C.POINTER(vp)]
+        L.b200_session_destroy.argtypes = [vp]
+        L.b200_session_destroy.restype = None
+        L.b200_session_gemm_host.argtypes = [vp, C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, PP]
+        L.b200_device_status.argtypes = [vp, C.POINTER(C.c_int * 4)]
+        L.b200_set_wait_budget_ns.argtypes = [u64]
+        L.b200_set_wait_budget_ns.restype = None
+        L.b200_set_profile_buffer.argtypes = [vp, C.c_int]
+        L.b200_set_profile_buffer.restype = None
+        L.b200_status_string.argtypes = [C.c_int]
+        L.b200_status_string.restype = C.c_char_p
+        L.b200_fill_u16_device.argtypes = [vp, i64, i64, u64, u64, C.c_int, f32, C.c_int, vp]
+        L.b200_fill_f32_device.argtypes = [vp, i64, i64, u64, u64, C.c_int, f32, vp]
+        L.b200_fill_u16_host.argtypes = [vp, i64, i64, u64, u64, C.c_int, f32, C.c_int]
+        L.b200_fill_u16_host.restype = None
+        L.b200_fill_f32_host.argtypes = [vp, i64, i64, u64, u64, C.c_int, f32]
+        L.b200_fill_f32_host.restype = None
+        _lib = L
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().b200_status_string(status).decode()
+
+
+def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Params:
+    p = Params()
+    st = lib().b200_gemm_default_params(M, N, K, dtype, C.byref(p))
+    if st != OK:
+        raise B200Error(st, "b200_gemm_default_params")
+    for k, v in overrides.items():
+        if not hasattr(p, k):
+            raise AttributeError(k)
+        setattr(p, k, v)
+    # keep "shift off" consistent when only the tile was overridden
+    if "tile_n" in overrides and "bar_step_rows_b" not in overrides:
+        p.bar_step_rows_b = p.tile_n
+    if "tile_m" in overrides and "bar_step_rows_a" not in overrides:
+        p.bar_step_rows_a = p.tile_m
+    return p
+
+
+def validate(M, N, K, dtype, p: Params) -> int:
+    return lib().b200_gemm_validate(M, N, K, dtype, C.byref(p))
+
+
+def smem_bytes(dtype, p: Params) -> int:
+    return lib().b200_gemm_smem_bytes(dtype, C.byref(p))
+
+
+def workspace_bytes(M, N, K, p: Params) -> int:
+    return lib().b200_gemm_workspace_bytes(M, N, K, C.byref(p))
+
+
+def gemm_raw(dtype, A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, p, ws_ptr=None, ws_bytes=0, stream=None) -> int:
+    """Direct call of b200_gemm_f16 / b200_gemm_bf16 with raw device addresses. Returns the status."""
+    fn = lib().b200_gemm_bf16 if dtype == BF16 else lib().b200_gemm_f16
+    return fn(A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, C.byref(p) if p is not None else None, ws_ptr, ws_bytes, stream)
+
+
+def gemm(A, Bt, Cm=None, D=None, alpha=1.0, beta=0.0, params: Params | None = None, workspace=None, stream=None):
+    """D = alpha * A @ Bt.T + beta * C on torch CUDA tensors (fp16 or bf16 A, Bt; fp32 C, D).
+
+    Thin convenience over the C ABI: it takes addresses from the tensors, allocates D (and the
+    split-K workspace) with torch when not given, and raises B200Error on a non-zero status."""
+    import torch
+    assert A.is_cuda and Bt.is_cuda and A.is_contiguous() and Bt.is_contiguous()
+    assert A.dtype == Bt.dtype and A.dtype in (torch.float16, torch.bfloat16)
+    M, K = A.shape
+    N, K2 = Bt.shape
+    assert K == K2
+    dtype = BF16 if A.dtype == torch.bfloat16 else F16
+    if D is None:
+        D = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    assert D.dtype == torch.float32 and D.is_contiguous() and D.shape == (M, N)
+    if Cm is not None:
+        assert Cm.dtype == torch.float32 and Cm.is_contiguous() and Cm.shape == (M, N)
+    p = params if params is not None else default_params(M, N, K, dtype)
+    need = workspace_bytes(M, N, K, p)
+    if need and workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=A.device)
+    sptr = stream if stream is not None else torch.cuda.current_stream(A.device).cuda_stream
+    with torch.cuda.device(A.device):
+        st = gemm_raw(dtype, A.data_ptr(), Bt.data_ptr(), Cm.data_ptr() if Cm is not None else None, D.data_ptr(),
+                      alpha, beta, M, N, K, p, workspace.data_ptr() if workspace is not None else None,
+                      workspace.numel() * workspace.element_size() if workspace is not None else 0, sptr)
+    if st != OK:
+        raise B200Error(st, "b200_gemm")
+    return D
+
+
+def device_status(stream=None):
+    """Synchronises and returns (status, [code, block, barrier, phase]) of the bounded-wait record."""
+    info = (C.c_int * 4)()
+    st = lib().b200_device_status(stream, C.byref(info))
+    return st, list(info)
+
+
+def set_wait_budget_ns(ns: int) -> None:
+    lib().b200_set_wait_budget_ns(ns)
+
+
+def num_sms() -> int:
+    return lib().b200_num_sms()
+
+
+class Session:
+    """b200_session: device buffers at maximal dimensions + the host-buffer GEMM call."""
+
+    def __init__(self, max_m, max_n, max_k):
+        self.h = C.c_void_p()
+        st = lib().b200_session_create(max_m, max_n, max_k, C.byref(self.h))
+        if st != OK:
+            raise B200Error(st, "b200_session_create")
+
+    def gemm_host(self, dtype, hA, hBt, hC, hD, alpha, beta, M, N, K, params=None):
+        """hA, hBt, hC, hD: objects with a host address: numpy arrays or (pinned) torch CPU tensors."""
+        def addr(x):
+            if x is None:
+                return None
+            return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
+        st = lib().b200_session_gemm_host(self.h, dtype, addr(hA), addr(hBt), addr(hC), addr(hD), alpha, beta, M, N, K,
+                                          C.byref(params) if params is not None else None)
+        if st != OK:
+            raise B200Error(st, "b200_session_gemm_host")
+
+    def close(self):
+        if self.h:
+            lib().b200_session_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def fill_u16_host(shape, seed, tensor_id, dist=UNIFORM, sigma=1.0, dtype=F16, begin=0):
+    import numpy as np
+    out = np.empty(shape, np.uint16)
+    lib().b200_fill_u16_host(out.ctypes.data, begin, out.size, seed, tensor_id, dist, sigma, dtype)
+    return out
+
+
+def fill_f32_host(shape, seed, tensor_id, dist=UNIFORM, sigma=1.0, begin=0):
+    import numpy as np
+    out = np.empty(shape, np.float32)
+    lib().b200_fill_f32_host(out.ctypes.data, begin, out.size, seed, tensor_id, dist, sigma)
+    return out
+
+
+def fill_device(t, seed, tensor_id, dist=UNIFORM, sigma=1.0, begin=0):
+    """Fills a contiguous torch CUDA tensor (fp16, bf16 or fp32) in place from the seeded generator."""
+    import torch
+    assert t.is_cuda and t.is_contiguous()
+    sptr = torch.cuda.current_stream(t.device).cuda_stream
+    with torch.cuda.device(t.device):
+        if t.dtype == torch.float32:
+            st = lib().b200_fill_f32_device(t.data_ptr(), begin, t.numel(), seed, tensor_id, dist, sigma, sptr)
+        else:
+            assert t.dtype in (torch.float16, torch.bfloat16)
+            st = lib().b200_fill_u16_device(t.data_ptr(), begin, t.numel(), seed, tensor_id, dist, sigma,
+                                            BF16 if t.dtype == torch.bfloat16 else F16, sptr)
+    if st != OK:
+        raise B200Error(st, "b200_fill_device")
+    return t

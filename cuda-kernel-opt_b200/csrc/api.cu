@@ -1,0 +1,421 @@
+// C ABI of the library (include/b200_gemm.h): validation, TMA descriptor encoding, launches,
+// the host-buffer session and the seeded input generator. No CPU fallback exists: without an
+// sm_100 device every compute entry point returns an error status.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../include/b200_gemm.h"
+#include "gemm_sm100.cuh"
+#include "ptx_sm100.cuh"
+#include "synth.h"
+
+namespace b200 {
+namespace {
+
+thread_local int t_last_cuda_error = 0;
+std::atomic<uint64_t> g_wait_budget_ns{2000000000ull};
+std::atomic<long long *> g_prof_ptr{nullptr};
+std::atomic<int> g_prof_blocks{0};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceInfo {
+    int ready = 0;  // 0 = not probed, 1 = usable, -1 = unusable
+    int status = B200_UNSUPPORTED_DEVICE;
+    int num_sms = 0;
+};
+
+constexpr int kMaxDevices = 64;
+DeviceInfo g_devices[kMaxDevices];
+std::mutex g_mutex;
+EncodeTiledFn g_encode = nullptr;
+
+int fail_cuda(cudaError_t e) {
+    t_last_cuda_error = static_cast<int>(e);
+    return B200_CUDA_ERROR;
+}
+
+// First call on a device: check the architecture, resolve the driver's tensor-map encoder and
+// opt the kernels into large dynamic shared memory.
+int device_info(const DeviceInfo **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (dev < 0 || dev >= kMaxDevices) return B200_UNSUPPORTED_DEVICE;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo &d = g_devices[dev];
+    if (d.ready == 0) {
+        d.ready = -1;
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess) {
+            d.status = fail_cuda(e);
+            return d.status;
+        }
+        if (prop.major != 10) {
+            d.status = B200_UNSUPPORTED_DEVICE;
+            return d.status;
+        }
+        d.num_sms = prop.multiProcessorCount;
+        if (!g_encode) {
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+            if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+                d.status = fail_cuda(e != cudaSuccess ? e : cudaErrorUnknown);
+                return d.status;
+            }
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        const int pe = prepare_kernels();
+        if (pe != 0) {
+            d.status = fail_cuda(static_cast<cudaError_t>(pe));
+            return d.status;
+        }
+        d.status = B200_OK;
+        d.ready = 1;
+    }
+    *out = &d;
+    return d.status;
+}
+
+int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const void *ptr, uint64_t inner,
+              uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * static_cast<uint64_t>(elem_bytes)};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(map, type, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        t_last_cuda_error = static_cast<int>(cudaErrorInvalidValue);
+        return B200_CUDA_ERROR;
+    }
+    return B200_OK;
+}
+
+void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
+    std::memset(p, 0, sizeof(*p));
+    p->tile_m = 128;
+    p->tile_n = 256;
+    while (p->tile_n > 16 && (N % p->tile_n)) p->tile_n /= 2;
+    p->segment_dim_k = 64;
+    p->bar_steps_a = 0;
+    p->bar_steps_b = 0;
+    p->bar_step_rows_a = p->tile_m;  // shift synchronisation off
+    p->bar_step_rows_b = p->tile_n;
+    p->tile_group_m = 8;
+    p->num_stages = 4;
+    p->num_producer_warps = 1;
+    p->num_consumer_warps = 4;
+    p->num_sms = 0;
+    p->cta_group = 1;
+    p->split_k = 1;
+    p->epilogue = 0;
+    (void)M;
+    (void)K;
+}
+
+int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M,
+              int64_t N, int64_t K, const b200_gemm_params *user, void *workspace, size_t workspace_bytes,
+              cudaStream_t stream) {
+    if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
+    b200_gemm_params local;
+    if (!user) {
+        default_params(M, N, K, &local);
+        user = &local;
+    }
+    const DeviceInfo *dev = nullptr;
+    int st = device_info(&dev);
+    if (st != B200_OK) return st;
+    const Plan p = make_plan(*user, dev->num_sms);
+    if (p.status != B200_OK) return p.status;
+    st = check_shape(p, M, N, K);
+    if (st != B200_OK) return st;
+    if (!A || !Bt || !D) return B200_INVALID_POINTER;
+    if (beta != 0.0f && !C) return B200_INVALID_POINTER;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bt) | reinterpret_cast<uintptr_t>(D) |
+         reinterpret_cast<uintptr_t>(C)) & 15u)
+        return B200_INVALID_POINTER;
+    if (p.split_k > 1) {
+        const size_t need = static_cast<size_t>(p.split_k) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
+        if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
+        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
+    }
+
+    GemmArgs a;
+    std::memset(&a, 0, sizeof(a));
+    const CUtensorMapDataType in_type = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    st = encode_2d(&a.map_a, in_type, 2, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M), kBoxK,
+                   static_cast<uint32_t>(p.a_box_rows));
+    if (st != B200_OK) return st;
+    st = encode_2d(&a.map_b, in_type, 2, Bt, static_cast<uint64_t>(K), static_cast<uint64_t>(N), kBoxK,
+                   static_cast<uint32_t>(p.chunk_n / p.cta_group));
+    if (st != B200_OK) return st;
+    int epi_mode = p.epi_mode;
+    if (p.mma_m != 128 || p.split_k > 1) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
+    if (epi_mode) {
+        st = encode_2d(&a.map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                       kEpiBoxCols, 32);
+        if (st != B200_OK) return st;
+    }
+    a.C = C;
+    a.D = D;
+    a.partial = static_cast<float *>(workspace);
+    a.alpha = alpha;
+    a.beta = beta;
+    a.M = static_cast<int>(M);
+    a.N = static_cast<int>(N);
+    a.K = static_cast<int>(K);
+    a.tiles_m = static_cast<int>((M + p.tile_m - 1) / p.tile_m);
+    a.tiles_n = static_cast<int>(N / p.tile_n);
+    a.num_tiles = a.tiles_m * a.tiles_n;
+    a.split_k = p.split_k;
+    a.num_units = a.num_tiles * p.split_k;
+    a.num_segs = static_cast<int>(K / p.seg_k);
+    a.tile_m = p.tile_m;
+    a.tile_n = p.tile_n;
+    a.cta_rows_a = p.cta_rows_a;
+    a.mma_m = p.mma_m;
+    a.kblocks = p.kblocks;
+    a.stages = p.stages;
+    a.tile_group_m = p.tile_group_m;
+    a.a_box_rows = p.a_box_rows;
+    a.a_boxes = p.a_boxes;
+    a.a_priv = p.a_priv;
+    a.a_bars = p.a_bars;
+    a.chunk_n = p.chunk_n;
+    a.b_priv = p.b_priv;
+    a.b_res_chunks = p.b_res_chunks;
+    a.b_bars = p.b_bars;
+    a.producer_warps = p.producer_warps;
+    a.epi_warps = p.epi_warps;
+    a.acc_cols = p.acc_cols;
+    a.tmem_cols = p.tmem_cols;
+    a.a_stage_bytes = p.a_stage_bytes;
+    a.stage_bytes = p.stage_bytes;
+    a.off_epi = p.off_epi;
+    a.off_bars = p.off_bars;
+    a.off_tmem_ptr = p.off_tmem_ptr;
+    a.epi_mode = epi_mode;
+    a.idesc_chunk = umma_idesc(p.tile_m, p.chunk_n, dtype == B200_BF16);
+    a.idesc_res = umma_idesc(p.tile_m, p.b_res_chunks * p.chunk_n, dtype == B200_BF16);
+    a.wait_budget_cycles = static_cast<long long>(g_wait_budget_ns.load() * 2ull);  // SM clock is below 2 GHz
+
+    a.prof = g_prof_ptr.load();
+    a.prof_blocks = g_prof_blocks.load();
+    a.debug_flags = user->reserved[0];
+
+    const int le = launch_gemm(p, a, stream);
+    if (le != 0) return fail_cuda(static_cast<cudaError_t>(le));
+    if (p.split_k > 1) {
+        const int re = launch_splitk_reduce(a.partial, C, D, alpha, beta, M * N, p.split_k, stream);
+        if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
+    }
+    return B200_OK;
+}
+
+__global__ void fill_u16_kernel(uint16_t *dst, long long begin, long long count, uint64_t key, int dist, float sigma,
+                                int dtype) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        dst[i] = synth::value_u16(key, static_cast<uint64_t>(begin + i), dist, sigma, dtype);
+}
+
+__global__ void fill_f32_kernel(float *dst, long long begin, long long count, uint64_t key, int dist, float sigma) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        dst[i] = synth::value(key, static_cast<uint64_t>(begin + i), dist, sigma);
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+struct b200_session {
+    int64_t max_m, max_n, max_k;
+    void *dA, *dB;
+    float *dC, *dD;
+    cudaStream_t stream;
+};
+
+extern "C" {
+
+int b200_gemm_default_params(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p) {
+    if (!p) return B200_INVALID_POINTER;
+    (void)dtype;
+    default_params(M, N, K, p);
+    return B200_OK;
+}
+
+int b200_gemm_validate(int64_t M, int64_t N, int64_t K, int dtype, const b200_gemm_params *p) {
+    if (!p) return B200_INVALID_POINTER;
+    if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
+    const Plan plan = make_plan(*p, p->num_sms > 0 ? p->num_sms : 148);
+    if (plan.status != B200_OK) return plan.status;
+    return check_shape(plan, M, N, K);
+}
+
+int64_t b200_gemm_smem_bytes(int dtype, const b200_gemm_params *p) {
+    (void)dtype;
+    if (!p) return -1;
+    const Plan plan = make_plan(*p, p->num_sms > 0 ? p->num_sms : 148);
+    return plan.status == B200_OK ? plan.smem_bytes : -1;
+}
+
+int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p) {
+    (void)K;
+    if (!p || p->split_k <= 1) return 0;
+    return static_cast<int64_t>(p->split_k) * M * N * static_cast<int64_t>(sizeof(float));
+}
+
+int b200_gemm_f16(const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M, int64_t N,
+                  int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes, void *stream) {
+    return gemm_impl(B200_F16, A, Bt, C, D, alpha, beta, M, N, K, p, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M, int64_t N,
+                   int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes, void *stream) {
+    return gemm_impl(B200_BF16, A, Bt, C, D, alpha, beta, M, N, K, p, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_session **out) {
+    if (!out || max_m <= 0 || max_n <= 0 || max_k <= 0) return B200_INVALID_SHAPE;
+    const DeviceInfo *dev = nullptr;
+    const int st = device_info(&dev);
+    if (st != B200_OK) return st;
+    b200_session *s = new (std::nothrow) b200_session();
+    if (!s) return B200_CUDA_ERROR;
+    std::memset(s, 0, sizeof(*s));
+    s->max_m = max_m;
+    s->max_n = max_n;
+    s->max_k = max_k;
+    cudaError_t e = cudaMalloc(&s->dA, static_cast<size_t>(max_m) * max_k * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&s->dB, static_cast<size_t>(max_n) * max_k * 2);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dC), static_cast<size_t>(max_m) * max_n * 4);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dD), static_cast<size_t>(max_m) * max_n * 4);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        b200_session_destroy(s);
+        return fail_cuda(e);
+    }
+    *out = s;
+    return B200_OK;
+}
+
+void b200_session_destroy(b200_session *s) {
+    if (!s) return;
+    if (s->stream) cudaStreamDestroy(s->stream);
+    cudaFree(s->dA);
+    cudaFree(s->dB);
+    cudaFree(s->dC);
+    cudaFree(s->dD);
+    delete s;
+}
+
+int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const void *hBt, const float *hC, float *hD,
+                           float alpha, float beta, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p) {
+    if (!s || !hA || !hBt || !hD) return B200_INVALID_POINTER;
+    if (M > s->max_m || N > s->max_n || K > s->max_k) return B200_INVALID_SHAPE;
+    if (beta != 0.0f && !hC) return B200_INVALID_POINTER;
+    cudaError_t e = cudaMemcpyAsync(s->dA, hA, static_cast<size_t>(M) * K * 2, cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(s->dB, hBt, static_cast<size_t>(N) * K * 2, cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess && beta != 0.0f)
+        e = cudaMemcpyAsync(s->dC, hC, static_cast<size_t>(M) * N * 4, cudaMemcpyHostToDevice, s->stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    const int st = gemm_impl(dtype, s->dA, s->dB, beta != 0.0f ? s->dC : nullptr, s->dD, alpha, beta, M, N, K, p, nullptr, 0,
+                             s->stream);
+    if (st != B200_OK) return st;
+    e = cudaMemcpyAsync(hD, s->dD, static_cast<size_t>(M) * N * 4, cudaMemcpyDeviceToHost, s->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return B200_OK;
+}
+
+int b200_device_status(void *stream, int info[4]) {
+    int rec[4] = {0, 0, 0, 0};
+    const int e = read_device_status(rec, static_cast<cudaStream_t>(stream));
+    if (e != 0) return fail_cuda(static_cast<cudaError_t>(e));
+    if (info)
+        for (int i = 0; i < 4; ++i) info[i] = rec[i];
+    return rec[0] == 0 ? B200_OK : rec[0];
+}
+
+void b200_set_wait_budget_ns(uint64_t ns) { g_wait_budget_ns.store(ns ? ns : 1); }
+
+void b200_set_profile_buffer(void *device_ptr, int blocks) {
+    g_prof_ptr.store(static_cast<long long *>(device_ptr));
+    g_prof_blocks.store(device_ptr ? blocks : 0);
+}
+
+const char *b200_status_string(int status) {
+    switch (status) {
+        case B200_OK: return "ok";
+        case B200_INVALID_CONFIG: return "invalid configuration (tunables outside the domain or over the shared/tensor memory budget)";
+        case B200_INVALID_SHAPE: return "invalid shape (M, N, K must be positive; N a multiple of tile_n, K of segment_dim_k)";
+        case B200_INVALID_POINTER: return "null or misaligned pointer";
+        case B200_CUDA_ERROR: return "CUDA error";
+        case B200_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired";
+        case B200_WORKSPACE_TOO_SMALL: return "workspace missing or too small";
+        case B200_UNSUPPORTED_DEVICE: return "no sm_100 device: this library has no other code path";
+        default: return "unknown status";
+    }
+}
+
+int b200_last_cuda_error(void) { return t_last_cuda_error; }
+
+int b200_num_sms(void) {
+    const DeviceInfo *dev = nullptr;
+    if (device_info(&dev) != B200_OK) return -1;
+    return dev->num_sms;
+}
+
+int b200_fill_u16_device(void *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                         float sigma, int dtype, void *stream) {
+    if (!dst || count < 0) return B200_INVALID_POINTER;
+    if (count == 0) return B200_OK;
+    int blocks = static_cast<int>((count + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    fill_u16_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint16_t *>(dst), begin, count,
+                                                                           synth::key_of(seed, tensor_id), dist, sigma, dtype);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? B200_OK : fail_cuda(e);
+}
+
+int b200_fill_f32_device(float *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                         float sigma, void *stream) {
+    if (!dst || count < 0) return B200_INVALID_POINTER;
+    if (count == 0) return B200_OK;
+    int blocks = static_cast<int>((count + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    fill_f32_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(dst, begin, count, synth::key_of(seed, tensor_id),
+                                                                           dist, sigma);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? B200_OK : fail_cuda(e);
+}
+
+void b200_fill_u16_host(uint16_t *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                        float sigma, int dtype) {
+    const uint64_t key = synth::key_of(seed, tensor_id);
+    for (int64_t i = 0; i < count; ++i) dst[i] = synth::value_u16(key, static_cast<uint64_t>(begin + i), dist, sigma, dtype);
+}
+
+void b200_fill_f32_host(float *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                        float sigma) {
+    const uint64_t key = synth::key_of(seed, tensor_id);
+    for (int64_t i = 0; i < count; ++i) dst[i] = synth::value(key, static_cast<uint64_t>(begin + i), dist, sigma);
+}
+
+}  // extern "C"

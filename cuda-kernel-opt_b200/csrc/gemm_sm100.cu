@@ -1,0 +1,792 @@
+// D = alpha * A * B^T + beta * C on the 5th-generation tensor cores of sm_100a.
+//
+// One persistent, warp-specialised kernel replaces the reference's four
+// gemm_shmem_tc_async*_kernel generations (matmul_shmem_tc_async.cu:211-341,
+// matmul_shmem_tc_async_opt_port_{0,1,2}.cu:225-354, :515-699, :638-878):
+//
+//   producer warp(s)  one elected lane issues TMA tile loads of A and B^T K-segments into a
+//                     num_stages deep shared-memory ring (replaces load_tile_async / load_tile);
+//   MMA warp          one thread issues tcgen05.mma from shared-memory descriptors, accumulating
+//                     in tensor memory (replaces the wmma fragment loops of consume);
+//   epilogue warps    drain tensor memory to registers, apply alpha / beta*C, write D either with
+//                     128-bit stores or through swizzled shared memory and TMA stores (replaces
+//                     store_matrix_sync + store_tile).
+//
+// Synchronisation is mbarriers only. A stage owns "full" barriers completed by TMA byte counts
+// and "empty" barriers completed by tcgen05.commit. The reference's shift synchronisation
+// (port_1.cu:164-328, port_2.cu:173-405: private barriers for the leading rows / columns of the
+// stage buffers, one residual barrier for the rest) becomes sub-tile barriers inside a stage:
+// the B^T buffer is split into column sub-tiles, each with its own TMA boxes, full barrier and
+// MMA, issued in load order, so the first sub-tile's MMA starts before the rest of the stage has
+// landed; the A buffer is split into row boxes with their own barriers.
+//
+// Two accumulator slots in tensor memory let the drain of tile i overlap the MMAs of tile i+1,
+// where the reference drains the whole pipeline at every tile (async.cu:339).
+//
+// Every wait is bounded: when its budget runs out the CTA records {code, block, barrier, phase}
+// in a device status word, raises a block-wide abort flag so all roles leave their loops, frees
+// its tensor memory and returns normally.
+#include "gemm_sm100.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+__device__ int g_device_status[4];
+
+namespace {
+
+constexpr int kMaxThreads = 544;  // (8 producer + 1 MMA + 8 epilogue warps) * 32
+
+struct Unit {
+    int m0, n0, slice, seg_begin, seg_end;
+};
+
+// Launch constants the role loops need, copied once from the kernel parameter into registers.
+// The parameter is __grid_constant__ and its address escapes (tensor maps), so reading a field
+// after an asm statement with a memory clobber is a fresh load through the parameter window;
+// those loads sat on the critical path of the single-thread producer and MMA loops.
+struct Cfg {
+    int num_units, num_tiles, tiles_m, tiles_n, tile_group_m, tile_m, tile_n, num_segs, split_k;
+    int kblocks, stages, stage_bytes, a_stage_bytes, cta_rows_a;
+    int a_box_rows, a_boxes, a_priv, a_bars, chunk_n, b_priv, b_res_chunks, b_bars;
+    int acc_cols, mma_m, epi_mode, epi_warps, M, N;
+    uint32_t idesc_chunk, idesc_res;
+    long long budget;
+};
+
+// Work unit -> tile and K slice. Tiles follow the reference's grouped order
+// (get_tile_offset_cd, port_0.cu:201-210): tile_group_m tile rows are walked column-major inside
+// a group so concurrently running CTAs share B^T column panels in L2; the last group may be short.
+__device__ __forceinline__ Unit decode_unit(const Cfg &c, int u) {
+    Unit w;
+    const int t = u % c.num_tiles;
+    w.slice = u / c.num_tiles;
+    const int group_tile_count = c.tile_group_m * c.tiles_n;
+    const int group_first_row = (t / group_tile_count) * c.tile_group_m;
+    const int group_rows = min(c.tiles_m - group_first_row, c.tile_group_m);
+    const int in_group = t % group_tile_count;
+    w.m0 = (group_first_row + in_group % group_rows) * c.tile_m;
+    w.n0 = (in_group / group_rows) * c.tile_n;
+    w.seg_begin = static_cast<int>(static_cast<long long>(w.slice) * c.num_segs / c.split_k);
+    w.seg_end = static_cast<int>(static_cast<long long>(w.slice + 1) * c.num_segs / c.split_k);
+    return w;
+}
+
+// Bounded mbarrier wait. Returns false when the budget ran out here or elsewhere in the block.
+__device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
+                                       int bar_id) {
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+#ifdef B200_WAIT_SLEEP
+        __nanosleep(B200_WAIT_SLEEP);
+#endif
+        if ((++spins & 31u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > budget) {
+                *abort_flag = 1;
+                if (atomicCAS(&g_device_status[0], 0, B200_DEVICE_TIMEOUT) == 0) {
+                    g_device_status[1] = static_cast<int>(blockIdx.x);
+                    g_device_status[2] = bar_id;
+                    g_device_status[3] = static_cast<int>(parity);
+                }
+                __threadfence();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
+                                         int bar_id) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return wait_slow(bar, parity, budget, abort_flag, bar_id);
+}
+
+// All lanes of a converged warp wait; the result is the same in every lane.
+__device__ __forceinline__ bool wait_all(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
+                                         int bar_id) {
+    bool ok = mbar_try_wait(bar, parity);
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if (!ok) ok = wait_slow(bar, parity, budget, abort_flag, bar_id);
+    return __all_sync(0xffffffffu, ok);
+}
+
+template <int CG>
+__device__ __forceinline__ void commit_to(uint32_t bar) {
+    if constexpr (CG == 1) {
+        umma_commit<1>(bar);
+    } else {
+        // Both CTAs of the pair hold a barrier at this offset; complete the two of them.
+        asm volatile(
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+            "h"(static_cast<uint16_t>(3))
+            : "memory");
+    }
+}
+
+}  // namespace
+
+// CG: CTAs per tcgen05 group. SIMPLE: one full and one empty barrier per stage (no sub-tiles),
+// which allows the lean producer and MMA loops below. PROF: per-role cycle counters.
+template <int CG, bool SIMPLE, bool PROF>
+__global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid_constant__ GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    Cfg c;
+    c.num_units = g.num_units; c.num_tiles = g.num_tiles; c.tiles_m = g.tiles_m; c.tiles_n = g.tiles_n;
+    c.tile_group_m = g.tile_group_m; c.tile_m = g.tile_m; c.tile_n = g.tile_n; c.num_segs = g.num_segs;
+    c.split_k = g.split_k; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
+    c.a_stage_bytes = g.a_stage_bytes; c.cta_rows_a = g.cta_rows_a; c.a_box_rows = g.a_box_rows;
+    c.a_boxes = g.a_boxes; c.a_priv = g.a_priv; c.a_bars = g.a_bars; c.chunk_n = g.chunk_n; c.b_priv = g.b_priv;
+    c.b_res_chunks = g.b_res_chunks; c.b_bars = g.b_bars; c.acc_cols = g.acc_cols; c.mma_m = g.mma_m;
+    c.epi_mode = g.epi_mode; c.epi_warps = g.epi_warps; c.M = g.M; c.N = g.N;
+    c.idesc_chunk = g.idesc_chunk; c.idesc_res = g.idesc_res; c.budget = g.wait_budget_cycles;
+    const int off_bars = g.off_bars, off_tmem_ptr = g.off_tmem_ptr, off_epi = g.off_epi;
+    const int tmem_cols = g.tmem_cols;
+    const int P = g.producer_warps;
+    const int dbg = g.debug_flags;  // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage)
+    const float g_alpha = g.alpha, g_beta = g.beta;
+    const float *const gC = g.C;
+    float *const gD = g.D;
+    float *const g_partial = g.partial;
+    long long *const prof = (PROF && g.prof && static_cast<int>(blockIdx.x) < g.prof_blocks) ? g.prof + 16 * blockIdx.x : nullptr;
+
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *const sm = smem_raw + (base - raw);
+    const uint32_t bars = base + off_bars;
+    volatile int *const abort_flag = reinterpret_cast<volatile int *>(sm + off_tmem_ptr + 4);
+    volatile uint32_t *const tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + off_tmem_ptr);
+
+    // Warp-uniform values are broadcast from lane 0 so the compiler can prove them uniform: role
+    // dispatch and the role loops then stay convergent code, and addresses, descriptors and
+    // coordinates of the TMA / tcgen05 instructions can live in uniform registers.
+    const int tid = threadIdx.x;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const int lane = tid & 31;
+    const int mma_warp = P;
+    const uint32_t rank = (CG == 2) ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
+    const int group = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int num_groups = static_cast<int>(gridDim.x) / CG;
+
+    // Barrier map, per stage: [full A x a_bars][full B x b_bars][empty A][pad x (a_bars-1)][empty B x b_bars];
+    // after the stages: tmem_full[2], tmem_empty[2].
+    const uint32_t stage_bar_bytes = 8u * 2u * static_cast<uint32_t>(c.a_bars + c.b_bars);
+    const uint32_t full_b_off = 8u * static_cast<uint32_t>(c.a_bars);
+    const uint32_t empty_a_off = 8u * static_cast<uint32_t>(c.a_bars + c.b_bars);
+    const uint32_t empty_b_off = 8u * static_cast<uint32_t>(2 * c.a_bars + c.b_bars);
+    const uint32_t tmem_full0 = bars + static_cast<uint32_t>(c.stages) * stage_bar_bytes;
+    const uint32_t tmem_empty0 = tmem_full0 + 16u;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < c.stages; ++s) {
+            const uint32_t sb = bars + static_cast<uint32_t>(s) * stage_bar_bytes;
+            const bool one_full = (c.a_bars == 1 && c.b_bars == 1);
+            for (int j = 0; j < c.a_bars; ++j) mbar_init(sb + 8u * j, (one_full && P > 1) ? 2 : 1);
+            for (int t = 0; t < c.b_bars; ++t) mbar_init(sb + full_b_off + 8u * t, 1);
+            mbar_init(sb + empty_a_off, 1);
+            for (int t = 0; t < c.b_bars; ++t) mbar_init(sb + empty_b_off + 8u * t, 1);
+        }
+        mbar_init(tmem_full0, 1);
+        mbar_init(tmem_full0 + 8, 1);
+        mbar_init(tmem_empty0, c.epi_warps * CG);
+        mbar_init(tmem_empty0 + 8, c.epi_warps * CG);
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&g.map_a);
+        tma_prefetch_desc(&g.map_b);
+        if (c.epi_mode) tma_prefetch_desc(&g.map_d);
+    }
+    if (warp == mma_warp) {
+        tmem_alloc<CG>(base + off_tmem_ptr, static_cast<uint32_t>(tmem_cols));
+        tmem_relinquish<CG>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if constexpr (CG == 2) {
+        cluster_arrive();
+        cluster_wait();
+    }
+    tc_fence_after_sync();
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+
+    const int b_box_rows = c.chunk_n / CG;  // B^T rows per TMA box in this CTA
+
+    // With one barrier per operand per stage (no sub-tiles) A and B^T share one full and one
+    // empty barrier: one wait and one commit per stage for the MMA warp.
+    const bool merged = (c.a_bars == 1 && c.b_bars == 1);
+
+    if (SIMPLE && warp < P) {
+        // ------------------------------------------------------------------ producers, lean form
+        // One full and one empty barrier per stage. With one producer warp it issues the A and
+        // the B^T boxes; with more, warp 0 issues A and warp 1 issues B^T (the reference's split,
+        // port_1.cu:197) and both arm the same full barrier. The loop carries running addresses,
+        // so one stage costs a wait, an arm and one copy instruction per box.
+        const bool do_a = (P == 1) || (warp == 0);
+        const bool do_b = (P == 1) || (warp == 1);
+        if (do_a || do_b) {
+            const bool issuer = elect_one();
+            const uint32_t a_kb_bytes = static_cast<uint32_t>(c.cta_rows_a * kSwizzleBytes);
+            const uint32_t b_kb_bytes = static_cast<uint32_t>((c.tile_n / CG) * kSwizzleBytes);
+            const uint32_t my_bytes = static_cast<uint32_t>(c.kblocks * CG) * ((do_a ? a_kb_bytes : 0u) + (do_b ? b_kb_bytes : 0u));
+            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
+            const bool arm = issuer && rank == 0;
+            const bool issue_a = issuer && do_a && !(dbg & 2);
+            const bool issue_b = issuer && do_b && !(dbg & 2);
+            int s = 0;
+            uint32_t ph = 0, it = 0;
+            uint32_t stage = base, sb = bars, sbl = bars_leader;
+            bool ok = true;
+            long long t_wait = 0;
+            const long long t_begin = PROF ? clock64() : 0;
+            for (int u = group; ok && u < c.num_units; u += num_groups) {
+                const Unit w = decode_unit(c, u);
+                const int a_row = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
+                const int b_row = w.n0 + static_cast<int>(rank) * (c.tile_n / CG);
+                int k = w.seg_begin * c.kblocks * kBoxK;
+                for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
+                    const long long tw = PROF ? clock64() : 0;
+                    ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
+                    if (PROF) t_wait += clock64() - tw;
+                    if (!ok) break;
+                    if (arm) mbar_arrive_expect_tx(sb, (dbg & 2) ? 0u : my_bytes);
+                    uint32_t da = stage, db = stage + static_cast<uint32_t>(c.a_stage_bytes);
+                    for (int kb = 0; kb < c.kblocks; ++kb) {
+                        if constexpr (CG == 2) {
+                            if (issue_a) tma_load_2d_pair(da, &g.map_a, sbl, k, a_row);
+                            if (issue_b) tma_load_2d_pair(db, &g.map_b, sbl, k, b_row);
+                        } else {
+                            if (issue_a) tma_load_2d(da, &g.map_a, sb, k, a_row);
+                            if (issue_b) tma_load_2d(db, &g.map_b, sb, k, b_row);
+                        }
+                        da += a_kb_bytes;
+                        db += b_kb_bytes;
+                        k += kBoxK;
+                    }
+                    ++it;
+                    stage += static_cast<uint32_t>(c.stage_bytes);
+                    sb += stage_bar_bytes;
+                    sbl += stage_bar_bytes;
+                    if (++s == c.stages) {
+                        s = 0;
+                        ph ^= 1u;
+                        stage = base;
+                        sb = bars;
+                        sbl = bars_leader;
+                    }
+                }
+            }
+            if (PROF && prof && lane == 0) {
+                prof[warp == 0 ? 0 : 3] = t_wait;
+                prof[warp == 0 ? 1 : 4] = clock64() - t_begin;
+                prof[warp == 0 ? 2 : 5] = it;
+            }
+        }
+    } else if (SIMPLE && warp == mma_warp) {
+        // ------------------------------------------------------------------ MMA issue, lean form
+        if (rank == 0) {
+            const bool issuer = elect_one();
+            const bool issue = issuer && !(dbg & 1);
+            const uint64_t a_desc0 = umma_desc_sw128(base);
+            const uint64_t b_desc0 = umma_desc_sw128(base + static_cast<uint32_t>(c.a_stage_bytes));
+            const uint64_t stage_step = static_cast<uint64_t>(c.stage_bytes >> 4);
+            const uint64_t a_kb_step = static_cast<uint64_t>((c.cta_rows_a * kSwizzleBytes) >> 4);
+            const uint64_t b_kb_step = static_cast<uint64_t>(((c.tile_n / CG) * kSwizzleBytes) >> 4);
+            const uint32_t idesc = c.idesc_res;
+            int s = 0;
+            uint32_t ph = 0, it = 0, tl = 0;
+            uint32_t sb = bars;
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            bool ok = true;
+            long long t_full = 0, t_acc = 0;
+            const long long t_begin = PROF ? clock64() : 0;
+            for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
+                const Unit w = decode_unit(c, u);
+                const uint32_t acc = tl & 1u;
+                const uint32_t aph = (tl >> 1) & 1u;
+                const long long ta = PROF ? clock64() : 0;
+                ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                if (PROF) t_acc += clock64() - ta;
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_addr = tmem_base + acc * static_cast<uint32_t>(c.acc_cols);
+                uint32_t accumulate = 0;
+                for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
+                    const long long tf = PROF ? clock64() : 0;
+                    ok = wait_all(sb, ph, c.budget, abort_flag, 400 + s);
+                    if (PROF) t_full += clock64() - tf;
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    uint64_t da = a_desc, db = b_desc;
+                    for (int kb = 0; kb < c.kblocks; ++kb) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            // +32 bytes per 16-element K step inside the 128-byte swizzle row
+                            if (issue) umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, accumulate);
+                            accumulate = 1;
+                        }
+                        da += a_kb_step;
+                        db += b_kb_step;
+                    }
+                    if (issuer) commit_to<CG>(sb + empty_a_off);
+                    ++it;
+                    a_desc += stage_step;
+                    b_desc += stage_step;
+                    sb += stage_bar_bytes;
+                    if (++s == c.stages) {
+                        s = 0;
+                        ph ^= 1u;
+                        a_desc = a_desc0;
+                        b_desc = b_desc0;
+                        sb = bars;
+                    }
+                }
+                if (!ok) break;
+                if (issuer) commit_to<CG>(tmem_full0 + 8u * acc);
+            }
+            if (PROF && prof && lane == 0) {
+                prof[6] = t_full;
+                prof[7] = t_acc;
+                prof[8] = clock64() - t_begin;
+                prof[9] = it;
+            }
+        }
+        __syncwarp();
+    } else if (warp < P) {
+        // ------------------------------------------------------------------ producers, general form (sub-tile barriers)
+        // The warp runs its loops converged; one elected lane issues. In a two-CTA pair only the
+        // leader arms the full barriers (with the bytes of both CTAs); the peer's copies complete
+        // the leader's barriers through their cluster addresses.
+        const bool do_a = (P == 1) || (warp == 0);
+        const bool do_b = (P == 1) || (warp == 1);
+        if (do_a || do_b) {
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            long long t_wait = 0, t_issue_a = 0;
+            const long long t_begin = clock64();
+            const uint32_t a_priv_bytes = static_cast<uint32_t>(c.kblocks * c.a_box_rows * kSwizzleBytes) * CG;
+            const uint32_t a_res_bytes = a_priv_bytes * static_cast<uint32_t>(c.a_boxes - c.a_priv);
+            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
+            const bool issuer = elect_one();
+            for (int u = group; ok && u < c.num_units; u += num_groups) {
+                const Unit w = decode_unit(c, u);
+                const int a_row0 = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
+                for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg, ++it) {
+                    const int k0 = seg * c.kblocks * kBoxK;
+                    const uint32_t stage = base + static_cast<uint32_t>(s * c.stage_bytes);
+                    const uint32_t sb_off = static_cast<uint32_t>(s) * stage_bar_bytes;
+                    const uint32_t sb = bars + sb_off;            // this CTA's barriers (empty: waited here)
+                    const uint32_t sbl = bars_leader + sb_off;    // the leader's barriers (full: completed there)
+                    if (do_a) {
+                        const long long tw = prof ? clock64() : 0;
+                        ok = __all_sync(0xffffffffu, wait_bar(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s));
+                        if (prof) t_wait += clock64() - tw;
+                        if (!ok) break;
+                        const long long ti = prof ? clock64() : 0;
+                        for (int j = 0; j < c.a_bars; ++j) {
+                            const int first = j < c.a_priv ? j : c.a_priv;
+                            const int nbox = j < c.a_priv ? 1 : c.a_boxes - c.a_priv;
+                            uint32_t bytes = j < c.a_priv ? a_priv_bytes : a_res_bytes;
+                            if (merged && P == 1) bytes += static_cast<uint32_t>(c.kblocks * c.tile_n * kSwizzleBytes);
+                            if (dbg & 2) bytes = 0;
+                            if (issuer && rank == 0) mbar_arrive_expect_tx(sb + 8u * j, bytes);
+                            for (int kb = 0; kb < c.kblocks; ++kb) {
+                                for (int b = first; b < first + nbox; ++b) {
+                                    const uint32_t dst = stage + static_cast<uint32_t>(
+                                        (kb * c.cta_rows_a + b * c.a_box_rows) * kSwizzleBytes);
+                                    if (issuer && !(dbg & 2)) {
+                                        if constexpr (CG == 2) tma_load_2d_pair(dst, &g.map_a, sbl + 8u * j, k0 + kb * kBoxK, a_row0 + b * c.a_box_rows);
+                                        else tma_load_2d(dst, &g.map_a, sb + 8u * j, k0 + kb * kBoxK, a_row0 + b * c.a_box_rows);
+                                    }
+                                }
+                            }
+                        }
+                        if (prof) t_issue_a += clock64() - ti;
+                    }
+                    if (do_b) {
+                        const uint32_t stage_b = stage + static_cast<uint32_t>(c.a_stage_bytes);
+                        for (int t = 0; ok && t < c.b_bars; ++t) {
+                            if (!(merged && do_a)) {  // merged + same warp: the stage was acquired above
+                                const long long tw = prof ? clock64() : 0;
+                                ok = __all_sync(0xffffffffu, wait_bar(sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u,
+                                                                      c.budget, abort_flag, 200 + s * 32 + t));
+                                if (prof) t_wait += clock64() - tw;
+                                if (!ok) break;
+                            }
+                            {
+                                const int off_t = t * c.chunk_n;  // the residual follows the private sub-tiles
+                                const int w_t = t < c.b_priv ? c.chunk_n : c.b_res_chunks * c.chunk_n;
+                                const int rows_t = w_t / CG;
+                                const int nbox = rows_t / b_box_rows;
+                                const uint32_t bar_off = merged ? 0u : full_b_off + 8u * t;
+                                if (issuer && rank == 0 && !(merged && P == 1))
+                                    mbar_arrive_expect_tx(sb + bar_off, (dbg & 2) ? 0u : static_cast<uint32_t>(c.kblocks * w_t * kSwizzleBytes));
+                                const uint32_t sub = stage_b + static_cast<uint32_t>((off_t / CG) * c.kblocks * kSwizzleBytes);
+                                const int b_row0 = w.n0 + off_t + static_cast<int>(rank) * rows_t;
+                                for (int kb = 0; kb < c.kblocks; ++kb) {
+                                    for (int b = 0; b < nbox; ++b) {
+                                        const uint32_t dst = sub + static_cast<uint32_t>((kb * rows_t + b * b_box_rows) * kSwizzleBytes);
+                                        if (issuer && !(dbg & 2)) {
+                                            if constexpr (CG == 2) tma_load_2d_pair(dst, &g.map_b, sbl + bar_off, k0 + kb * kBoxK, b_row0 + b * b_box_rows);
+                                            else tma_load_2d(dst, &g.map_b, sb + bar_off, k0 + kb * kBoxK, b_row0 + b * b_box_rows);
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    if (++s == c.stages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+            if (prof && lane == 0) {
+                prof[warp == 0 ? 0 : 3] = t_wait;
+                prof[warp == 0 ? 1 : 4] = clock64() - t_begin;
+                prof[warp == 0 ? 2 : 5] = it;
+                if (warp == 0) prof[13] = t_issue_a;
+            }
+        }
+    } else if (warp == mma_warp) {
+        // ------------------------------------------------------------------ MMA issue
+        if (rank == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t it = 0;
+            uint32_t tl = 0;
+            bool ok = true;
+            long long t_full = 0, t_acc = 0, t_mma = 0, t_commit = 0;
+            const long long t_begin = clock64();
+            const bool issuer = elect_one();
+            for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
+                const Unit w = decode_unit(c, u);
+                const uint32_t acc = tl & 1u;
+                const uint32_t aph = (tl >> 1) & 1u;
+                const long long ta = prof ? clock64() : 0;
+                ok = __all_sync(0xffffffffu, wait_bar(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc)));
+                if (prof) t_acc += clock64() - ta;
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_base = tmem_base + acc * static_cast<uint32_t>(c.acc_cols);
+                for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg, ++it) {
+                    const uint32_t stage = base + static_cast<uint32_t>(s * c.stage_bytes);
+                    const uint32_t stage_b = stage + static_cast<uint32_t>(c.a_stage_bytes);
+                    const uint32_t sb = bars + static_cast<uint32_t>(s) * stage_bar_bytes;
+                    const long long tf = prof ? clock64() : 0;
+                    for (int j = 0; ok && j < c.a_bars; ++j)
+                        ok = __all_sync(0xffffffffu, wait_bar(sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j));
+                    if (prof) t_full += clock64() - tf;
+                    if (!ok) break;
+                    const uint32_t first_seg = (seg == w.seg_begin) ? 0u : 1u;
+                    for (int t = 0; t < c.b_bars; ++t) {
+                        if (!merged) {
+                            const long long tb = prof ? clock64() : 0;
+                            ok = __all_sync(0xffffffffu, wait_bar(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t));
+                            if (prof) t_full += clock64() - tb;
+                            if (!ok) break;
+                        }
+                        tc_fence_after_sync();
+                        const long long tm = prof ? clock64() : 0;
+                        {
+                            const int off_t = t * c.chunk_n;
+                            const int w_t = t < c.b_priv ? c.chunk_n : c.b_res_chunks * c.chunk_n;
+                            const int rows_t = w_t / CG;
+                            const uint32_t idesc = t < c.b_priv ? c.idesc_chunk : c.idesc_res;
+                            const uint32_t sub = stage_b + static_cast<uint32_t>((off_t / CG) * c.kblocks * kSwizzleBytes);
+                            for (int kb = 0; kb < c.kblocks; ++kb) {
+                                const uint64_t adesc = umma_desc_sw128(stage + static_cast<uint32_t>(kb * c.cta_rows_a * kSwizzleBytes));
+                                const uint64_t bdesc = umma_desc_sw128(sub + static_cast<uint32_t>(kb * rows_t * kSwizzleBytes));
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    // +32 bytes per 16-element K step inside the 128-byte swizzle row
+                                    if (issuer && !(dbg & 1))
+                                        umma_f16<CG>(d_base + static_cast<uint32_t>(off_t), adesc + static_cast<uint64_t>(2 * i),
+                                                     bdesc + static_cast<uint64_t>(2 * i), idesc, (first_seg | kb | i) ? 1u : 0u);
+                                }
+                            }
+                            if (!merged && issuer) commit_to<CG>(sb + empty_b_off + 8u * t);
+                        }
+                        if (prof) t_mma += clock64() - tm;
+                    }
+                    if (!ok) break;
+                    const long long tc2 = prof ? clock64() : 0;
+                    if (issuer) commit_to<CG>(sb + empty_a_off);
+                    if (prof) t_commit += clock64() - tc2;
+                    if (++s == c.stages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                if (issuer) commit_to<CG>(tmem_full0 + 8u * acc);
+            }
+            if (prof && lane == 0) {
+                prof[6] = t_full;
+                prof[7] = t_acc;
+                prof[8] = clock64() - t_begin;
+                prof[9] = it;
+                prof[14] = t_mma;
+                prof[15] = t_commit;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int e = warp - (P + 1);          // 0 .. epi_warps-1
+        const int q = warp & 3;                // TMEM lane quarter this warp may read
+        const int halves = c.epi_warps / 4;    // 1 or 2 warps per quarter
+        const int half = e / 4;
+        int col_begin = 0, col_end = c.tile_n;
+        if (halves == 2) {
+            const int mid = ((c.tile_n / 2 + 31) / 32) * 32;
+            col_begin = half ? min(mid, c.tile_n) : 0;
+            col_end = half ? c.tile_n : min(mid, c.tile_n);
+        }
+        const uint32_t tmem_empty_leader = (CG == 2) ? mapa_shared(tmem_empty0, 0) : tmem_empty0;
+        const uint32_t epi_buf = base + static_cast<uint32_t>(off_epi) + static_cast<uint32_t>(e) * 2u * 4096u;
+        // row of the tile this thread drains: 128-row atoms map row r to lane r; 64-row atoms use
+        // lanes 0-15 of each quarter (row 16 * quarter + lane).
+        const int row_in_cta = (c.mma_m == 128) ? (q * 32 + lane) : (q * 16 + (lane & 15));
+        const bool lane_has_row = (c.mma_m == 128) || (lane < 16);
+        const bool to_partial = c.split_k > 1;
+        const float alpha = to_partial ? 1.0f : g_alpha;
+        const float beta = to_partial ? 0.0f : g_beta;
+        uint32_t tl = 0;
+        uint32_t store_idx = 0;
+        bool ok = true;
+        long long t_tfull = 0;
+        const long long t_begin = clock64();
+        for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
+            const Unit w = decode_unit(c, u);
+            const uint32_t acc = tl & 1u;
+            const uint32_t aph = (tl >> 1) & 1u;
+            const long long te = prof ? clock64() : 0;
+            ok = wait_bar(tmem_full0 + 8u * acc, aph, c.budget, abort_flag, 600 + static_cast<int>(acc));
+            ok = __all_sync(0xffffffffu, ok);
+            if (prof) t_tfull += clock64() - te;
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = w.m0 + static_cast<int>(rank) * c.cta_rows_a + row_in_cta;
+            const bool row_ok = lane_has_row && row < c.M;
+            float *const out = to_partial ? g_partial + static_cast<size_t>(w.slice) * c.M * c.N : gD;
+            const size_t row_off = static_cast<size_t>(row) * c.N + w.n0;
+            const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
+            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+                uint32_t r[32];
+                const bool wide = (col_end - c0) >= 32;
+                if (wide) {
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
+                } else {
+                    uint32_t r16[16];
+                    tmem_ld_32x16(t_row + static_cast<uint32_t>(c0), r16);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = r16[j];
+#pragma unroll
+                    for (int j = 16; j < 32; ++j) r[j] = 0;
+                }
+                tmem_ld_wait();
+                const int nvec = wide ? 8 : 4;
+                if (c.epi_mode == 0 || !wide) {
+                    if (row_ok) {
+                        float4 *dst = reinterpret_cast<float4 *>(out + row_off + c0);
+                        const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (j < nvec) {
+                                float4 v;
+                                v.x = alpha * __uint_as_float(r[4 * j + 0]);
+                                v.y = alpha * __uint_as_float(r[4 * j + 1]);
+                                v.z = alpha * __uint_as_float(r[4 * j + 2]);
+                                v.w = alpha * __uint_as_float(r[4 * j + 3]);
+                                if (beta != 0.0f) {
+                                    const float4 cv = __ldg(csrc + j);
+                                    v.x += beta * cv.x;
+                                    v.y += beta * cv.y;
+                                    v.z += beta * cv.z;
+                                    v.w += beta * cv.w;
+                                }
+                                dst[j] = v;
+                            }
+                        }
+                    }
+                } else {
+                    // registers -> 128-byte-swizzled shared memory -> one TMA store of 32 x 32 fp32
+                    const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
+                    if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
+                    __syncwarp();
+                    const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 v;
+                        v.x = alpha * __uint_as_float(r[4 * j + 0]);
+                        v.y = alpha * __uint_as_float(r[4 * j + 1]);
+                        v.z = alpha * __uint_as_float(r[4 * j + 2]);
+                        v.w = alpha * __uint_as_float(r[4 * j + 3]);
+                        if (beta != 0.0f && row_ok) {
+                            const float4 cv = __ldg(csrc + j);
+                            v.x += beta * cv.x;
+                            v.y += beta * cv.y;
+                            v.z += beta * cv.z;
+                            v.w += beta * cv.w;
+                        }
+                        const uint32_t addr = buf + static_cast<uint32_t>(lane) * 128u + static_cast<uint32_t>((j ^ (lane & 7)) * 16);
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+                                     "f"(v.w)
+                                     : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&g.map_d, buf, w.n0 + c0, w.m0 + static_cast<int>(rank) * c.cta_rows_a + q * 32);
+                        tma_store_commit();
+                    }
+                    ++store_idx;
+                }
+            }
+            // accumulator slot drained: hand it back to the MMA thread
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_leader + 8u * acc);
+                else mbar_arrive(tmem_empty0 + 8u * acc);
+            }
+        }
+        if (c.epi_mode && lane == 0) tma_store_wait<0>();
+        __syncwarp();
+        if (prof && e == 0 && lane == 0) {
+            prof[10] = t_tfull;
+            prof[11] = clock64() - t_begin;
+            prof[12] = tl;
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if constexpr (CG == 2) {
+        cluster_arrive();
+        cluster_wait();
+    }
+    if (warp == mma_warp) {
+        if (*abort_flag) {
+            // give copies and MMAs still in flight a bounded time to land before the memory goes
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {
+            }
+        }
+        tc_fence_after_sync();
+        tmem_dealloc<CG>(tmem_base, static_cast<uint32_t>(tmem_cols));
+    }
+}
+
+// D = alpha * sum_s partial[s] + beta * C, the second step of split-K. Slices are summed in
+// ascending order, so the result does not depend on scheduling.
+__global__ void splitk_reduce_kernel(const float4 *__restrict__ partial, const float4 *__restrict__ C,
+                                     float4 *__restrict__ D, float alpha, float beta, long long n4, int split_k) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 s = partial[i];
+        for (int k = 1; k < split_k; ++k) {
+            const float4 v = partial[static_cast<long long>(k) * n4 + i];
+            s.x += v.x;
+            s.y += v.y;
+            s.z += v.z;
+            s.w += v.w;
+        }
+        float4 o;
+        o.x = alpha * s.x;
+        o.y = alpha * s.y;
+        o.z = alpha * s.z;
+        o.w = alpha * s.w;
+        if (beta != 0.0f) {
+            const float4 c = C[i];
+            o.x += beta * c.x;
+            o.y += beta * c.y;
+            o.z += beta * c.z;
+            o.w += beta * c.w;
+        }
+        D[i] = o;
+    }
+}
+
+namespace {
+typedef void (*KernelFn)(const GemmArgs);
+
+KernelFn pick_kernel(int cta_group, bool simple, bool prof) {
+    if (cta_group == 2) {
+        if (simple) return prof ? gemm_sm100_kernel<2, true, true> : gemm_sm100_kernel<2, true, false>;
+        return prof ? gemm_sm100_kernel<2, false, true> : gemm_sm100_kernel<2, false, false>;
+    }
+    if (simple) return prof ? gemm_sm100_kernel<1, true, true> : gemm_sm100_kernel<1, true, false>;
+    return prof ? gemm_sm100_kernel<1, false, true> : gemm_sm100_kernel<1, false, false>;
+}
+}  // namespace
+
+int prepare_kernels() {
+    for (int cg = 1; cg <= 2; ++cg)
+        for (int simple = 0; simple < 2; ++simple)
+            for (int prof = 0; prof < 2; ++prof) {
+                const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void *>(pick_kernel(cg, simple != 0, prof != 0)),
+                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+                if (e != cudaSuccess) return static_cast<int>(e);
+            }
+    return 0;
+}
+
+int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p.grid), 1, 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(p.threads), 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(p.smem_bytes);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    if (p.cta_group == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    const bool simple = (p.a_bars == 1 && p.b_bars == 1 && p.a_boxes == 1 && p.b_priv == 0 && p.b_res_chunks == 1);
+    const KernelFn fn = pick_kernel(p.cta_group, simple, args.prof != nullptr);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, args);
+    return static_cast<int>(e);
+}
+
+int launch_splitk_reduce(const float *partial, const float *C, float *D, float alpha, float beta, int64_t mn,
+                         int split_k, cudaStream_t stream) {
+    const long long n4 = mn / 4;
+    int blocks = static_cast<int>((n4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4 *>(partial),
+                                                     reinterpret_cast<const float4 *>(C), reinterpret_cast<float4 *>(D),
+                                                     alpha, beta, n4, split_k);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int read_device_status(int out[4], cudaStream_t stream) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int host[4] = {0, 0, 0, 0};
+    e = cudaMemcpyFromSymbol(host, g_device_status, sizeof(host));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (host[0] != 0) {
+        const int zero[4] = {0, 0, 0, 0};
+        e = cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero));
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    for (int i = 0; i < 4; ++i) out[i] = host[i];
+    return 0;
+}
+
+}  // namespace b200

@@ -1,0 +1,49 @@
+// Arguments of the sm_100a GEMM kernel and its launch entry, shared by the kernel and the C ABI.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "plan.h"
+
+namespace b200 {
+
+struct alignas(64) GemmArgs {
+    CUtensorMap map_a;  // A   as {K, M}  two-byte elements, box {64, a_box_rows}, 128-byte swizzle
+    CUtensorMap map_b;  // B^T as {K, N}  two-byte elements, box {64, chunk_n / cta_group}
+    CUtensorMap map_d;  // D   as {N, M}  fp32, box {32, 32}, 128-byte swizzle (TMA-store epilogue)
+    const float *C;
+    float *D;
+    float *partial;     // split-K workspace: split_k slabs of M x N fp32
+    float alpha, beta;
+    int M, N, K;
+    int tiles_m, tiles_n, num_tiles, num_units;
+    int num_segs;       // K / seg_k
+    int split_k;
+    // plan
+    int tile_m, tile_n, cta_rows_a, mma_m;
+    int kblocks, stages, tile_group_m;
+    int a_box_rows, a_boxes, a_priv, a_bars;
+    int chunk_n, b_priv, b_res_chunks, b_bars;
+    int producer_warps, epi_warps;
+    int acc_cols, tmem_cols;
+    int a_stage_bytes, stage_bytes;
+    int off_epi, off_bars, off_tmem_ptr;
+    int epi_mode;
+    uint32_t idesc_chunk, idesc_res;
+    long long wait_budget_cycles;
+    long long *prof;    // optional cycle counters, 16 per CTA for the first prof_blocks CTAs
+    int prof_blocks;
+    int debug_flags;
+};
+
+// Launches the kernel for plan p on `stream`. Returns a cudaError_t as int.
+int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream);
+int launch_splitk_reduce(const float *partial, const float *C, float *D, float alpha, float beta, int64_t mn,
+                         int split_k, cudaStream_t stream);
+// Reads and clears the device-side timeout record {code, block, barrier, phase}.
+int read_device_status(int out[4], cudaStream_t stream);
+int prepare_kernels();  // opt-in shared memory size; once per device
+
+}  // namespace b200

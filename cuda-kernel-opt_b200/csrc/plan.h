@@ -1,0 +1,176 @@
+// Host-side planning: turns the caller's tunables into the launch plan of the sm_100a kernel
+// (tile split, TMA boxes, barrier counts, shared-memory map, TMEM columns, block size) or a
+// status. Pure C++: usable and testable without a GPU.
+//
+// It is the counterpart of the reference launcher's asserts and of get_shmem_req /
+// get_num_acc / get_warp_tile_rows (matmul_shmem_tc_async_opt_port_2.cu:1112-1125, :1057-1086,
+// :158-169): same tunables, same refusal of what does not fit, but as return codes.
+#pragma once
+
+#include <cstdint>
+#include "../../include/b200_gemm.h"
+
+namespace b200 {
+
+constexpr int kSmemLimit = 232448;      // 227 KiB: largest opt-in dynamic shared memory per CTA
+constexpr int kTmemColumns = 512;       // 32-bit columns of tensor memory per SM
+constexpr int kSwizzleBytes = 128;      // one TMA box / UMMA atom row: 64 two-byte elements
+constexpr int kBoxK = 64;               // K elements per TMA box
+constexpr int kMaxSubBars = 17;         // private sub-tile barriers (<= 16) + one residual
+constexpr int kMaxStages = 16;          // NUM_STAGES_MAX of the reference (matmul_shmem_tc_async.cu:43)
+constexpr int kEpiBoxCols = 32;         // columns drained per tcgen05.ld / per TMA-store box
+constexpr int kMinSmemRequest = 120000; // more than half an SM's shared memory: one CTA per SM,
+                                        // so two CTAs never contend for the 512 TMEM columns
+
+struct Plan {
+    int status = B200_INVALID_CONFIG;
+    // tile
+    int tile_m = 0, tile_n = 0, cta_group = 1;
+    int cta_rows_a = 0;   // rows of A each CTA stages (tile_m / cta_group)
+    int cta_rows_b = 0;   // rows of B^T each CTA stages (tile_n / cta_group)
+    int mma_m = 0;        // M of one tcgen05.mma as seen by one CTA's tensor memory (64 or 128)
+    int seg_k = 0, kblocks = 0, stages = 0;
+    // sub-tile ("shift synchronisation") split of a stage
+    int a_box_rows = 0, a_boxes = 0;      // A rows per TMA box, boxes per k-block per CTA
+    int a_priv = 0, a_bars = 0;           // leading A boxes with private barriers; total A barriers
+    int chunk_n = 0;                      // tile columns per B^T sub-tile
+    int b_priv = 0, b_res_chunks = 0;     // private sub-tiles; sub-tiles on the residual barrier
+    int b_bars = 0;
+    // roles
+    int producer_warps = 0, epi_warps = 0, threads = 0;
+    // resources
+    int tmem_cols = 0, acc_cols = 0;      // allocation; columns per accumulator slot (2 slots)
+    int stage_bytes = 0, a_stage_bytes = 0, b_stage_bytes = 0;
+    int epi_mode = 0, epi_bytes = 0;
+    int num_barriers = 0;
+    int off_epi = 0, off_bars = 0, off_tmem_ptr = 0;
+    int smem_bytes = 0;                   // dynamic shared memory requested (includes alignment slack)
+    int split_k = 1;
+    int tile_group_m = 1;
+    int grid = 0;
+};
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+inline int pow2_at_least(int x) {
+    int p = 32;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+// Validates tunables that do not depend on the problem shape and lays out shared memory.
+inline Plan make_plan(const b200_gemm_params &q, int num_sms_device) {
+    Plan p;
+    p.status = B200_INVALID_CONFIG;
+    const int cg = q.cta_group == 0 ? 1 : q.cta_group;
+    if (cg != 1 && cg != 2) return p;
+    p.cta_group = cg;
+    // tile_m: 128 or 64 for one CTA; 256 for a pair (each CTA holds 128 rows).
+    if (cg == 1 && q.tile_m != 128 && q.tile_m != 64) return p;
+    if (cg == 2 && q.tile_m != 256) return p;
+    p.tile_m = q.tile_m;
+    p.cta_rows_a = q.tile_m / cg;
+    p.mma_m = p.cta_rows_a;
+    // tile_n: N of the MMA. M=128 per CTA needs N % 16 == 0, M=64 needs N % 8; a pair splits N.
+    const int n_gran = 16 * cg;
+    if (q.tile_n < n_gran || q.tile_n > 256 || q.tile_n % n_gran) return p;
+    p.tile_n = q.tile_n;
+    p.cta_rows_b = q.tile_n / cg;
+    if (q.segment_dim_k < kBoxK || q.segment_dim_k % kBoxK) return p;  // port_2.cu:1113
+    p.seg_k = q.segment_dim_k;
+    p.kblocks = q.segment_dim_k / kBoxK;
+    if (q.num_stages < 1 || q.num_stages > kMaxStages) return p;       // port_2.cu:1121
+    p.stages = q.num_stages;
+    if (q.tile_group_m < 1) return p;                                  // port_2.cu comment :631
+    p.tile_group_m = q.tile_group_m;
+    if (q.num_producer_warps != 1 && q.num_producer_warps != 2 && q.num_producer_warps != 4 &&
+        q.num_producer_warps != 8)
+        return p;                                                      // async.cu:516
+    p.producer_warps = q.num_producer_warps;
+    if (q.num_consumer_warps != 4 && q.num_consumer_warps != 8) return p;  // async.cu:517
+    p.epi_warps = q.num_consumer_warps;
+    p.threads = (p.producer_warps + 1 + p.epi_warps) * 32;
+    if (q.split_k < 0 || q.split_k > 64) return p;
+    p.split_k = q.split_k == 0 ? 1 : q.split_k;
+    if (q.epilogue != 0 && q.epilogue != 1) return p;
+    p.epi_mode = q.epilogue;
+
+    // Sub-tile split of the A stage buffer (rows per barrier step). 0 or the full extent = off.
+    int step_a = q.bar_step_rows_a;
+    if (step_a <= 0 || step_a >= p.tile_m) step_a = p.tile_m;
+    if (step_a == p.tile_m) {
+        p.a_box_rows = p.cta_rows_a;
+        p.a_boxes = 1;
+        p.a_priv = 0;
+        p.a_bars = 1;
+    } else {
+        if (step_a % 16 || p.cta_rows_a % step_a) return p;
+        p.a_box_rows = step_a;
+        p.a_boxes = p.cta_rows_a / step_a;
+        if (q.bar_steps_a < 0 || q.bar_steps_a > p.a_boxes) return p;  // port_2.cu:1116-1120
+        p.a_priv = q.bar_steps_a;
+        p.a_bars = p.a_priv + (p.a_priv < p.a_boxes ? 1 : 0);
+    }
+    // Sub-tile split of the B^T stage buffer (tile columns per barrier step).
+    int step_b = q.bar_step_rows_b;
+    if (step_b <= 0 || step_b >= p.tile_n) step_b = p.tile_n;
+    if (step_b == p.tile_n) {
+        p.chunk_n = p.tile_n;
+        p.b_priv = 0;
+        p.b_res_chunks = 1;
+        p.b_bars = 1;
+    } else {
+        if (step_b % n_gran || p.tile_n % step_b) return p;
+        const int chunks = p.tile_n / step_b;
+        if (chunks > 16) return p;
+        p.chunk_n = step_b;
+        if (q.bar_steps_b < 0 || q.bar_steps_b > chunks) return p;
+        p.b_priv = q.bar_steps_b;
+        p.b_res_chunks = chunks - p.b_priv;
+        p.b_bars = p.b_priv + (p.b_res_chunks > 0 ? 1 : 0);
+    }
+    if (p.a_bars > kMaxSubBars || p.b_bars > kMaxSubBars) return p;
+
+    // Tensor memory: two accumulator slots so the drain of tile i overlaps the MMAs of tile i+1.
+    // M=64 per CTA keeps the 16-lanes-per-quarter layout of one 64-row atom.
+    p.acc_cols = p.tile_n;
+    p.tmem_cols = pow2_at_least(2 * p.acc_cols);
+    if (p.tmem_cols > kTmemColumns) return p;
+
+    // Shared memory map (offsets from a 1024-byte aligned base).
+    p.a_stage_bytes = p.cta_rows_a * p.seg_k * 2;
+    p.b_stage_bytes = p.cta_rows_b * p.seg_k * 2;
+    p.stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
+    if (p.a_stage_bytes % 1024 || p.b_stage_bytes % 1024) return p;
+    // every sub-tile base must stay 1024-byte aligned (8 rows of 128 bytes)
+    if ((p.a_box_rows % 8) || ((p.chunk_n / cg) % 8)) return p;
+    p.off_epi = p.stages * p.stage_bytes;
+    p.epi_bytes = p.epi_mode ? p.epi_warps * 2 * 32 * kEpiBoxCols * 4 : 0;  // two 32x32 fp32 boxes per warp
+    p.num_barriers = p.stages * 2 * (p.a_bars + p.b_bars) /* full + empty */ + 4 /* tmem full/empty x2 */;
+    p.off_bars = p.off_epi + p.epi_bytes;
+    p.off_tmem_ptr = p.off_bars + p.num_barriers * 8;
+    const int used = p.off_tmem_ptr + 16;
+    p.smem_bytes = used + 1024;  // slack to align the dynamic base to 1024 bytes
+    if (p.smem_bytes > kSmemLimit) return p;  // the harness's filter, port_2.cu:1229-1231
+    if (p.smem_bytes < kMinSmemRequest) p.smem_bytes = kMinSmemRequest;
+
+    int sms = q.num_sms > 0 ? q.num_sms : num_sms_device;
+    if (sms < cg) return p;
+    p.grid = sms - sms % cg;
+    p.status = B200_OK;
+    return p;
+}
+
+// Shape checks of the reference launcher (port_2.cu:1114-1115) plus what the new tiling adds.
+inline int check_shape(const Plan &p, int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return B200_INVALID_SHAPE;
+    // N must tile exactly; a ragged last tile row of M is handled by TMA zero fill on load and
+    // clipped stores (the reference requires both to be tile multiples, port_2.cu:1114).
+    if (N % p.tile_n) return B200_INVALID_SHAPE;
+    if (K % p.seg_k) return B200_INVALID_SHAPE;
+    if (M > (int64_t(1) << 30) || N > (int64_t(1) << 30) || K > (int64_t(1) << 30)) return B200_INVALID_SHAPE;
+    if (p.split_k > 1 && (K / p.seg_k) < p.split_k) return B200_INVALID_SHAPE;
+    return B200_OK;
+}
+
+}  // namespace b200

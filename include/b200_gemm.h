@@ -1,0 +1,151 @@
+/*
+ * b200_gemm.h - C ABI of the B200 (sm_100a) asynchronous tensor-core GEMM.
+ *
+ *     D = alpha * A * B^T + beta * C
+ *
+ * A is m x k row-major, Bt is B stored transposed as n x k row-major (both fp16 or both bf16),
+ * C and D are m x n row-major fp32, accumulation is fp32. Every pointer of the device entry
+ * points is a DEVICE pointer owned by the caller; the calls allocate nothing, enqueue on the
+ * given stream and return without synchronising.
+ *
+ * Each entry point names the interface of the reference (alfin3/cuda-kernel-opt) it stands in
+ * for, as file:line of that project.
+ */
+#ifndef B200_GEMM_H
+#define B200_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. The reference's launchers return void, assert on the parameter domain and check
+ * CUDA errors only under -DDEBUG (matmul_shmem_tc_async.cu:45-54, :511-517); here every failure
+ * is a return value and nothing asserts, aborts or traps. */
+enum {
+    B200_OK = 0,
+    B200_INVALID_CONFIG = 1,   /* tunables outside the supported domain, or over the smem/TMEM budget */
+    B200_INVALID_SHAPE = 2,    /* M, N, K not multiples of the tile / K segment, or not positive */
+    B200_INVALID_POINTER = 3,  /* null or misaligned operand (A, Bt, D need 16-byte alignment) */
+    B200_CUDA_ERROR = 4,       /* a CUDA runtime/driver call failed; see b200_last_cuda_error() */
+    B200_DEVICE_TIMEOUT = 5,   /* a bounded wait inside the kernel expired; see b200_device_status() */
+    B200_WORKSPACE_TOO_SMALL = 6,
+    B200_UNSUPPORTED_DEVICE = 7 /* not an sm_100 GPU */
+};
+
+enum { B200_F16 = 0, B200_BF16 = 1 };
+
+/* Tunables. The first twelve are the reference launcher's own (matmul_shmem_tc_async_opt_port_2.cu
+ * :1088-1109); tile_dim is split into tile_m/tile_n and cta_group/split_k are added for the B200.
+ *
+ * tile_m             output-tile rows: 128 (one CTA), 256 (two-CTA pair, cta_group = 2) or 64
+ * tile_n             output-tile columns: multiple of 16 in [16, 256]
+ * segment_dim_k      K extent staged per pipeline stage; multiple of 64
+ * bar_steps_a/b      number of leading sub-tiles of the A / B^T stage buffer with a private "full"
+ *                    barrier; the rest share one residual barrier (port_2.cu:627-630)
+ * bar_step_rows_a/b  rows of A / rows of B^T (= columns of the tile) per sub-tile; equal to the
+ *                    tile extent = no sub-tiles = shift synchronisation off (port_1.cu:508-509)
+ * tile_group_m       tile rows per L2 rasterisation group (port_0.cu:201-210)
+ * num_stages         depth of the shared-memory ring
+ * num_producer_warps 1 = one warp issues the A and the B^T copies; >= 2 = separate A and B^T
+ *                    issuing warps (the reference's split, port_1.cu:197); further warps idle
+ * num_consumer_warps 4 or 8 warps draining the accumulator (one or two per 32 TMEM lanes)
+ * num_sms            size of the persistent grid (CTAs); 0 = all SMs of the device
+ * cta_group          1, or 2 for the two-CTA tcgen05 pair (tile_m = 256)
+ * split_k            K slices computed by different CTAs into the workspace and summed; 1 = off
+ */
+typedef struct b200_gemm_params {
+    int tile_m;
+    int tile_n;
+    int segment_dim_k;
+    int bar_steps_a;
+    int bar_steps_b;
+    int bar_step_rows_a;
+    int bar_step_rows_b;
+    int tile_group_m;
+    int num_stages;
+    int num_producer_warps;
+    int num_consumer_warps;
+    int num_sms;
+    int cta_group;
+    int split_k;
+    int epilogue;  /* 0 = registers -> global 128-bit stores, 1 = registers -> smem -> TMA store */
+    int reserved[3];
+} b200_gemm_params;
+
+/* Fills *p with the tuned default for the shape (what the reference's harness hard-codes per
+ * sweep, port_2.cu:1518-1564). dtype is B200_F16 or B200_BF16. */
+int b200_gemm_default_params(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p);
+
+/* Host-only validation: the reference's asserts (port_2.cu:1112-1123) and its harness's
+ * shared-memory filter (port_2.cu:1229-1232) as a status. Touches no GPU. */
+int b200_gemm_validate(int64_t M, int64_t N, int64_t K, int dtype, const b200_gemm_params *p);
+
+/* Dynamic shared memory the configuration needs, in bytes; the counterpart of get_shmem_req
+ * (port_2.cu:1057-1086). Negative if the configuration is invalid. */
+int64_t b200_gemm_smem_bytes(int dtype, const b200_gemm_params *p);
+
+/* Bytes of caller-provided device workspace the configuration needs (0 unless split_k > 1). */
+int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p);
+
+/* The GEMM. Stands in for gemm_shmem_tc_async (matmul_shmem_tc_async.cu:494-557) and
+ * gemm_shmem_tc_async_opt_port (matmul_shmem_tc_async_opt_port_0.cu:515-579, _1.cu:889-965,
+ * _2.cu:1088-1168) with DT = half (b200_gemm_f16) or bf16 (b200_gemm_bf16) and DT_ACC = float.
+ * C may be null when beta == 0. workspace may be null when none is needed. stream is a
+ * cudaStream_t (null = the legacy default stream, which is what the reference launches on). */
+int b200_gemm_f16(const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M,
+                  int64_t N, int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes,
+                  void *stream);
+int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M,
+                   int64_t N, int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes,
+                   void *stream);
+
+/* Host-buffer call: what the reference's harness does around one launch - cudaMemcpy of A, B^T
+ * (and C when beta != 0) to the device, the launch, cudaMemcpy of D back, which is also the
+ * synchronisation (port_2.cu:1210-1212, :1238-1242). Device buffers come from a session created
+ * once at the maximal dimensions, as the harness cudaMallocs once (port_2.cu:1200-1203). Host
+ * pointers may be pageable or pinned. Returns after D is in host memory. */
+typedef struct b200_session b200_session;
+int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_session **out);
+void b200_session_destroy(b200_session *s);
+int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const void *hBt, const float *hC, float *hD,
+                           float alpha, float beta, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p);
+
+/* Synchronises the stream and reports whether any kernel of this library hit a bounded-wait
+ * timeout on the current device since the last call. info (may be null) receives
+ * {code, block, barrier id, phase}. Clears the record. */
+int b200_device_status(void *stream, int info[4]);
+/* Test hook: the budget of every in-kernel wait, in nanoseconds (default 2e9). */
+void b200_set_wait_budget_ns(uint64_t ns);
+
+/* Tracing hook: when device_ptr is non-null, the first `blocks` CTAs of every later GEMM launch
+ * write 16 int64 cycle counters each (clock64) into it: [0..2] A-producer {cycles waiting for free
+ * stages, cycles in loop, stages filled}, [3..5] the same for a separate B^T producer, [6..9] MMA
+ * thread {cycles waiting for data, cycles waiting for a free accumulator, cycles in loop, stages},
+ * [10..12] first epilogue warp {cycles waiting for a finished tile, cycles in loop, tiles}. The
+ * reference only times whole launches with CUDA events (matmul_shmem_tc_async.cu:787-795). */
+void b200_set_profile_buffer(void *device_ptr, int blocks);
+
+const char *b200_status_string(int status);
+int b200_last_cuda_error(void); /* cudaError_t of the last failed CUDA call on this thread */
+int b200_num_sms(void);         /* multiprocessor count of the current device, <= 0 on error */
+
+/* Seeded synthetic inputs: element `index` of tensor `tensor_id` under `seed` from a counter
+ * hash, identical on host and device. dist 0 = uniform [-1, 1), 1 = normal(0, sigma) (sum of
+ * twelve uniforms). The reference fills with rand() seeded from the clock (matmul_test.h:239,
+ * :328-339), which cannot be reproduced; these replace it. */
+int b200_fill_u16_device(void *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                         float sigma, int dtype, void *stream);
+int b200_fill_f32_device(float *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                         float sigma, void *stream);
+void b200_fill_u16_host(uint16_t *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                        float sigma, int dtype);
+void b200_fill_f32_host(float *dst, int64_t begin, int64_t count, uint64_t seed, uint64_t tensor_id, int dist,
+                        float sigma);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_GEMM_H */
