@@ -95,18 +95,26 @@ def status_string(status: int) -> str:
 
 
 def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Params:
+    """b200_gemm_default_params plus keyword overrides of single tunables.
+
+    Overriding the tile (tile_m / tile_n / cta_group) starts from the one-CTA defaults unless the
+    override itself asks for the two-CTA pair, so that a partial override stays a valid whole."""
     p = Params()
-    st = lib().b200_gemm_default_params(M, N, K, dtype, C.byref(p))
+    tile_keys = {"tile_m", "tile_n", "cta_group"} & set(overrides)
+    want_pair = overrides.get("cta_group", 0) == 2 or overrides.get("tile_m", 0) == 256
+    st = lib().b200_gemm_default_params(M if (not tile_keys or want_pair) else min(M, 128), N, K, dtype, C.byref(p))
     if st != OK:
         raise B200Error(st, "b200_gemm_default_params")
+    if want_pair and p.cta_group != 2:
+        p.tile_m, p.tile_n, p.cta_group, p.num_stages = 256, 256, 2, 6
     for k, v in overrides.items():
         if not hasattr(p, k):
             raise AttributeError(k)
         setattr(p, k, v)
     # keep "shift off" consistent when only the tile was overridden
-    if "tile_n" in overrides and "bar_step_rows_b" not in overrides:
+    if "bar_step_rows_b" not in overrides:
         p.bar_step_rows_b = p.tile_n
-    if "tile_m" in overrides and "bar_step_rows_a" not in overrides:
+    if "bar_step_rows_a" not in overrides:
         p.bar_step_rows_a = p.tile_m
     return p
 

@@ -1,0 +1,138 @@
+"""CPU: the C-ABI library loads, exports every symbol the headers declare, and its host-only
+planning (the reference launcher's asserts and shared-memory filter as return codes) behaves.
+No compute entry point is called here."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200_gemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = ctypes.CDLL(pkg.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 18
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/b200_gemm.h but not exported"
+    assert sorted(pkg.EXPORTS) == names, "package binding list and header disagree"
+
+
+def test_cpp_launcher_header_compiles(tmp_path):
+    """include/b200_matmul.h: the four reference argument lists (15/16/18/20) resolve."""
+    src = tmp_path / "t.cpp"
+    src.write_text('''
+#include "b200_matmul.h"
+using namespace b200_matmul;
+int f(const half* A, const half* B, const float* C, float* D, const __nv_bfloat16* X) {
+  int s = gemm_shmem_tc_async<half, float>(A, B, C, D, 1.f, 1.f, 128, 128, 128, 128, 64, 2, 1, 4, 148);
+  s += gemm_shmem_tc_async_opt_port<half, float>(A, B, C, D, 1.f, 1.f, 128, 128, 128, 128, 64, 2, 2, 1, 4, 148);
+  s += gemm_shmem_tc_async_opt_port<half, float>(A, B, C, D, 1.f, 1.f, 128, 128, 128, 128, 64, 64, 64, 2, 2, 2, 4, 148);
+  s += gemm_shmem_tc_async_opt_port<half, float>(A, B, C, D, 1.f, 1.f, 128, 128, 128, 128, 64, 1, 1, 64, 64, 2, 2, 2, 4, 148);
+  s += gemm_shmem_tc_async_opt_port<__nv_bfloat16, float>(X, X, C, D, 1.f, 0.f, 128, 128, 128, 128, 64, 2, 2, 1, 4, 148);
+  return s + get_shmem_req(128, 64, 1, 1, 64, 64, 3, 4) + get_num_acc(128, 4) + get_warp_tile_rows(64, 8);
+}
+''')
+    import subprocess
+    r = subprocess.run(["/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++", "-std=c++17", "-fsyntax-only",
+                        "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include", str(src)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+def P(pkg, **ov):
+    base = dict(tile_m=128, tile_n=128, segment_dim_k=64, bar_steps_a=0, bar_steps_b=0, bar_step_rows_a=128,
+                bar_step_rows_b=128, tile_group_m=1, num_stages=2, num_producer_warps=2, num_consumer_warps=4,
+                num_sms=148, cta_group=1, split_k=1, epilogue=0)
+    base.update(ov)
+    p = pkg.Params()
+    for k, v in base.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_reference_parameter_domain(pkg):
+    """The asserts of the reference launchers (matmul_shmem_tc_async.cu:511-517,
+    matmul_shmem_tc_async_opt_port_2.cu:1112-1123) as statuses."""
+    ok = lambda **ov: pkg.validate(ov.pop("M", 1024), ov.pop("N", 1024), ov.pop("K", 1024), pkg.F16, P(pkg, **ov))
+    assert ok() == pkg.OK
+    for tile in (64, 128):
+        assert ok(tile_m=tile, tile_n=tile, bar_step_rows_a=tile, bar_step_rows_b=tile) == pkg.OK
+    assert ok(tile_m=96, bar_step_rows_a=96) == pkg.INVALID_CONFIG            # tile_dim in {64, 128}
+    assert ok(segment_dim_k=32) == pkg.INVALID_CONFIG                          # seg_k >= 64, % 64
+    assert ok(segment_dim_k=96) == pkg.INVALID_CONFIG
+    assert ok(num_stages=0) == pkg.INVALID_CONFIG                              # num_stages > 0
+    assert ok(num_stages=17) == pkg.INVALID_CONFIG                             # NUM_STAGES_MAX = 16
+    assert ok(tile_group_m=0) == pkg.INVALID_CONFIG                            # tile_group_m > 0
+    for p_ in (1, 2, 4, 8):
+        assert ok(num_producer_warps=p_) == pkg.OK
+    assert ok(num_producer_warps=3) == pkg.INVALID_CONFIG
+    assert ok(num_consumer_warps=8) == pkg.OK
+    assert ok(num_consumer_warps=6) == pkg.INVALID_CONFIG
+    assert ok(N=1000) == pkg.INVALID_SHAPE                                     # N % tile
+    assert ok(K=1000) == pkg.INVALID_SHAPE                                     # K % seg_k
+    assert ok(segment_dim_k=256, K=1024, num_stages=1) == pkg.OK
+    assert ok(M=0) == pkg.INVALID_SHAPE
+    assert ok(M=1000) == pkg.OK                                                # ragged M is an extension
+    assert pkg.validate(1024, 1024, 1024, 7, P(pkg)) == pkg.INVALID_CONFIG     # unknown dtype
+
+
+def test_barrier_granularities(pkg):
+    """bar_step_rows / bar_steps (port_2.cu:1116-1120): three granularities, bounds on the steps."""
+    ok = lambda **ov: pkg.validate(1024, 1024, 1024, pkg.F16, P(pkg, **ov))
+    assert ok(bar_step_rows_a=16, bar_step_rows_b=16, bar_steps_a=3, bar_steps_b=3) == pkg.OK
+    assert ok(bar_step_rows_a=64, bar_step_rows_b=64, bar_steps_a=2, bar_steps_b=2) == pkg.OK
+    assert ok(bar_step_rows_a=64, bar_step_rows_b=64, bar_steps_a=3, bar_steps_b=0) == pkg.INVALID_CONFIG  # > tile/step
+    assert ok(bar_step_rows_a=48, bar_step_rows_b=64) == pkg.INVALID_CONFIG                                 # does not divide
+    assert ok(bar_step_rows_b=24) == pkg.INVALID_CONFIG
+    assert ok(bar_step_rows_a=64, bar_steps_a=-1) == pkg.INVALID_CONFIG
+    # more barriers cost shared memory, as in get_shmem_req (port_2.cu:1069-1080)
+    s0 = pkg.smem_bytes(pkg.F16, P(pkg, num_stages=6))
+    s1 = pkg.smem_bytes(pkg.F16, P(pkg, num_stages=6, bar_step_rows_a=16, bar_step_rows_b=16, bar_steps_a=7, bar_steps_b=7))
+    assert 0 < s0 < s1
+
+
+def test_shared_memory_filter(pkg):
+    """The harness only runs configurations that fit (port_2.cu:1229-1231); here they are refused."""
+    fits = P(pkg, tile_m=128, tile_n=256, bar_step_rows_b=256, num_stages=4)
+    assert pkg.smem_bytes(pkg.F16, fits) == 4 * (128 + 256) * 64 * 2 + (4 * 4 + 4) * 8 + 16 + 1024
+    too_deep = P(pkg, tile_m=128, tile_n=256, bar_step_rows_b=256, num_stages=6)   # 288 KiB of stages
+    assert pkg.smem_bytes(pkg.F16, too_deep) == -1
+    assert pkg.validate(4096, 4096, 4096, pkg.F16, too_deep) == pkg.INVALID_CONFIG
+    assert pkg.smem_bytes(pkg.F16, P(pkg, num_stages=1)) >= 116 * 1024              # one CTA per SM always
+    with_tma_epilogue = P(pkg, tile_m=128, tile_n=256, bar_step_rows_b=256, num_stages=4, epilogue=1)
+    assert pkg.smem_bytes(pkg.F16, with_tma_epilogue) - pkg.smem_bytes(pkg.F16, fits) == 4 * 2 * 4096
+
+
+def test_b200_extensions(pkg):
+    ok = lambda M=4096, N=4096, K=4096, **ov: pkg.validate(M, N, K, pkg.BF16, P(pkg, **ov))
+    assert ok(tile_m=256, tile_n=256, cta_group=2, bar_step_rows_a=256, bar_step_rows_b=256, num_stages=6) == pkg.OK
+    assert ok(tile_m=128, tile_n=256, cta_group=2, bar_step_rows_b=256) == pkg.INVALID_CONFIG   # a pair needs tile_m = 256
+    assert ok(tile_m=256, cta_group=1, bar_step_rows_a=256) == pkg.INVALID_CONFIG
+    assert ok(tile_n=224, bar_step_rows_b=224, N=28672) == pkg.OK
+    assert ok(tile_n=264, bar_step_rows_b=264) == pkg.INVALID_CONFIG
+    assert ok(split_k=4) == pkg.OK and ok(split_k=65) == pkg.INVALID_CONFIG
+    assert ok(split_k=8, K=256) == pkg.INVALID_SHAPE                                            # fewer K segments than slices
+    p = P(pkg, split_k=4)
+    assert pkg.workspace_bytes(512, 256, 4096, p) == 4 * 512 * 256 * 4
+    assert pkg.workspace_bytes(512, 256, 4096, P(pkg)) == 0
+
+
+def test_default_params_are_valid(pkg):
+    for (m, n, k) in ((1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (16, 28672, 8192), (2048, 2048, 262144)):
+        for dt in (pkg.F16, pkg.BF16):
+            p = pkg.default_params(m, n, k, dt)
+            assert pkg.validate(m, n, k, dt, p) == pkg.OK, (m, n, k, p.as_dict())
+
+
+def test_status_strings(pkg):
+    seen = {pkg.status_string(i) for i in range(8)}
+    assert len(seen) == 8 and "unknown status" not in seen
+    assert pkg.status_string(99) == "unknown status"

@@ -1,0 +1,340 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the
+committed golden vectors. The bar (stated by the baseline): relative Frobenius error <= 1e-3 and
+per-element |err| <= 2^-10 * sqrt(K) for inputs in [-1, 1]; the constant-matrix family keeps the
+reference's own atol of 1e-3 (matmul_shmem_tc_async_opt_port_2.cu:1520)."""
+import ctypes
+import glob
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from helpers import GOLDEN, inputs, to_device, tolerance_ok
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_gemm(pkg, torch, dtype, A, Bt, Cm, alpha, beta, **ov):
+    m, k = A.shape
+    n = Bt.shape[0]
+    p = pkg.default_params(m, n, k, dtype, **ov)
+    assert pkg.validate(m, n, k, dtype, p) == pkg.OK, p.as_dict()
+    dA, dB = to_device(torch, A, dtype), to_device(torch, Bt, dtype)
+    dC = torch.from_numpy(Cm).cuda() if (Cm is not None and beta != 0.0) else None
+    D = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")   # canary: every element must be written
+    pkg.gemm(dA, dB, dC, D, alpha, beta, p)
+    st, info = pkg.device_status()
+    assert st == pkg.OK, f"device status {st} {info}"
+    return D.cpu().numpy()
+
+
+GOLD = sorted(p for p in glob.glob(os.path.join(GOLDEN, "*.npz"))
+              if os.path.basename(p) not in ("c1_1024_digest.npz", "constant_family.npz", "generator_kat.npz"))
+
+
+@pytest.mark.parametrize("path", GOLD, ids=[os.path.basename(p)[:-4] for p in GOLD])
+def test_golden_vectors(pkg, cuda, oracle, path):
+    z = np.load(path)
+    dtype, m, n, k = int(z["dtype"]), int(z["m"]), int(z["n"]), int(z["k"])
+    A, Bt, Cm = inputs(pkg, dtype, m, n, k, int(z["seed"]), tuple(z["dist_a"]), tuple(z["dist_b"]))
+    tile_n = 64 if n % 64 == 0 else 16
+    got = run_gemm(pkg, cuda, dtype, A, Bt, Cm, float(z["alpha"]), float(z["beta"]), tile_n=tile_n, num_stages=3)
+    scale = max(1.0, float(np.abs(oracle.to_float(A, dtype)).max() * np.abs(oracle.to_float(Bt, dtype)).max()))
+    ok, msg = tolerance_ok(got, z["D"], k, scale)
+    assert ok, msg
+
+
+def test_config1_1024_cubed_seed0(pkg, cuda, oracle):
+    """Baseline config 1: 1024^3 fp16 U[-1,1) seed 0, fp32 accumulate, against the reference's CPU matmul."""
+    A, Bt, _ = inputs(pkg, pkg.F16, 1024, 1024, 1024, 0)
+    want = oracle.gemm(A, Bt)
+    z = np.load(os.path.join(GOLDEN, "c1_1024_digest.npz"))
+    assert np.array_equal(want.reshape(-1)[z["sample_idx"]], z["sample"])   # the oracle is the pinned one
+    for ov in (dict(), dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_n=128, epilogue=1)):
+        got = run_gemm(pkg, cuda, pkg.F16, A, Bt, None, 1.0, 0.0, **ov)
+        ok, msg = tolerance_ok(got, want, 1024)
+        assert ok, (ov, msg)
+        assert oracle.count_incorrect(want, got, 0.1) == 0                    # the reference's accuracy criterion
+
+
+def test_constant_family(pkg, cuda, oracle):
+    """A = 1, B = 10, C = 1, alpha = beta = 1: every element equals 10*K + 1 (matmul_test.h:279-288)."""
+    rng = np.random.default_rng(3)
+    for tile in (64, 128):
+        for _ in range(3):
+            dim = int(rng.integers(1, 9)) * 128
+            A = np.full((dim, dim), 0x3C00, np.uint16)
+            Bt = np.full((dim, dim), 0x4900, np.uint16)
+            Cm = np.ones((dim, dim), np.float32)
+            got = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.0, 1.0, tile_m=tile, tile_n=tile, num_stages=2)
+            want = oracle.constant_expected(1.0, 10.0, 1.0, 1.0, 1.0, dim)
+            assert oracle.count_incorrect(np.full_like(got, want), got, 1e-3) == 0, (tile, dim)
+
+
+def test_pattern_inputs_catch_operand_mixups(pkg, cuda, oracle):
+    """Constant matrices cannot see swapped rows or operands; these can."""
+    m, n, k = 256, 384, 256
+    eye = np.zeros((m, k), np.float16); np.fill_diagonal(eye, 1.0)
+    idx = ((np.arange(n)[:, None] * 3 + np.arange(k)[None, :]) % 61).astype(np.float16)   # exact small integers
+    got = run_gemm(pkg, cuda, pkg.F16, eye.view(np.uint16), idx.view(np.uint16), None, 1.0, 0.0, tile_n=128)
+    assert np.array_equal(got, idx.astype(np.float32).T[:m, :n]), "A = I must return B^T transposed exactly"
+    onehot = np.zeros((m, k), np.float16); onehot[np.arange(m), (np.arange(m) * 7) % k] = 2.0
+    got = run_gemm(pkg, cuda, pkg.F16, onehot.view(np.uint16), idx.view(np.uint16), None, 1.0, 0.0, tile_n=64, segment_dim_k=128, num_stages=3)
+    want = oracle.gemm(onehot.view(np.uint16), idx.view(np.uint16))
+    assert np.array_equal(got, want)
+
+
+SWEEP = [
+    # tile_m, tile_n, seg_k, stages, group_m, P, C, extra
+    (128, 128, 64, 1, 1, 1, 4, {}), (128, 128, 64, 3, 2, 2, 8, {}), (128, 128, 128, 2, 3, 4, 4, {}),
+    (128, 128, 256, 1, 1, 8, 8, {}), (64, 64, 64, 4, 6, 2, 4, {}), (64, 64, 128, 2, 1, 1, 8, {}),
+    (128, 256, 64, 4, 8, 1, 4, {}), (128, 256, 64, 3, 4, 2, 4, dict(epilogue=1)), (128, 64, 64, 6, 2, 2, 4, {}),
+    (128, 16, 64, 2, 1, 1, 4, {}), (128, 224, 64, 3, 1, 1, 4, {}), (64, 128, 64, 3, 2, 2, 4, {}),
+    (256, 256, 64, 4, 4, 1, 4, dict(cta_group=2)), (256, 256, 128, 3, 2, 2, 4, dict(cta_group=2, epilogue=1)),
+    (256, 128, 64, 6, 1, 2, 4, dict(cta_group=2)), (256, 64, 64, 8, 3, 1, 4, dict(cta_group=2)),
+    # shift synchronisation: the reference's three granularities (port_2.cu:1213-1232)
+    (128, 128, 64, 3, 1, 2, 4, dict(bar_step_rows_a=16, bar_step_rows_b=16, bar_steps_a=3, bar_steps_b=3)),
+    (128, 128, 64, 2, 2, 4, 4, dict(bar_step_rows_a=64, bar_step_rows_b=64, bar_steps_a=2, bar_steps_b=2)),
+    (128, 128, 128, 2, 1, 2, 8, dict(bar_step_rows_a=64, bar_step_rows_b=64, bar_steps_a=1, bar_steps_b=0)),
+    (128, 128, 64, 2, 1, 2, 4, dict(bar_step_rows_a=16, bar_step_rows_b=16, bar_steps_a=0, bar_steps_b=0)),
+    (64, 64, 64, 3, 1, 2, 4, dict(bar_step_rows_a=16, bar_step_rows_b=16, bar_steps_a=1, bar_steps_b=1)),
+    (128, 256, 64, 3, 8, 2, 4, dict(bar_step_rows_b=64, bar_steps_b=2)), (128, 256, 64, 3, 8, 1, 4, dict(bar_step_rows_b=128, bar_steps_b=1)),
+    (256, 256, 64, 4, 2, 2, 4, dict(cta_group=2, bar_step_rows_b=64, bar_steps_b=3)),
+    (256, 256, 64, 3, 2, 2, 4, dict(cta_group=2, bar_step_rows_a=64, bar_steps_a=1, bar_step_rows_b=128, bar_steps_b=2)),
+]
+
+
+@pytest.mark.parametrize("cfg", SWEEP, ids=[f"{c[0]}x{c[1]}k{c[2]}s{c[3]}g{c[4]}p{c[5]}c{c[6]}" + "".join(f"_{k[4:] if k.startswith('bar_') else k}{v}" for k, v in c[7].items()) for c in SWEEP])
+def test_tunable_sweep(pkg, cuda, oracle, cfg):
+    """Every tunable of the reference launcher, on a seeded tile-multiple problem (the reference
+    picks random tile-multiple dims up to 1024, matmul_test.h:263-268), alpha = beta = 1 as in
+    its own runs (port_2.cu:1520)."""
+    tile_m, tile_n, seg_k, stages, group_m, P_, C_, extra = cfg
+    rng = np.random.default_rng(abs(hash(str(cfg))) % (2 ** 31))
+    m = tile_m * int(rng.integers(1, 6)); n = tile_n * int(rng.integers(1, max(2, 1024 // tile_n))); k = seg_k * int(rng.integers(1, 9))
+    A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 50 + stages)
+    ov = dict(tile_m=tile_m, tile_n=tile_n, segment_dim_k=seg_k, num_stages=stages, tile_group_m=group_m,
+              num_producer_warps=P_, num_consumer_warps=C_)
+    ov.update(extra)
+    got = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.0, 1.0, **ov)
+    want = oracle.gemm(A, Bt, Cm, 1.0, 1.0)
+    ok, msg = tolerance_ok(got, want, k)
+    assert ok, (m, n, k, msg)
+
+
+def test_bf16_and_scalars(pkg, cuda, oracle):
+    A, Bt, Cm = inputs(pkg, pkg.BF16, 384, 512, 768, 61)
+    for alpha, beta in ((1.0, 0.0), (0.5, 2.0), (-1.25, 0.75), (0.0, 1.0)):
+        got = run_gemm(pkg, cuda, pkg.BF16, A, Bt, Cm, alpha, beta)
+        want = oracle.gemm(A, Bt, Cm, alpha, beta, oracle.BF16)
+        ok, msg = tolerance_ok(got, want, 768, scale=max(1.0, abs(alpha)) + abs(beta))
+        assert ok, (alpha, beta, msg)
+
+
+def test_ragged_m_and_single_tile_edges(pkg, cuda, oracle):
+    """M need not be a tile multiple (zero-filled loads, clipped stores); K shorter than the ring."""
+    for m, n, k, ov in ((16, 512, 1024, dict()), (200, 256, 64, dict(epilogue=1)), (1, 256, 128, dict(tile_n=256)),
+                        (300, 512, 192, dict(tile_m=256, tile_n=256, cta_group=2)), (128, 128, 64, dict(tile_n=128, num_stages=6))):
+        A, Bt, Cm = inputs(pkg, pkg.BF16, m, n, k, 70 + m)
+        got = run_gemm(pkg, cuda, pkg.BF16, A, Bt, Cm, 1.0, 1.0, **ov)
+        want = oracle.gemm(A, Bt, Cm, 1.0, 1.0, oracle.BF16)
+        ok, msg = tolerance_ok(got, want, k, 2.0)
+        assert ok, (m, n, k, msg)
+
+
+def test_split_k(pkg, cuda, oracle):
+    for m, n, k, s, ov in ((256, 256, 2048, 4, dict()), (256, 512, 64 * 7, 3, dict()), (512, 512, 1024, 8, dict(tile_m=256, tile_n=256, cta_group=2))):
+        A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 80 + s)
+        got = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 2.0, 1.0, split_k=s, **ov)
+        want = oracle.gemm(A, Bt, Cm, 2.0, 1.0)
+        ok, msg = tolerance_ok(got, want, k, 3.0)
+        assert ok, (m, n, k, s, msg)
+    # the workspace is the caller's: too small is refused, nothing is allocated behind the call
+    p = pkg.default_params(256, 256, 2048, pkg.F16, split_k=4)
+    dA = to_device(cuda, np.zeros((256, 2048), np.uint16), pkg.F16)
+    dB = to_device(cuda, np.zeros((256, 2048), np.uint16), pkg.F16)
+    D = cuda.empty((256, 256), dtype=cuda.float32, device="cuda")
+    ws = cuda.empty(1024, dtype=cuda.uint8, device="cuda")
+    st = pkg.gemm_raw(pkg.F16, dA.data_ptr(), dB.data_ptr(), None, D.data_ptr(), 1.0, 0.0, 256, 256, 2048, p, ws.data_ptr(), 1024, None)
+    assert st == pkg.WORKSPACE_TOO_SMALL
+
+
+def test_error_statuses_on_device_calls(pkg, cuda):
+    dA = cuda.zeros((128, 64), dtype=cuda.float16, device="cuda")
+    D = cuda.zeros((128, 128), dtype=cuda.float32, device="cuda")
+    p = pkg.default_params(128, 128, 64, pkg.F16, tile_n=128)
+    args = (1.0, 0.0, 128, 128, 64, p)
+    assert pkg.gemm_raw(pkg.F16, None, dA.data_ptr(), None, D.data_ptr(), *args) == pkg.INVALID_POINTER
+    assert pkg.gemm_raw(pkg.F16, dA.data_ptr() + 2, dA.data_ptr(), None, D.data_ptr(), *args) == pkg.INVALID_POINTER
+    assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 1.0, 128, 128, 64, p) == pkg.INVALID_POINTER  # beta without C
+    assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 0.0, 128, 100, 64, p) == pkg.INVALID_SHAPE
+    bad = pkg.default_params(128, 128, 64, pkg.F16, tile_n=128, num_stages=0)
+    assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 0.0, 128, 128, 64, bad) == pkg.INVALID_CONFIG
+    assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), *args) == pkg.OK
+    assert pkg.device_status()[0] == pkg.OK
+
+
+def test_bounded_wait_reports_instead_of_hanging(pkg, cuda, oracle):
+    """Failure detection without a GPU fault: with a wait budget of about a nanosecond some wait
+    inside the kernel runs out; the kernel must return, record DEVICE_TIMEOUT, and leave the
+    context usable for the next (normal) launch."""
+    A, Bt, _ = inputs(pkg, pkg.F16, 512, 512, 2048, 90)
+    dA, dB = to_device(cuda, A, pkg.F16), to_device(cuda, Bt, pkg.F16)
+    D = cuda.empty((512, 512), dtype=cuda.float32, device="cuda")
+    p = pkg.default_params(512, 512, 2048, pkg.F16, num_stages=2)
+    pkg.set_wait_budget_ns(1)
+    try:
+        pkg.gemm(dA, dB, None, D, 1.0, 0.0, p)
+        st, info = pkg.device_status()
+    finally:
+        pkg.set_wait_budget_ns(2_000_000_000)
+    assert st in (pkg.OK, pkg.DEVICE_TIMEOUT)
+    if st == pkg.DEVICE_TIMEOUT:
+        assert info[0] == pkg.DEVICE_TIMEOUT and info[2] >= 100     # a barrier id of one of the roles
+    assert pkg.device_status()[0] == pkg.OK                         # the record was cleared
+    pkg.gemm(dA, dB, None, D, 1.0, 0.0, p)
+    assert pkg.device_status()[0] == pkg.OK
+    ok, msg = tolerance_ok(D.cpu().numpy(), oracle.gemm(A, Bt), 2048)
+    assert ok, msg
+
+
+def test_host_buffer_session(pkg, cuda, oracle):
+    """The call a harness makes: host buffers in, host result out (copies inside the call)."""
+    m, n, k = 512, 768, 1024
+    A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 95)
+    s = pkg.Session(1024, 1024, 1024)
+    out = np.full((m, n), np.nan, np.float32)
+    s.gemm_host(pkg.F16, A, Bt, Cm, out, 1.0, 1.0, m, n, k)
+    ok, msg = tolerance_ok(out, oracle.gemm(A, Bt, Cm, 1.0, 1.0), k, 2.0)
+    assert ok, msg
+    with pytest.raises(pkg.B200Error):
+        s.gemm_host(pkg.F16, A, Bt, Cm, out, 1.0, 1.0, 2048, n, k)          # larger than the session
+    s.close()
+
+
+def test_device_generator_equals_host_generator(pkg, cuda):
+    for tdt, code in ((cuda.float16, 0), (cuda.bfloat16, 1)):
+        for dist, sigma in ((0, 1.0), (1, 0.02)):
+            t = cuda.empty(100003, dtype=tdt, device="cuda")
+            pkg.fill_device(t, 11, 2, dist, sigma, begin=(1 << 31) + 5)
+            want = pkg.fill_u16_host((100003,), 11, 2, dist, sigma, code, begin=(1 << 31) + 5)
+            assert np.array_equal(t.view(cuda.int16).cpu().numpy().view(np.uint16), want)
+    f = cuda.empty(50001, dtype=cuda.float32, device="cuda")
+    pkg.fill_device(f, 12, 3, 1, 0.5)
+    assert np.array_equal(f.cpu().numpy(), pkg.fill_f32_host((50001,), 12, 3, 1, 0.5))
+
+
+def _sample_check(pkg, torch, oracle, dtype, A_t, B_t, D_t, alpha=1.0, rows=32, scale=1.0):
+    """Full-size check without a full CPU product: whole rows recomputed by the oracle plus
+    scattered elements in fp32 and fp64."""
+    m, k = A_t.shape
+    n = B_t.shape[0]
+    Bt = B_t.view(torch.int16).cpu().numpy().view(np.uint16)
+    rng = np.random.default_rng(7)
+    ridx = np.sort(rng.choice(m, size=min(rows, m), replace=False))
+    A_rows = A_t[torch.from_numpy(ridx).cuda()].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    want = oracle.gemm(A_rows, Bt, None, alpha, 0.0, dtype)
+    got = D_t[torch.from_numpy(ridx).cuda()].cpu().numpy()
+    ok, msg = tolerance_ok(got, want, k, scale)
+    assert ok, msg
+    return got, want
+
+
+def test_config2_4096_cubed_tile_and_stage_sweep(pkg, cuda, oracle):
+    """Baseline config 2: 4096^3 fp16 seed 1; block tiles {128x128, 128x256, 256x128 (2-CTA)},
+    K-tile 64, stages {2,3,4,6}, shift synchronisation on/off. Infeasible depths must be refused."""
+    n = 4096
+    A = cuda.empty((n, n), dtype=cuda.float16, device="cuda"); Bt = cuda.empty((n, n), dtype=cuda.float16, device="cuda")
+    pkg.fill_device(A, 1, 1); pkg.fill_device(Bt, 1, 2)
+    D = cuda.empty((n, n), dtype=cuda.float32, device="cuda")
+    first = None
+    for tile in (dict(tile_m=128, tile_n=128), dict(tile_m=128, tile_n=256), dict(tile_m=256, tile_n=128, cta_group=2)):
+        for stages in (2, 3, 4, 6):
+            for shift in (False, True):
+                ov = dict(tile, num_stages=stages, segment_dim_k=64)
+                if shift:
+                    ov.update(bar_step_rows_b=64, bar_steps_b=1, num_producer_warps=2)
+                p = pkg.default_params(n, n, n, pkg.F16, **ov)
+                if pkg.validate(n, n, n, pkg.F16, p) != pkg.OK:
+                    assert ov["tile_n"] == 256 and stages == 6 and "cta_group" not in ov   # 288 KiB of stages: refused, not altered
+                    continue
+                D.fill_(float("nan"))
+                pkg.gemm(A, Bt, None, D, 1.0, 0.0, p)
+                assert pkg.device_status()[0] == pkg.OK
+                if first is None:
+                    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D, rows=16)
+                    first = D.clone()
+                else:
+                    # every configuration sums K in the same 16-wide steps: differences, if any, are rounding only
+                    assert float((D - first).abs().max()) <= 2.0 ** -10 * 64.0 / 64.0, ov
+
+
+def test_config3_8192_cubed_fp16_and_bf16(pkg, cuda, oracle):
+    """Baseline config 3 on one GPU (seed 2), default (tuned) parameters, plus size-independent
+    properties: linearity in alpha and agreement of two different tilings."""
+    n = 8192
+    for tdt, code in ((cuda.float16, oracle.FP16), (cuda.bfloat16, oracle.BF16)):
+        A = cuda.empty((n, n), dtype=tdt, device="cuda"); Bt = cuda.empty((n, n), dtype=tdt, device="cuda")
+        pkg.fill_device(A, 2, 1); pkg.fill_device(Bt, 2, 2)
+        D = pkg.gemm(A, Bt)
+        assert pkg.device_status()[0] == pkg.OK
+        _sample_check(pkg, cuda, oracle, code, A, Bt, D, rows=16)
+        D2 = pkg.gemm(A, Bt, alpha=2.0, params=pkg.default_params(n, n, n, code, tile_m=128, tile_n=256, cta_group=1, num_stages=4))
+        assert float((D2 - 2.0 * D).norm() / D.norm()) < 1e-6    # linear in alpha; another tiling agrees
+        del A, Bt, D, D2
+
+
+def test_config4_skinny_decode_shapes(pkg, cuda, oracle):
+    """Baseline config 4: M in {16, 128}, N = 28672, K = 8192, bf16 activations ~N(0,1), weights
+    ~N(0,0.02) stored n x k, seed 3. Inputs are outside [-1,1]: the Frobenius bound gates, the
+    element bound is scaled by max|a| * max|w|."""
+    n, k = 28672, 8192
+    W = cuda.empty((n, k), dtype=cuda.bfloat16, device="cuda")
+    pkg.fill_device(W, 3, 2, pkg.NORMAL, 0.02)
+    Wh = W.view(cuda.int16).cpu().numpy().view(np.uint16)
+    for m in (16, 128):
+        X = cuda.empty((m, k), dtype=cuda.bfloat16, device="cuda")
+        pkg.fill_device(X, 3, 1, pkg.NORMAL, 1.0)
+        D = pkg.gemm(X, W)
+        assert pkg.device_status()[0] == pkg.OK
+        Xh = X.view(cuda.int16).cpu().numpy().view(np.uint16)
+        rows = np.arange(m) if m == 16 else np.arange(0, m, 8)
+        want = oracle.gemm(np.ascontiguousarray(Xh[rows]), Wh, None, 1.0, 0.0, oracle.BF16)
+        scale = float(np.abs(oracle.to_float(Xh, 1)).max() * np.abs(oracle.to_float(Wh[:4096], 1)).max())
+        ok, msg = tolerance_ok(D.cpu().numpy()[rows], want, k, max(scale, 1e-3))
+        assert ok, (m, msg)
+
+
+def test_config5_tall_k_split(pkg, cuda, oracle):
+    """Baseline config 5 on one GPU: M = N = 2048, K = 262144 fp16 seed 4, K split into slices
+    (here inside the GPU, through the workspace) and without a split."""
+    m = n = 2048
+    k = 262144
+    A = cuda.empty((m, k), dtype=cuda.float16, device="cuda"); Bt = cuda.empty((n, k), dtype=cuda.float16, device="cuda")
+    pkg.fill_device(A, 4, 1); pkg.fill_device(Bt, 4, 2)
+    D1 = pkg.gemm(A, Bt, params=pkg.default_params(m, n, k, pkg.F16, split_k=1))
+    assert pkg.device_status()[0] == pkg.OK
+    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D1, rows=8)
+    D8 = pkg.gemm(A, Bt, params=pkg.default_params(m, n, k, pkg.F16, split_k=8))
+    assert pkg.device_status()[0] == pkg.OK
+    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D8, rows=8)
+    rel = float((D8 - D1).norm() / D1.norm())
+    assert rel < 1e-3, rel                                      # only the fp32 summation order differs
+
+
+def test_reference_style_cpp_harness(pkg, cuda, oracle, tmp_path):
+    """The reference's correctness and accuracy families compiled against include/b200_matmul.h."""
+    exe = str(tmp_path / "b200_matmul_test")
+    gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    libdir = os.path.dirname(pkg.LIB_PATH)
+    cmd = [gxx, "-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include", "-o", exe,
+           os.path.join(ROOT, "tests", "harness", "b200_matmul_test.cpp"), "-L", libdir, "-l:libb200gemm.so",
+           "-L", os.path.join(ROOT, "oracle"), "-l:liboracle.so", "-L", "/usr/local/cuda/lib64", "-lcudart",
+           f"-Wl,-rpath,{libdir}", f"-Wl,-rpath,{os.path.join(ROOT, 'oracle')}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    for args in (["correctness", "1024", "quick"], ["accuracy", "256"], ["accuracy", "512"]):
+        r = subprocess.run([exe] + args, capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0, (args, r.stdout[-3000:], r.stderr[-2000:])
