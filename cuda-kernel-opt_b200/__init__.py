@@ -25,7 +25,7 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 # every symbol include/b200_gemm.h declares
 EXPORTS = [
     "b200_gemm_default_params", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
-    "b200_gemm_f16", "b200_gemm_bf16", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
+    "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_splitk_noalloc", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
     "b200_fill_u16_device", "b200_fill_f32_device", "b200_fill_u16_host", "b200_fill_f32_host",
 ]
@@ -69,6 +69,8 @@ def lib():
         for fn in (L.b200_gemm_f16, L.b200_gemm_bf16):
             fn.argtypes = [vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp, sz, vp]
             fn.restype = C.c_int
+        L.b200_gemm_splitk_noalloc.argtypes = [C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp]
+        L.b200_gemm_splitk_noalloc.restype = C.c_int
         L.b200_session_create.argtypes = [i64, i64, i64, C.POINTER(vp)]
         L.b200_session_destroy.argtypes = [vp]
         L.b200_session_destroy.restype = None
@@ -135,6 +137,12 @@ def gemm_raw(dtype, A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, p, ws_ptr
     """Direct call of b200_gemm_f16 / b200_gemm_bf16 with raw device addresses. Returns the status."""
     fn = lib().b200_gemm_bf16 if dtype == BF16 else lib().b200_gemm_f16
     return fn(A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, C.byref(p) if p is not None else None, ws_ptr, ws_bytes, stream)
+
+
+def gemm_splitk_noalloc_raw(dtype, A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, p, stream=None) -> int:
+    """Direct call of b200_gemm_splitk_noalloc (split-K with the library's built-in scratch:
+    no allocation, no caller workspace; split_k * M * N <= 8 Mi). Returns the status."""
+    return lib().b200_gemm_splitk_noalloc(dtype, A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, C.byref(p), stream)
 
 
 def gemm(A, Bt, Cm=None, D=None, alpha=1.0, beta=0.0, params: Params | None = None, workspace=None, stream=None):

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200gemm.so")
-SOURCES = ["gemm_sm100.cu", "api.cu"]
+SOURCES = ["gemm_sm100.cu", "api.cu", "gemm_noalloc.cu"]
 HEADERS = ["gemm_sm100.cuh", "ptx_sm100.cuh", "plan.h", "synth.h", os.path.join("..", "..", "include", "b200_gemm.h")]
 
 NVCC_FLAGS = [

@@ -102,6 +102,26 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
                    int64_t N, int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes,
                    void *stream);
 
+/* Split-K GEMM that allocates nothing and needs no workspace from the caller. It has no
+ * counterpart in the reference (whose launchers never split K and never need scratch memory).
+ *
+ * For callers that cannot allocate device memory or be handed any: a step of a serving loop
+ * that must not hit cudaMalloc's device synchronisation, a callback that runs while another
+ * library holds its allocator lock, a plugin host that passes fixed input and output buffers only.
+ * The per-slice fp32 partial products go to a 32 MiB device array built into the library (every
+ * GPU that loads the library holds it until the process exits), so split_k * M * N must not
+ * exceed 8 Mi values; larger problems return B200_WORKSPACE_TOO_SMALL and belong to
+ * b200_gemm_f16 / b200_gemm_bf16 with a caller workspace. p->split_k must be >= 2.
+ *
+ * The first call on a device looks up the array's device address (once per device); make that
+ * first call outside any stream capture. No cudaMalloc, cudaFree or allocating library routine is
+ * called, on the first call or later. All calls on a device share the one array: it keeps the
+ * previous call's partials, every element a call reads it has written first (nothing needs
+ * clearing), and two calls whose kernels overlap on the GPU (different streams, no ordering)
+ * race on it - order them. dtype is B200_F16 or B200_BF16; other arguments as b200_gemm_f16. */
+int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt, const float *C, float *D, float alpha, float beta,
+                             int64_t M, int64_t N, int64_t K, const b200_gemm_params *p, void *stream);
+
 /* Host-buffer call: what the reference's harness does around one launch - cudaMemcpy of A, B^T
  * (and C when beta != 0) to the device, the launch, cudaMemcpy of D back, which is also the
  * synchronisation (port_2.cu:1210-1212, :1238-1242). Device buffers come from a session created
