@@ -29,6 +29,10 @@ import sys
 import threading
 import time
 
+# rank 0 prints exactly one line on stdout: keep NCCL's version banner off it
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -39,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM traffic of one launch of the dominant kernel from an ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum); see profiles/. None where no capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"c3_8192_f16": None}
+NCU_TRAFFIC_BYTES = {"c3_8192_f16": 1347851400}
 
 WORKLOADS = {
     # name: (M, N, K, dtype, seed, dist_a, dist_b, bound)
@@ -99,7 +103,7 @@ class ClockSampler(threading.Thread):
     def run(self):
         while not self.stop_flag:
             self.sample()
-            time.sleep(0.005)
+            time.sleep(0.001)
 
     def summary(self):
         sm = sorted(self.sm)
@@ -373,6 +377,21 @@ def run_ours(args):
         sess.close()
         del hA, hB, hD
 
+    # ---- optional: per-role cycle counters of CTA 0 from one extra launch (tracing hook of the library)
+    roles = None
+    if args.role_counters and rank == 0:
+        prof = torch.zeros((2, 16), dtype=torch.int64, device=dev)
+        pkg.lib().b200_set_profile_buffer(prof.data_ptr(), 2)
+        pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
+        torch.cuda.synchronize()
+        pkg.lib().b200_set_profile_buffer(None, 0)
+        r = prof.cpu().tolist()[0]
+        it, tiles = max(r[9], 1), max(r[12], 1)
+        roles = {"stages": r[9], "tiles": r[12], "producer_cycles_per_stage": r[1] / max(r[2], 1),
+                 "producer_wait_per_stage": r[0] / max(r[2], 1), "mma_cycles_per_stage": r[8] / it,
+                 "mma_wait_data_per_stage": r[6] / it, "mma_wait_accumulator_per_tile": r[7] / tiles,
+                 "epilogue_cycles_per_tile": r[11] / tiles, "epilogue_wait_per_tile": r[10] / tiles}
+
     # ---- CPU baseline beside it (rank 0, N = 1 only, bounded sample)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -392,6 +411,8 @@ def run_ours(args):
             "gpu_launches": args.steps * launches_per_step,
             "per_gpu_tflops": (value / world) if unit == "TFLOPS" else None,
         }
+        if roles:
+            line["role_counters"] = roles
         if splitk_ranks:
             line["exposed_reduce_ms"] = exposed_ms
         print(json.dumps(line), flush=True)
@@ -413,6 +434,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--role-counters", action="store_true", help="add in-kernel per-role cycle counters of CTA 0")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
