@@ -36,7 +36,7 @@ class Params(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "tile_m", "tile_n", "segment_dim_k", "bar_steps_a", "bar_steps_b", "bar_step_rows_a", "bar_step_rows_b",
         "tile_group_m", "num_stages", "num_producer_warps", "num_consumer_warps", "num_sms", "cta_group", "split_k",
-        "epilogue")] + [("reserved", C.c_int * 3)]
+        "epilogue", "l2_hint", "diagnostic", "reserved")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
@@ -107,8 +107,10 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
     st = lib().b200_gemm_default_params(M if (not tile_keys or want_pair) else min(M, 128), N, K, dtype, C.byref(p))
     if st != OK:
         raise B200Error(st, "b200_gemm_default_params")
+    if tile_keys and not want_pair and M > 128:
+        p.l2_hint = 0          # the skinny-shape hint of the reduced-M base does not apply
     if want_pair and p.cta_group != 2:
-        p.tile_m, p.tile_n, p.cta_group, p.num_stages = 256, 256, 2, 6
+        p.tile_m, p.tile_n, p.cta_group, p.num_stages, p.l2_hint = 256, 256, 2, 6, 3
     for k, v in overrides.items():
         if not hasattr(p, k):
             raise AttributeError(k)
@@ -118,6 +120,9 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
         p.bar_step_rows_b = p.tile_n
     if "bar_step_rows_a" not in overrides:
         p.bar_step_rows_a = p.tile_m
+    if "num_stages" not in overrides:   # a default depth chosen for another tile may not fit this one
+        while p.num_stages > 1 and lib().b200_gemm_smem_bytes(dtype, C.byref(p)) < 0:
+            p.num_stages -= 1
     return p
 
 

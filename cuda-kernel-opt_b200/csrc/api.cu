@@ -116,13 +116,31 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
         p->cta_group = 2;
         p->num_stages = 6;
         p->num_producer_warps = 2;
+        p->l2_hint = 3;  // keep operand panels in L2: fewer DRAM re-reads, measured +2.5 % under the power limit
     } else {
+        // One row of tiles (skinny, HBM-bound: decode shapes) or N not a multiple of 256: a one-CTA
+        // tile whose width divides N and fills the last wave of the persistent grid best.
         p->tile_m = 128;
-        p->tile_n = 256;
-        while (p->tile_n > 16 && (N % p->tile_n)) p->tile_n /= 2;
         p->cta_group = 1;
-        p->num_stages = p->tile_n > 128 ? 4 : 6;
+        int best_n = 16;
+        double best_eff = -1.0;
+        const int64_t rows = (M + 127) / 128;
+        for (int tn = 256; tn >= 16; tn -= 16) {
+            if (N % tn) continue;
+            const int64_t tiles = rows * (N / tn);
+            const int64_t waves = (tiles + 147) / 148;
+            const double eff = double(tiles) / double(waves * 148) * (tn >= 128 ? 1.0 : tn / 128.0);
+            if (eff > best_eff + 1e-9) {
+                best_eff = eff;
+                best_n = tn;
+            }
+        }
+        p->tile_n = best_n;
+        const int stage_bytes = (128 + best_n) * 128;
+        p->num_stages = 200000 / stage_bytes > 8 ? 8 : 200000 / stage_bytes;
         p->num_producer_warps = 1;
+        // weights stream through once (evict_first), the few activation rows are re-read by every CTA
+        p->l2_hint = (M <= 128) ? 1 : 0;
     }
     p->segment_dim_k = 64;
     p->bar_steps_a = 0;
@@ -224,7 +242,8 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
 
     a.prof = g_prof_ptr.load();
     a.prof_blocks = g_prof_blocks.load();
-    a.debug_flags = user->reserved[0];
+    a.debug_flags = user->diagnostic;
+    a.l2_hint = user->l2_hint;
 
     const int le = launch_gemm(p, a, stream);
     if (le != 0) return fail_cuda(static_cast<cudaError_t>(le));

@@ -234,6 +234,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint32_t my_bytes = static_cast<uint32_t>(c.kblocks * CG) * ((do_a ? a_kb_bytes : 0u) + (do_b ? b_kb_bytes : 0u));
             const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
             const bool arm = issuer && rank == 0;
+            const int hint = g.l2_hint;
+            const uint64_t pol_a = l2_policy(hint >= 1 ? 2 : 0);
+            const uint64_t pol_b = l2_policy(hint == 1 ? 1 : (hint == 3 ? 2 : 0));
             const bool issue_a = issuer && do_a && !(dbg & 2);
             const bool issue_b = issuer && do_b && !(dbg & 2);
             int s = 0;
@@ -256,11 +259,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     uint32_t da = stage, db = stage + static_cast<uint32_t>(c.a_stage_bytes);
                     for (int kb = 0; kb < c.kblocks; ++kb) {
                         if constexpr (CG == 2) {
-                            if (issue_a) tma_load_2d_pair(da, &g.map_a, sbl, k, a_row);
-                            if (issue_b) tma_load_2d_pair(db, &g.map_b, sbl, k, b_row);
+                            if (issue_a) tma_load_2d_pair_hint(da, &g.map_a, sbl, k, a_row, pol_a);
+                            if (issue_b) tma_load_2d_pair_hint(db, &g.map_b, sbl, k, b_row, pol_b);
                         } else {
-                            if (issue_a) tma_load_2d(da, &g.map_a, sb, k, a_row);
-                            if (issue_b) tma_load_2d(db, &g.map_b, sb, k, b_row);
+                            if (issue_a) tma_load_2d_hint(da, &g.map_a, sb, k, a_row, pol_a);
+                            if (issue_b) tma_load_2d_hint(db, &g.map_b, sb, k, b_row, pol_b);
                         }
                         da += a_kb_bytes;
                         db += b_kb_bytes;

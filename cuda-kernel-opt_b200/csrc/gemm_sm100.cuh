@@ -36,6 +36,7 @@ struct alignas(64) GemmArgs {
     long long *prof;    // optional cycle counters, 16 per CTA for the first prof_blocks CTAs
     int prof_blocks;
     int debug_flags;
+    int l2_hint;
 };
 
 // Launches the kernel for plan p on `stream`. Returns a cudaError_t as int.

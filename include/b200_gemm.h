@@ -55,6 +55,7 @@ enum { B200_F16 = 0, B200_BF16 = 1 };
  * num_sms            size of the persistent grid (CTAs); 0 = all SMs of the device
  * cta_group          1, or 2 for the two-CTA tcgen05 pair (tile_m = 256)
  * split_k            K slices computed by different CTAs into the workspace and summed; 1 = off
+ * epilogue, l2_hint  see the fields
  */
 typedef struct b200_gemm_params {
     int tile_m;
@@ -72,7 +73,12 @@ typedef struct b200_gemm_params {
     int cta_group;
     int split_k;
     int epilogue;  /* 0 = registers -> global 128-bit stores, 1 = registers -> smem -> TMA store */
-    int reserved[3];
+    int l2_hint;   /* L2 eviction priority of the operand loads: 0 = normal for both, 1 = A evict_last and
+                      B^T evict_first (A row panels are the reused operand of the grouped tile order),
+                      2 = A evict_last, 3 = both evict_last */
+    int diagnostic; /* must be 0. Bit 0 issues no MMA, bit 1 no operand load: pipeline ceilings for
+                       profiling; the output is garbage */
+    int reserved;
 } b200_gemm_params;
 
 /* Fills *p with the tuned default for the shape (what the reference's harness hard-codes per
