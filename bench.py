@@ -400,6 +400,23 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         _, cpu, _ = cpu_reference_rate(args.workload, seconds_budget=args.cpu_seconds)
 
+    # ---- optional reported baseline: the reference's own WMMA kernel recompiled for sm_100a
+    wmma = None
+    if args.wmma_baseline and rank == 0 and world == 1 and M == N == K:
+        exe = os.path.join(ROOT, "oracle", "_ref", "ref_wmma_async")
+        if os.path.exists(exe):
+            import subprocess
+            del A, Bt, D
+            torch.cuda.empty_cache()
+            r = subprocess.run([exe, str(M), "128", "64", "1", "3", "4", "8", "2"], capture_output=True, text=True, timeout=600)
+            try:
+                wmma = json.loads(r.stdout.strip().splitlines()[-1])
+                wmma["what"] = "gemm_shmem_tc_async<half,float> of the reference (matmul_shmem_tc_async.cu), nvcc -arch=sm_100a, tile 128, seg_k 64, 3 stages, 4+8 warps"
+            except Exception:
+                wmma = {"error": (r.stdout + r.stderr)[-300:]}
+        else:
+            wmma = {"unavailable": "oracle/_ref/ref_wmma_async not built (make -C oracle wmma, needs the reference tree)"}
+
     if rank == 0:
         line = {
             "metric": METRIC if args.workload == "c3_8192_f16" else f"{unit} on {args.workload}",
@@ -416,6 +433,8 @@ def run_ours(args):
         }
         if roles:
             line["role_counters"] = roles
+        if wmma:
+            line["reference_wmma_kernel"] = wmma
         if splitk_ranks:
             line["exposed_reduce_ms"] = exposed_ms
         print(json.dumps(line), flush=True)
@@ -437,6 +456,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--wmma-baseline", action="store_true",
+                    help="also time the reference's WMMA kernel recompiled for sm_100a (oracle/_ref, if built)")
     ap.add_argument("--role-counters", action="store_true", help="add in-kernel per-role cycle counters of CTA 0")
     args = ap.parse_args()
     if args.impl == "reference":
