@@ -274,17 +274,25 @@ def run_ours(args):
     D = torch.empty((m_loc, n_loc), dtype=torch.float32, device=dev)
 
     overrides = json.loads(args.params) if args.params else {}
+    fused = splitk_ranks and args.exchange == "fused"
     if args.workload.startswith("c5") and not overrides:
         # 64 tiles of 256 x 256 on 74 CTA pairs: split K inside the GPU so every pair has equal work
-        overrides = {"cta_group": 2, "split_k": 8}
+        # (the fused exchange pushes finished tiles to their owners and takes no in-GPU split)
+        overrides = {"cta_group": 2} if fused else {"cta_group": 2, "split_k": 8}
     p = pkg.default_params(m_loc, n_loc, k_loc, dtype, **overrides)
     st = pkg.validate(m_loc, n_loc, k_loc, dtype, p)
     assert st == pkg.OK, f"invalid configuration {p.as_dict()}: {pkg.status_string(st)}"
     ws_bytes = pkg.workspace_bytes(m_loc, n_loc, k_loc, p)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-    launches_per_step = 1 + (1 if p.split_k > 1 else 0)
+    launches_per_step = 1 + (1 if (p.split_k > 1 or fused) else 0)
+    push = shard.PushExchange(pkg, M, N) if fused else None
+    D_rows = torch.empty((M // world, N), dtype=torch.float32, device=dev) if fused else None
+    if fused:
+        parallelism = f"split-K x{world}, reduce-scatter fused into the epilogue (NVLink peer stores)"
 
     def step():
+        if fused:
+            return push.gemm_reduce_scatter(A, Bt, D_rows, p)
         pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
         if splitk_ranks:
             return shard.reduce_scatter_rows(D)
@@ -308,10 +316,14 @@ def run_ours(args):
     sampler.start()
     for e0, e1, e2 in ev:
         e0.record()
-        pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
-        e1.record()                                    # end of the GEMM kernel(s) of this step
-        if splitk_ranks:
-            shard.reduce_scatter_rows(D)
+        if fused:
+            push.gemm_reduce_scatter(A, Bt, D_rows, p)
+            e1.record()
+        else:
+            pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
+            e1.record()                                # end of the GEMM kernel(s) of this step
+            if splitk_ranks:
+                shard.reduce_scatter_rows(D)
         e2.record()
     barrier()
     sampler.stop_flag = True
@@ -438,6 +450,16 @@ def run_ours(args):
         if splitk_ranks:
             line["exposed_reduce_ms"] = exposed_ms
         print(json.dumps(line), flush=True)
+    if fused and args.check:
+        pkg.gemm(A, Bt, None, D, 1.0, 0.0, p)
+        want = shard.reduce_scatter_rows(D)
+        got = push.gemm_reduce_scatter(A, Bt, D_rows, p)
+        torch.cuda.synchronize()
+        rel = float((got - want).norm() / want.norm())
+        st, info = pkg.device_status()
+        print(f"[rank {rank}] fused vs NCCL reduce-scatter: rel diff {rel:.3e}, device status {st}", file=sys.stderr, flush=True)
+    if push is not None:
+        push.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -452,6 +474,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c3_8192_f16")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--exchange", choices=["nccl", "fused"], default="fused",
+                    help="split-K workloads on N > 1: NCCL reduce-scatter after the GEMM, or fused into its epilogue")
+    ap.add_argument("--check", action="store_true", help="split-K workloads: compare fused and NCCL results")
     ap.add_argument("--params", default="", help="JSON overrides of the launch tunables")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", action="store_true")

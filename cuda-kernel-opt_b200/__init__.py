@@ -25,7 +25,8 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 # every symbol include/b200_gemm.h declares
 EXPORTS = [
     "b200_gemm_default_params", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
-    "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_splitk_noalloc", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
+    "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
+    "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
     "b200_fill_u16_device", "b200_fill_f32_device", "b200_fill_u16_host", "b200_fill_f32_host",
 ]
@@ -71,6 +72,13 @@ def lib():
             fn.restype = C.c_int
         L.b200_gemm_splitk_noalloc.argtypes = [C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp]
         L.b200_gemm_splitk_noalloc.restype = C.c_int
+        L.b200_gemm_push.argtypes = [C.c_int, vp, vp, i64, i64, i64, PP, C.c_int, C.c_int, C.POINTER(vp), C.POINTER(vp), vp, C.c_int, vp]
+        L.b200_push_reduce.argtypes = [vp, vp, C.c_int, C.c_int, vp, vp, f32, f32, i64, i64, vp]
+        L.b200_peer_alloc.argtypes = [sz, C.POINTER(vp)]
+        L.b200_peer_free.argtypes = [vp]
+        L.b200_peer_export.argtypes = [vp, C.c_char_p]
+        L.b200_peer_import.argtypes = [C.c_char_p, C.POINTER(vp)]
+        L.b200_peer_release.argtypes = [vp]
         L.b200_session_create.argtypes = [i64, i64, i64, C.POINTER(vp)]
         L.b200_session_destroy.argtypes = [vp]
         L.b200_session_destroy.restype = None

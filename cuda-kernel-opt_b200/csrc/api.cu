@@ -154,9 +154,16 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
     p->epilogue = 0;
 }
 
+struct PushTarget {  // split-K over GPUs with the exchange fused into the epilogue; world == 0: off
+    int world = 0, rank = 0, epoch = 0;
+    void *const *slots = nullptr;
+    void *const *flags = nullptr;
+    void *done = nullptr;
+};
+
 int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M,
               int64_t N, int64_t K, const b200_gemm_params *user, void *workspace, size_t workspace_bytes,
-              cudaStream_t stream) {
+              cudaStream_t stream, const PushTarget *push = nullptr) {
     if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
     b200_gemm_params local;
     if (!user) {
@@ -170,7 +177,16 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if (p.status != B200_OK) return p.status;
     st = check_shape(p, M, N, K);
     if (st != B200_OK) return st;
-    if (!A || !Bt || !D) return B200_INVALID_POINTER;
+    const bool pushing = push && push->world > 0;
+    if (pushing) {
+        if (push->world > 8 || push->rank < 0 || push->rank >= push->world || !push->slots || !push->flags || !push->done)
+            return B200_INVALID_CONFIG;
+        if (p.split_k != 1 || M % push->world || (M / push->world) % 128 || (M / push->world) % p.cta_rows_a)
+            return B200_INVALID_SHAPE;  // every CTA's rows must belong to one owner
+        for (int o = 0; o < push->world; ++o)
+            if (!push->slots[o] || !push->flags[o]) return B200_INVALID_POINTER;
+    }
+    if (!A || !Bt || (!D && !pushing)) return B200_INVALID_POINTER;
     if (beta != 0.0f && !C) return B200_INVALID_POINTER;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bt) | reinterpret_cast<uintptr_t>(D) |
          reinterpret_cast<uintptr_t>(C)) & 15u)
@@ -191,7 +207,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
                    static_cast<uint32_t>(p.chunk_n / p.cta_group));
     if (st != B200_OK) return st;
     int epi_mode = p.epi_mode;
-    if (p.mma_m != 128 || p.split_k > 1) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
+    if (p.mma_m != 128 || p.split_k > 1 || pushing) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
     if (epi_mode) {
         st = encode_2d(&a.map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
                        kEpiBoxCols, 32);
@@ -240,6 +256,17 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.idesc_res = umma_idesc(p.tile_m, p.b_res_chunks * p.chunk_n, dtype == B200_BF16);
     a.wait_budget_cycles = static_cast<long long>(g_wait_budget_ns.load() * 2ull);  // SM clock is below 2 GHz
 
+    if (pushing) {
+        for (int o = 0; o < push->world; ++o) {
+            a.push_slot[o] = static_cast<float *>(push->slots[o]);
+            a.push_flag[o] = static_cast<int *>(push->flags[o]);
+        }
+        a.push_done = static_cast<unsigned int *>(push->done);
+        a.push_world = push->world;
+        a.push_rank = push->rank;
+        a.push_rows = static_cast<int>(M / push->world);
+        a.push_epoch = push->epoch;
+    }
     a.prof = g_prof_ptr.load();
     a.prof_blocks = g_prof_blocks.load();
     a.debug_flags = user->diagnostic;
@@ -319,6 +346,70 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
                    int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes, void *stream) {
     return gemm_impl(B200_BF16, A, Bt, C, D, alpha, beta, M, N, K, p, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
+                   int world, int rank, void *const *slot_ptrs, void *const *flag_ptrs, void *done_counter, int epoch,
+                   void *stream) {
+    PushTarget t;
+    t.world = world;
+    t.rank = rank;
+    t.epoch = epoch;
+    t.slots = slot_ptrs;
+    t.flags = flag_ptrs;
+    t.done = done_counter;
+    if (world < 1) return B200_INVALID_CONFIG;
+    return gemm_impl(dtype, A, Bt, nullptr, nullptr, 1.0f, 0.0f, M, N, K, p, nullptr, 0, static_cast<cudaStream_t>(stream), &t);
+}
+
+int b200_push_reduce(const float *my_slots, const int *my_flags, int world, int epoch, const float *C, float *D, float alpha,
+                     float beta, int64_t rows, int64_t N, void *stream) {
+    if (!my_slots || !my_flags || !D || world < 1 || world > 8 || rows <= 0 || N <= 0 || (rows * N) % 4) return B200_INVALID_SHAPE;
+    if (beta != 0.0f && !C) return B200_INVALID_POINTER;
+    const int e = launch_push_reduce(my_slots, my_flags, world, epoch, C, D, alpha, beta, rows, N,
+                                     static_cast<long long>(g_wait_budget_ns.load() * 2ull), static_cast<cudaStream_t>(stream));
+    return e == 0 ? B200_OK : fail_cuda(static_cast<cudaError_t>(e));
+}
+
+int b200_peer_alloc(size_t bytes, void **out) {
+    if (!out || bytes == 0) return B200_INVALID_POINTER;
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    if (e != cudaSuccess) return fail_cuda(e);
+    *out = p;
+    return B200_OK;
+}
+
+int b200_peer_free(void *ptr) {
+    const cudaError_t e = cudaFree(ptr);
+    return e == cudaSuccess ? B200_OK : fail_cuda(e);
+}
+
+int b200_peer_export(void *ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!ptr || !handle) return B200_INVALID_POINTER;
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) return fail_cuda(e);
+    std::memcpy(handle, &h, 64);
+    return B200_OK;
+}
+
+int b200_peer_import(const unsigned char handle[64], void **out) {
+    if (!handle || !out) return B200_INVALID_POINTER;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    void *p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail_cuda(e);
+    *out = p;
+    return B200_OK;
+}
+
+int b200_peer_release(void *imported) {
+    const cudaError_t e = cudaIpcCloseMemHandle(imported);
+    return e == cudaSuccess ? B200_OK : fail_cuda(e);
 }
 
 int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_session **out) {

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int off_bars = g.off_bars, off_tmem_ptr = g.off_tmem_ptr, off_epi = g.off_epi;
     const int tmem_cols = g.tmem_cols;
     const int P = g.producer_warps;
+    const int push_world = g.push_world, push_rank = g.push_rank, push_rows = g.push_rows;
     const int dbg = g.debug_flags;  // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage)
     const float g_alpha = g.alpha, g_beta = g.beta;
     const float *const gC = g.C;
@@ -558,8 +559,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         const int row_in_cta = (c.mma_m == 128) ? (q * 32 + lane) : (q * 16 + (lane & 15));
         const bool lane_has_row = (c.mma_m == 128) || (lane < 16);
         const bool to_partial = c.split_k > 1;
-        const float alpha = to_partial ? 1.0f : g_alpha;
-        const float beta = to_partial ? 0.0f : g_beta;
+        const float alpha = (to_partial || push_world > 0) ? 1.0f : g_alpha;
+        const float beta = (to_partial || push_world > 0) ? 0.0f : g_beta;
         uint32_t tl = 0;
         uint32_t store_idx = 0;
         bool ok = true;
@@ -577,8 +578,15 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             tc_fence_after_sync();
             const int row = w.m0 + static_cast<int>(rank) * c.cta_rows_a + row_in_cta;
             const bool row_ok = lane_has_row && row < c.M;
-            float *const out = to_partial ? g_partial + static_cast<size_t>(w.slice) * c.M * c.N : gD;
-            const size_t row_off = static_cast<size_t>(row) * c.N + w.n0;
+            float *out = to_partial ? g_partial + static_cast<size_t>(w.slice) * c.M * c.N : gD;
+            size_t row_off = static_cast<size_t>(row) * c.N + w.n0;
+            if (push_world > 0) {
+                // the 128 rows this CTA drains belong to one owner (rows per owner is a multiple of 128)
+                const int cta_row0 = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
+                const int owner = cta_row0 / push_rows;
+                out = g.push_slot[owner];
+                row_off = (static_cast<size_t>(push_rank) * push_rows + static_cast<size_t>(row - owner * push_rows)) * c.N + w.n0;
+            }
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                 uint32_t r[32];
@@ -661,6 +669,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             }
         }
         if (c.epi_mode && lane == 0) tma_store_wait<0>();
+        if (push_world > 0) __threadfence_system();  // this thread's peer stores are ordered before the flag below
         __syncwarp();
         if (prof && e == 0 && lane == 0) {
             prof[10] = t_tfull;
@@ -675,6 +684,17 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     if constexpr (CG == 2) {
         cluster_arrive();
         cluster_wait();
+    }
+    if (push_world > 0 && tid == 0 && !*abort_flag) {
+        // Count finished CTAs; the last one tells every owner that this rank's slots are complete.
+        __threadfence();
+        const unsigned int done = atomicAdd(g.push_done, 1u);
+        if (done == gridDim.x - 1) {
+            __threadfence_system();
+            for (int o = 0; o < push_world; ++o) *reinterpret_cast<volatile int *>(g.push_flag[o] + push_rank) = g.push_epoch;
+            __threadfence_system();
+            *g.push_done = 0u;
+        }
     }
     if (warp == mma_warp) {
         if (*abort_flag) {
@@ -716,6 +736,72 @@ __global__ void splitk_reduce_kernel(const float4 *__restrict__ partial, const f
         }
         D[i] = o;
     }
+}
+
+// Owner side of the fused split-K exchange. Block-wide bounded wait on the source ranks' flags
+// (written by peers over NVLink), then an ordered sum of the slots. Slots are read with .cg loads:
+// they were written by other GPUs, L1 is not coherent with those writes.
+__global__ void push_reduce_kernel(const float4 *slots, const int *flags, int world, int epoch, const float4 *__restrict__ C,
+                                   float4 *__restrict__ D, float alpha, float beta, long long n4, long long budget) {
+    __shared__ int ok_flag;
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        int ok = 1;
+        for (int s = 0; s < world && ok; ++s) {
+            while (*reinterpret_cast<const volatile int *>(flags + s) != epoch) {
+                __nanosleep(200);
+                if (clock64() - t0 > budget) {
+                    ok = 0;
+                    if (atomicCAS(&g_device_status[0], 0, B200_DEVICE_TIMEOUT) == 0) {
+                        g_device_status[1] = static_cast<int>(blockIdx.x);
+                        g_device_status[2] = 700 + s;
+                        g_device_status[3] = epoch;
+                    }
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+        ok_flag = ok;
+    }
+    __syncthreads();
+    if (!ok_flag) return;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 s = __ldcg(slots + i);
+        for (int k = 1; k < world; ++k) {
+            const float4 v = __ldcg(slots + static_cast<long long>(k) * n4 + i);
+            s.x += v.x;
+            s.y += v.y;
+            s.z += v.z;
+            s.w += v.w;
+        }
+        float4 o;
+        o.x = alpha * s.x;
+        o.y = alpha * s.y;
+        o.z = alpha * s.z;
+        o.w = alpha * s.w;
+        if (beta != 0.0f) {
+            const float4 c = C[i];
+            o.x += beta * c.x;
+            o.y += beta * c.y;
+            o.z += beta * c.z;
+            o.w += beta * c.w;
+        }
+        D[i] = o;
+    }
+}
+
+int launch_push_reduce(const float *slots, const int *flags, int world, int epoch, const float *C, float *D, float alpha,
+                       float beta, int64_t rows, int64_t n, long long budget_cycles, cudaStream_t stream) {
+    const long long n4 = rows * n / 4;
+    int blocks = static_cast<int>((n4 + 255) / 256);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    push_reduce_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4 *>(slots), flags, world, epoch,
+                                                   reinterpret_cast<const float4 *>(C), reinterpret_cast<float4 *>(D), alpha,
+                                                   beta, n4, budget_cycles);
+    return static_cast<int>(cudaGetLastError());
 }
 
 namespace {

@@ -37,6 +37,14 @@ struct alignas(64) GemmArgs {
     int prof_blocks;
     int debug_flags;
     int l2_hint;
+    // split-K across GPUs with the reduce-scatter fused into the epilogue ("push" mode, world > 0):
+    // the fp32 tile rows owned by GPU o are stored straight into o's slot area over NVLink
+    // (plain peer stores), slot [source rank][rows per owner][N]; the last CTA to finish raises
+    // this rank's flag on every owner.
+    float *push_slot[8];
+    int *push_flag[8];
+    unsigned int *push_done;  // local counter of finished CTAs (zero between launches)
+    int push_world, push_rank, push_rows, push_epoch;
 };
 
 // Launches the kernel for plan p on `stream`. Returns a cudaError_t as int.
@@ -45,6 +53,10 @@ int launch_splitk_reduce(const float *partial, const float *C, float *D, float a
                          int split_k, cudaStream_t stream);
 // Reads and clears the device-side timeout record {code, block, barrier, phase}.
 int read_device_status(int out[4], cudaStream_t stream);
+// Owner side of push mode: waits (bounded) until every source rank's flag shows `epoch`, then
+// D = alpha * sum over sources of slot[src] + beta * C for this GPU's rows.
+int launch_push_reduce(const float *slots, const int *flags, int world, int epoch, const float *C, float *D, float alpha,
+                       float beta, int64_t rows, int64_t n, long long budget_cycles, cudaStream_t stream);
 int prepare_kernels();  // opt-in shared memory size; once per device
 
 }  // namespace b200

@@ -76,3 +76,100 @@ def reduce_scatter_rows(partial, group=None):
         r = dist.get_rank(group)
         out.copy_(full[r * (m // world):(r + 1) * (m // world)])
     return out
+
+
+class PushExchange:
+    """Split-K over the GPUs of a box with the reduce-scatter fused into the GEMM epilogue
+    (b200_gemm_push / b200_push_reduce): peers' fp32 tiles arrive in this GPU's slot area by plain
+    NVLink stores while the GEMM is still running; what is left after the GEMM is a flag wait
+    and one ordered sum of `world` local slabs. torch.distributed only carries the 64-byte IPC
+    handles at set-up and a barrier per step (slot reuse).
+
+    Two slot areas alternate by step. No per-step barrier is needed: a rank starts the push of step
+    e+2 (same area as step e) only after its own reduce of step e+1, which waited for every peer's
+    flag of step e+1, which each peer raised (in stream order) after its reduce of step e.
+    """
+
+    def __init__(self, pkg, M: int, N: int, group=None):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        self.pkg, self.C, self.dist, self.group = pkg, C, dist, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if M % self.world or (M // self.world) % 128:
+            raise ValueError("rows per GPU must be a multiple of 128")
+        self.M, self.N, self.rows = M, N, M // self.world
+        lib = pkg.lib()
+        self.slots = C.c_void_p()
+        self.flags = C.c_void_p()
+        self.done = C.c_void_p()
+        for ptr, nbytes in ((self.slots, 2 * self.world * self.rows * N * 4), (self.flags, 64 * 4), (self.done, 64)):
+            st = lib.b200_peer_alloc(nbytes, C.byref(ptr))
+            if st != pkg.OK:
+                raise pkg.B200Error(st, "b200_peer_alloc")
+        handles = []
+        for ptr in (self.slots, self.flags):
+            buf = C.create_string_buffer(64)
+            st = lib.b200_peer_export(ptr, buf)
+            if st != pkg.OK:
+                raise pkg.B200Error(st, "b200_peer_export")
+            handles.append(bytes(buf.raw))
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=group)
+        self.imported = []
+        self.area_bytes = self.world * self.rows * N * 4
+        self.slot_ptrs = (C.c_void_p * 8)()
+        self.flag_ptrs = (C.c_void_p * 8)()
+        for o in range(self.world):
+            if o == self.rank:
+                self.slot_ptrs[o], self.flag_ptrs[o] = self.slots.value, self.flags.value
+                continue
+            for which, arr in ((0, self.slot_ptrs), (1, self.flag_ptrs)):
+                out = C.c_void_p()
+                st = lib.b200_peer_import(gathered[o][which], C.byref(out))
+                if st != pkg.OK:
+                    raise pkg.B200Error(st, "b200_peer_import")
+                arr[o] = out.value
+                self.imported.append(out)
+        self.slot_ptrs_odd = (C.c_void_p * 8)()
+        for o in range(self.world):
+            self.slot_ptrs_odd[o] = self.slot_ptrs[o] + self.area_bytes
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def gemm_reduce_scatter(self, A, Bt, D_rows, params, Cm_rows=None, alpha=1.0, beta=0.0, stream=None):
+        """A: M x K_local, Bt: N x K_local (this rank's K slice); D_rows: (M/world) x N fp32, this
+        rank's rows of the full product. Asynchronous on the current stream."""
+        import torch
+        pkg, lib = self.pkg, self.pkg.lib()
+        dtype = pkg.BF16 if A.dtype == torch.bfloat16 else pkg.F16
+        self.epoch += 1
+        sptr = stream if stream is not None else torch.cuda.current_stream(A.device).cuda_stream
+        odd = self.epoch & 1
+        st = lib.b200_gemm_push(dtype, A.data_ptr(), Bt.data_ptr(), self.M, self.N, A.shape[1], self.C.byref(params),
+                                self.world, self.rank, self.slot_ptrs_odd if odd else self.slot_ptrs, self.flag_ptrs,
+                                self.done, self.epoch, sptr)
+        if st != pkg.OK:
+            raise pkg.B200Error(st, "b200_gemm_push")
+        st = lib.b200_push_reduce(self.slots.value + (self.area_bytes if odd else 0), self.flags, self.world, self.epoch,
+                                  Cm_rows.data_ptr() if Cm_rows is not None else None, D_rows.data_ptr(), alpha, beta,
+                                  self.rows, self.N, sptr)
+        if st != pkg.OK:
+            raise pkg.B200Error(st, "b200_push_reduce")
+        return D_rows
+
+    def close(self):
+        import torch
+        torch.cuda.synchronize()
+        self.dist.barrier(group=self.group)
+        lib = self.pkg.lib()
+        for p in self.imported:
+            lib.b200_peer_release(p)
+        self.imported = []
+        self.dist.barrier(group=self.group)
+        for p in (self.slots, self.flags, self.done):
+            if p:
+                lib.b200_peer_free(p)
+        self.slots = self.flags = self.done = None

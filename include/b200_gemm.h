@@ -128,6 +128,37 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
 int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt, const float *C, float *D, float alpha, float beta,
                              int64_t M, int64_t N, int64_t K, const b200_gemm_params *p, void *stream);
 
+/* Split-K across the GPUs of a box with the reduce-scatter fused into the GEMM epilogue. The
+ * reference is single-GPU (cudaSetDevice(0), matmul_shmem_tc_async_opt_port_2.cu:1503-1510) and
+ * never splits K; this is the multi-GPU form of the same launcher for tall-K problems.
+ *
+ * Rank r multiplies its K slice (A: M x K_local, Bt: N x K_local). GPU o owns rows
+ * [o*M/world, (o+1)*M/world) of D. b200_gemm_push stores every finished fp32 tile straight into
+ * the owner's slot area over NVLink (plain peer stores, no TMA on remote memory): slot_ptrs[o]
+ * is owner o's area of world x (M/world) x N floats, indexed [source rank][row][col], as mapped
+ * into this process (b200_peer_import); flag_ptrs[o] is owner o's array of `world` ints. The last
+ * CTA to finish writes `epoch` into flag[o][rank] on every owner. done_counter is a zeroed
+ * local unsigned int. M/world must be a multiple of 128 (256 for the two-CTA tile), split_k = 1.
+ *
+ * b200_push_reduce, enqueued on the owner after its own b200_gemm_push, waits (bounded; a
+ * DEVICE_TIMEOUT record if a peer never arrives) until all `world` flags show `epoch`, then
+ * writes D_rows = alpha * sum over sources of slot[src] + beta * C_rows, sources in ascending
+ * order. Use a new epoch (> 0, increasing) for every GEMM; slots of epoch e may be overwritten
+ * only after every rank has finished b200_push_reduce of epoch e (a barrier per step, or two
+ * alternating slot areas). */
+int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
+                   int world, int rank, void *const *slot_ptrs, void *const *flag_ptrs, void *done_counter, int epoch,
+                   void *stream);
+int b200_push_reduce(const float *my_slots, const int *my_flags, int world, int epoch, const float *C, float *D, float alpha,
+                     float beta, int64_t rows, int64_t N, void *stream);
+/* Device memory that other processes of the box can map (cudaMalloc + CUDA IPC), zero-filled; the
+ * 64-byte handle travels by any host channel (the bench uses torch.distributed). */
+int b200_peer_alloc(size_t bytes, void **out);
+int b200_peer_free(void *ptr);
+int b200_peer_export(void *ptr, unsigned char handle[64]);
+int b200_peer_import(const unsigned char handle[64], void **out);
+int b200_peer_release(void *imported);
+
 /* Host-buffer call: what the reference's harness does around one launch - cudaMemcpy of A, B^T
  * (and C when beta != 0) to the device, the launch, cudaMemcpy of D back, which is also the
  * synchronisation (port_2.cu:1210-1212, :1238-1242). Device buffers come from a session created
