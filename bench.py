@@ -277,14 +277,13 @@ def run_ours(args):
     fused = splitk_ranks and args.exchange == "fused"
     if args.workload.startswith("c5") and not overrides:
         # 64 tiles of 256 x 256 on 74 CTA pairs: split K inside the GPU so every pair has equal work
-        # (the fused exchange pushes finished tiles to their owners and takes no in-GPU split)
-        overrides = {"cta_group": 2} if fused else {"cta_group": 2, "split_k": 8}
+        overrides = {"cta_group": 2, "split_k": 8}
     p = pkg.default_params(m_loc, n_loc, k_loc, dtype, **overrides)
     st = pkg.validate(m_loc, n_loc, k_loc, dtype, p)
     assert st == pkg.OK, f"invalid configuration {p.as_dict()}: {pkg.status_string(st)}"
     ws_bytes = pkg.workspace_bytes(m_loc, n_loc, k_loc, p)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-    launches_per_step = 1 + (1 if (p.split_k > 1 or fused) else 0)
+    launches_per_step = 1 + (1 if p.split_k > 1 else 0) + (1 if fused else 0)
     push = shard.PushExchange(pkg, M, N) if fused else None
     D_rows = torch.empty((M // world, N), dtype=torch.float32, device=dev) if fused else None
     if fused:
@@ -292,7 +291,7 @@ def run_ours(args):
 
     def step():
         if fused:
-            return push.gemm_reduce_scatter(A, Bt, D_rows, p)
+            return push.gemm_reduce_scatter(A, Bt, D_rows, p, workspace=ws if ws_bytes else None)
         pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
         if splitk_ranks:
             return shard.reduce_scatter_rows(D)
@@ -317,7 +316,7 @@ def run_ours(args):
     for e0, e1, e2 in ev:
         e0.record()
         if fused:
-            push.gemm_reduce_scatter(A, Bt, D_rows, p)
+            push.gemm_reduce_scatter(A, Bt, D_rows, p, workspace=ws if ws_bytes else None)
             e1.record()
         else:
             pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)

@@ -72,7 +72,7 @@ def lib():
             fn.restype = C.c_int
         L.b200_gemm_splitk_noalloc.argtypes = [C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp]
         L.b200_gemm_splitk_noalloc.restype = C.c_int
-        L.b200_gemm_push.argtypes = [C.c_int, vp, vp, i64, i64, i64, PP, C.c_int, C.c_int, C.POINTER(vp), C.POINTER(vp), vp, C.c_int, vp]
+        L.b200_gemm_push.argtypes = [C.c_int, vp, vp, i64, i64, i64, PP, C.c_int, C.c_int, C.POINTER(vp), C.POINTER(vp), vp, C.c_int, vp, sz, vp]
         L.b200_push_reduce.argtypes = [vp, vp, C.c_int, C.c_int, vp, vp, f32, f32, i64, i64, vp]
         L.b200_peer_alloc.argtypes = [sz, C.POINTER(vp)]
         L.b200_peer_free.argtypes = [vp]

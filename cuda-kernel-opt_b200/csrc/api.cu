@@ -135,6 +135,7 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
                 best_n = tn;
             }
         }
+        if (best_eff < 0.0) best_n = 128;  // no width divides N: ragged last tile column
         p->tile_n = best_n;
         const int stage_bytes = (128 + best_n) * 128;
         p->num_stages = 200000 / stage_bytes > 8 ? 8 : 200000 / stage_bytes;
@@ -181,7 +182,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if (pushing) {
         if (push->world > 8 || push->rank < 0 || push->rank >= push->world || !push->slots || !push->flags || !push->done)
             return B200_INVALID_CONFIG;
-        if (p.split_k != 1 || M % push->world || (M / push->world) % 128 || (M / push->world) % p.cta_rows_a)
+        if (M % push->world || (M / push->world) % 128 || (M / push->world) % p.cta_rows_a || N % 4)
             return B200_INVALID_SHAPE;  // every CTA's rows must belong to one owner
         for (int o = 0; o < push->world; ++o)
             if (!push->slots[o] || !push->flags[o]) return B200_INVALID_POINTER;
@@ -222,11 +223,11 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.N = static_cast<int>(N);
     a.K = static_cast<int>(K);
     a.tiles_m = static_cast<int>((M + p.tile_m - 1) / p.tile_m);
-    a.tiles_n = static_cast<int>(N / p.tile_n);
+    a.tiles_n = static_cast<int>((N + p.tile_n - 1) / p.tile_n);
     a.num_tiles = a.tiles_m * a.tiles_n;
     a.split_k = p.split_k;
     a.num_units = a.num_tiles * p.split_k;
-    a.num_segs = static_cast<int>(K / p.seg_k);
+    a.num_segs = static_cast<int>((K + p.seg_k - 1) / p.seg_k);
     a.tile_m = p.tile_m;
     a.tile_n = p.tile_n;
     a.cta_rows_a = p.cta_rows_a;
@@ -256,7 +257,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.idesc_res = umma_idesc(p.tile_m, p.b_res_chunks * p.chunk_n, dtype == B200_BF16);
     a.wait_budget_cycles = static_cast<long long>(g_wait_budget_ns.load() * 2ull);  // SM clock is below 2 GHz
 
-    if (pushing) {
+    if (pushing && p.split_k == 1) {
         for (int o = 0; o < push->world; ++o) {
             a.push_slot[o] = static_cast<float *>(push->slots[o]);
             a.push_flag[o] = static_cast<int *>(push->flags[o]);
@@ -274,7 +275,17 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
 
     const int le = launch_gemm(p, a, stream);
     if (le != 0) return fail_cuda(static_cast<cudaError_t>(le));
-    if (p.split_k > 1) {
+    if (p.split_k > 1 && pushing) {
+        float *slots[8];
+        int *flags[8];
+        for (int o = 0; o < push->world; ++o) {
+            slots[o] = static_cast<float *>(push->slots[o]);
+            flags[o] = static_cast<int *>(push->flags[o]);
+        }
+        const int re = launch_splitk_reduce_push(a.partial, M, N, p.split_k, slots, flags, static_cast<unsigned int *>(push->done),
+                                                 push->world, push->rank, push->epoch, stream);
+        if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
+    } else if (p.split_k > 1) {
         const int re = launch_splitk_reduce(a.partial, C, D, alpha, beta, M * N, p.split_k, stream);
         if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
     }
@@ -350,7 +361,7 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
 
 int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
                    int world, int rank, void *const *slot_ptrs, void *const *flag_ptrs, void *done_counter, int epoch,
-                   void *stream) {
+                   void *workspace, size_t workspace_bytes, void *stream) {
     PushTarget t;
     t.world = world;
     t.rank = rank;
@@ -359,7 +370,8 @@ int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t 
     t.flags = flag_ptrs;
     t.done = done_counter;
     if (world < 1) return B200_INVALID_CONFIG;
-    return gemm_impl(dtype, A, Bt, nullptr, nullptr, 1.0f, 0.0f, M, N, K, p, nullptr, 0, static_cast<cudaStream_t>(stream), &t);
+    return gemm_impl(dtype, A, Bt, nullptr, nullptr, 1.0f, 0.0f, M, N, K, p, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), &t);
 }
 
 int b200_push_reduce(const float *my_slots, const int *my_flags, int world, int epoch, const float *C, float *D, float alpha,
@@ -485,7 +497,7 @@ const char *b200_status_string(int status) {
     switch (status) {
         case B200_OK: return "ok";
         case B200_INVALID_CONFIG: return "invalid configuration (tunables outside the domain or over the shared/tensor memory budget)";
-        case B200_INVALID_SHAPE: return "invalid shape (M, N, K must be positive; N a multiple of tile_n, K of segment_dim_k)";
+        case B200_INVALID_SHAPE: return "invalid shape (M, N, K must be positive, N a multiple of 4 and K of 8; split-K and multi-GPU forms add their own rules)";
         case B200_INVALID_POINTER: return "null or misaligned pointer";
         case B200_CUDA_ERROR: return "CUDA error";
         case B200_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired";

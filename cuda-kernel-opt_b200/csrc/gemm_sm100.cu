@@ -589,6 +589,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             }
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+                if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
                 uint32_t r[32];
                 const bool wide = (col_end - c0) >= 32;
                 if (wide) {
@@ -609,7 +610,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            if (j < nvec) {
+                            if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
                                 float4 v;
                                 v.x = alpha * __uint_as_float(r[4 * j + 0]);
                                 v.y = alpha * __uint_as_float(r[4 * j + 1]);
@@ -639,7 +640,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         v.y = alpha * __uint_as_float(r[4 * j + 1]);
                         v.z = alpha * __uint_as_float(r[4 * j + 2]);
                         v.w = alpha * __uint_as_float(r[4 * j + 3]);
-                        if (beta != 0.0f && row_ok) {
+                        if (beta != 0.0f && row_ok && w.n0 + c0 + 4 * j < c.N) {
                             const float4 cv = __ldg(csrc + j);
                             v.x += beta * cv.x;
                             v.y += beta * cv.y;
@@ -790,6 +791,68 @@ __global__ void push_reduce_kernel(const float4 *slots, const int *flags, int wo
         }
         D[i] = o;
     }
+}
+
+// Split-K inside the GPU combined with the exchange across GPUs: sums this rank's K slices
+// (ascending order) and stores each row of the sum into the slot area of the GPU that owns the
+// row (coalesced 128-bit peer stores over NVLink); the last block raises this rank's flags.
+struct PushDest {
+    float *slot[8];
+    int *flag[8];
+    unsigned int *done;
+    int world, rank, rows, epoch;
+};
+
+__global__ void splitk_reduce_push_kernel(const float4 *__restrict__ partial, long long n4, int split_k, int n_cols4,
+                                          const __grid_constant__ PushDest d) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 s = partial[i];
+        for (int k = 1; k < split_k; ++k) {
+            const float4 v = partial[static_cast<long long>(k) * n4 + i];
+            s.x += v.x;
+            s.y += v.y;
+            s.z += v.z;
+            s.w += v.w;
+        }
+        const long long row = i / n_cols4;
+        const int owner = static_cast<int>(row / d.rows);
+        const long long dst = (static_cast<long long>(d.rank) * d.rows + (row - static_cast<long long>(owner) * d.rows)) * n_cols4 + i % n_cols4;
+        reinterpret_cast<float4 *>(d.slot[owner])[dst] = s;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(d.done, 1u);
+        if (done == gridDim.x - 1) {
+            __threadfence_system();
+            for (int o = 0; o < d.world; ++o) *reinterpret_cast<volatile int *>(d.flag[o] + d.rank) = d.epoch;
+            __threadfence_system();
+            *d.done = 0u;
+        }
+    }
+}
+
+int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int split_k, float *const *slots, int *const *flags,
+                              unsigned int *done, int world, int rank, int epoch, cudaStream_t stream) {
+    PushDest d = {};
+    for (int o = 0; o < world; ++o) {
+        d.slot[o] = slots[o];
+        d.flag[o] = flags[o];
+    }
+    d.done = done;
+    d.world = world;
+    d.rank = rank;
+    d.rows = static_cast<int>(m / world);
+    d.epoch = epoch;
+    const long long n4 = m * n / 4;
+    int blocks = static_cast<int>((n4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    splitk_reduce_push_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4 *>(partial), n4, split_k,
+                                                          static_cast<int>(n / 4), d);
+    return static_cast<int>(cudaGetLastError());
 }
 
 int launch_push_reduce(const float *slots, const int *flags, int world, int epoch, const float *C, float *D, float alpha,

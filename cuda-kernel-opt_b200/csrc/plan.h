@@ -167,10 +167,13 @@ inline int check_shape(const Plan &p, int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0) return B200_INVALID_SHAPE;
     // N must tile exactly; a ragged last tile row of M is handled by TMA zero fill on load and
     // clipped stores (the reference requires both to be tile multiples, port_2.cu:1114).
-    if (N % p.tile_n) return B200_INVALID_SHAPE;
-    if (K % p.seg_k) return B200_INVALID_SHAPE;
+    // Ragged N and K are handled the same way (the reference also requires N % tile and
+    // K % segment_dim_k == 0, port_2.cu:1114-1115; its launcher-shaped wrappers keep that rule).
+    // What remains: 16-byte aligned rows, i.e. N % 4 == 0 for fp32 D and K % 8 == 0 for the
+    // two-byte operands (TMA global strides are multiples of 16 bytes).
+    if (N % 4 || K % 8) return B200_INVALID_SHAPE;
     if (M > (int64_t(1) << 30) || N > (int64_t(1) << 30) || K > (int64_t(1) << 30)) return B200_INVALID_SHAPE;
-    if (p.split_k > 1 && (K / p.seg_k) < p.split_k) return B200_INVALID_SHAPE;
+    if (p.split_k > 1 && ((K + p.seg_k - 1) / p.seg_k) < p.split_k) return B200_INVALID_SHAPE;
     return B200_OK;
 }
 

@@ -139,7 +139,7 @@ class PushExchange:
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
-    def gemm_reduce_scatter(self, A, Bt, D_rows, params, Cm_rows=None, alpha=1.0, beta=0.0, stream=None):
+    def gemm_reduce_scatter(self, A, Bt, D_rows, params, Cm_rows=None, alpha=1.0, beta=0.0, stream=None, workspace=None):
         """A: M x K_local, Bt: N x K_local (this rank's K slice); D_rows: (M/world) x N fp32, this
         rank's rows of the full product. Asynchronous on the current stream."""
         import torch
@@ -148,9 +148,12 @@ class PushExchange:
         self.epoch += 1
         sptr = stream if stream is not None else torch.cuda.current_stream(A.device).cuda_stream
         odd = self.epoch & 1
+        need = pkg.workspace_bytes(self.M, self.N, A.shape[1], params)
+        if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+            workspace = self._ws = torch.empty(need, dtype=torch.uint8, device=A.device)
         st = lib.b200_gemm_push(dtype, A.data_ptr(), Bt.data_ptr(), self.M, self.N, A.shape[1], self.C.byref(params),
                                 self.world, self.rank, self.slot_ptrs_odd if odd else self.slot_ptrs, self.flag_ptrs,
-                                self.done, self.epoch, sptr)
+                                self.done, self.epoch, workspace.data_ptr() if need else None, need, sptr)
         if st != pkg.OK:
             raise pkg.B200Error(st, "b200_gemm_push")
         st = lib.b200_push_reduce(self.slots.value + (self.area_bytes if odd else 0), self.flags, self.world, self.epoch,

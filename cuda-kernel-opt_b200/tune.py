@@ -1,0 +1,118 @@
+"""Sweep harness / autotuner for the launch tunables of one GEMM shape.
+
+The reference explores its tunables with hard-coded nested sweeps in main() that print one line
+per tuple (matmul_shmem_tc_async_opt_port_2.cu:1208-1232, :1554-1564). This is the same idea as a
+tool: candidate tuples for a shape are timed round-robin (so all of them see the same clock under
+the power limit), every finished candidate is appended to a JSONL file, an interrupted run resumes
+where it stopped, and the best tuple can be read back.
+
+    python cuda-kernel-opt_b200/tune.py 8192 8192 8192 --dtype f16 --out tune.jsonl
+
+Needs a B200; there is no CPU path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def candidates(M: int, N: int, K: int) -> list[dict]:
+    """Tunable tuples worth timing for the shape: tile shape x stages x producer warps x L2 hint
+    (x split-K when the tiles do not fill the GPU). Invalid ones are filtered by validate()."""
+    out = []
+    tiles = []
+    if M > 128:
+        tiles += [dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=256, tile_n=128, cta_group=2)]
+    tiles += [dict(tile_m=128, tile_n=tn, cta_group=1) for tn in (256, 224, 192, 128, 64) if N % tn == 0 or tn == 128]
+    for t in tiles:
+        per_stage = (t["tile_m"] // t["cta_group"] + t["tile_n"] // t["cta_group"]) * 128
+        deepest = min(8, 200000 // per_stage)
+        for stages in sorted({deepest, max(2, deepest - 2)}):
+            for pw in (1, 2):
+                for hint in ((0, 3) if M > 128 else (0, 1)):
+                    base = dict(t, num_stages=stages, num_producer_warps=pw, l2_hint=hint)
+                    out.append(base)
+                    n_tiles = -(-M // t["tile_m"]) * -(-N // t["tile_n"])
+                    slots = 148 // t["cta_group"]
+                    if n_tiles < slots and K >= 8192:
+                        for s in (2, 4, 8):
+                            out.append(dict(base, split_k=s))
+    return out
+
+
+def key_of(params: dict) -> str:
+    return json.dumps(params, sort_keys=True)
+
+
+def load(path: str) -> list[dict]:
+    if not os.path.exists(path):
+        return []
+    with open(path) as f:
+        return [json.loads(line) for line in f if line.strip()]
+
+
+def best(path: str, M: int, N: int, K: int, dtype: str = "f16") -> dict | None:
+    rows = [r for r in load(path) if r["shape"] == [M, N, K] and r["dtype"] == dtype and r["status"] == 0]
+    return min(rows, key=lambda r: r["ms"])["params"] if rows else None
+
+
+def tune(M: int, N: int, K: int, dtype: str = "f16", out: str = "tune.jsonl", rounds: int = 12, inner: int = 3, log=print):
+    import torch
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    code = pkg.BF16 if dtype == "bf16" else pkg.F16
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    done = {key_of(r["params"]) for r in load(out) if r["shape"] == [M, N, K] and r["dtype"] == dtype}
+    A = torch.empty((M, K), dtype=tdt, device="cuda")
+    Bt = torch.empty((N, K), dtype=tdt, device="cuda")
+    pkg.fill_device(A, 1, 1)
+    pkg.fill_device(Bt, 1, 2)
+    D = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    todo = []
+    for ov in candidates(M, N, K):
+        if key_of(ov) in done:
+            continue
+        p = pkg.default_params(M, N, K, code, **ov)
+        if pkg.validate(M, N, K, code, p) != pkg.OK:
+            continue
+        need = pkg.workspace_bytes(M, N, K, p)
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        todo.append((ov, p, ws if need else None, []))
+    log(f"{len(todo)} candidates to time, {len(done)} already in {out}")
+    for _ in range(rounds):
+        for ov, p, ws, times in todo:
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(inner + 1)]
+            pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws)
+            evs[0].record()
+            for i in range(inner):
+                pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws)
+                evs[i + 1].record()
+            torch.cuda.synchronize()
+            times.append(evs[0].elapsed_time(evs[inner]) / inner)
+    status, _ = pkg.device_status()
+    with open(out, "a") as f:
+        for ov, p, ws, times in todo:
+            ms = sorted(times)[len(times) // 2]
+            row = {"shape": [M, N, K], "dtype": dtype, "params": ov, "ms": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12,
+                   "gbs": (2.0 * (M * K + N * K) + 4.0 * M * N) / (ms * 1e-3) / 1e9, "status": status}
+            f.write(json.dumps(row) + "\n")
+    return best(out, M, N, K, dtype)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("M", type=int)
+    ap.add_argument("N", type=int)
+    ap.add_argument("K", type=int)
+    ap.add_argument("--dtype", choices=["f16", "bf16"], default="f16")
+    ap.add_argument("--out", default="tune.jsonl")
+    ap.add_argument("--rounds", type=int, default=12)
+    a = ap.parse_args()
+    b = tune(a.M, a.N, a.K, a.dtype, a.out, a.rounds)
+    print(json.dumps({"shape": [a.M, a.N, a.K], "dtype": a.dtype, "best": b}))

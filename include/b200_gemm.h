@@ -138,7 +138,9 @@ int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt, const flo
  * is owner o's area of world x (M/world) x N floats, indexed [source rank][row][col], as mapped
  * into this process (b200_peer_import); flag_ptrs[o] is owner o's array of `world` ints. The last
  * CTA to finish writes `epoch` into flag[o][rank] on every owner. done_counter is a zeroed
- * local unsigned int. M/world must be a multiple of 128 (256 for the two-CTA tile), split_k = 1.
+ * local unsigned int. M/world must be a multiple of 128 (256 for the two-CTA tile). With
+ * p->split_k > 1 the K slices of this GPU are first summed from the caller's workspace
+ * (b200_gemm_workspace_bytes) and the sum is what travels, as coalesced 128-bit peer stores.
  *
  * b200_push_reduce, enqueued on the owner after its own b200_gemm_push, waits (bounded; a
  * DEVICE_TIMEOUT record if a peer never arrives) until all `world` flags show `epoch`, then
@@ -148,7 +150,7 @@ int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt, const flo
  * alternating slot areas). */
 int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
                    int world, int rank, void *const *slot_ptrs, void *const *flag_ptrs, void *done_counter, int epoch,
-                   void *stream);
+                   void *workspace, size_t workspace_bytes, void *stream);
 int b200_push_reduce(const float *my_slots, const int *my_flags, int world, int epoch, const float *C, float *D, float alpha,
                      float beta, int64_t rows, int64_t N, void *stream);
 /* Device memory that other processes of the box can map (cudaMalloc + CUDA IPC), zero-filled; the

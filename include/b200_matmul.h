@@ -49,6 +49,8 @@ struct InputType<__nv_bfloat16> {
 template <typename DT>
 inline int launch(const DT *A, const DT *B, const float *C, float *D, float alpha, float beta, int M, int N, int K,
                   const b200_gemm_params &p) {
+    // the reference's rule (async.cu:513-514, port_2.cu:1114-1115); the C ABI itself also takes ragged shapes
+    if (M % p.tile_m || N % p.tile_n || K % p.segment_dim_k) return B200_INVALID_SHAPE;
     if (InputType<DT>::value == B200_BF16)
         return b200_gemm_bf16(A, B, C, D, alpha, beta, M, N, K, &p, nullptr, 0, nullptr);
     return b200_gemm_f16(A, B, C, D, alpha, beta, M, N, K, &p, nullptr, 0, nullptr);

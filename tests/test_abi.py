@@ -76,11 +76,12 @@ def test_reference_parameter_domain(pkg):
     assert ok(num_producer_warps=3) == pkg.INVALID_CONFIG
     assert ok(num_consumer_warps=8) == pkg.OK
     assert ok(num_consumer_warps=6) == pkg.INVALID_CONFIG
-    assert ok(N=1000) == pkg.INVALID_SHAPE                                     # N % tile
-    assert ok(K=1000) == pkg.INVALID_SHAPE                                     # K % seg_k
+    assert ok(N=1002) == pkg.INVALID_SHAPE                                     # rows of D must be 16-byte multiples
+    assert ok(K=1004) == pkg.INVALID_SHAPE                                     # rows of A, B^T must be 16-byte multiples
+    assert ok(N=1000) == pkg.OK and ok(K=1000) == pkg.OK                       # ragged tiles are an extension of the C ABI
     assert ok(segment_dim_k=256, K=1024, num_stages=1) == pkg.OK
     assert ok(M=0) == pkg.INVALID_SHAPE
-    assert ok(M=1000) == pkg.OK                                                # ragged M is an extension
+    assert ok(M=1000) == pkg.OK                                                # (the reference-shaped C++ launchers keep its tile-multiple rule)
     assert pkg.validate(1024, 1024, 1024, 7, P(pkg)) == pkg.INVALID_CONFIG     # unknown dtype
 
 

@@ -144,6 +144,19 @@ def test_ragged_m_and_single_tile_edges(pkg, cuda, oracle):
         assert ok, (m, n, k, msg)
 
 
+def test_ragged_n_and_k(pkg, cuda, oracle):
+    """N and K need not be tile / segment multiples either (N % 4 == 0, K % 8 == 0)."""
+    for m, n, k, ov in ((256, 1000, 1000, dict(tile_m=128, tile_n=128)), (300, 516, 200, dict(tile_m=128, tile_n=256, epilogue=1)),
+                        (512, 772, 1096, dict(tile_m=256, tile_n=256, cta_group=2)), (130, 36, 72, dict(tile_m=64, tile_n=64)),
+                        (256, 520, 520, dict(tile_m=128, tile_n=128, split_k=3, segment_dim_k=128, num_stages=3))):
+        A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 170 + n)
+        got = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.0, 1.0, **ov)
+        want = oracle.gemm(A, Bt, Cm, 1.0, 1.0)
+        ok, msg = tolerance_ok(got, want, k, 2.0)
+        assert ok, (m, n, k, ov, msg)
+    assert pkg.validate(256, 1002, 1000, pkg.F16, pkg.default_params(256, 1000, 1000, pkg.F16)) == pkg.INVALID_SHAPE
+
+
 def test_split_k(pkg, cuda, oracle):
     for m, n, k, s, ov in ((256, 256, 2048, 4, dict()), (256, 512, 64 * 7, 3, dict()), (512, 512, 1024, 8, dict(tile_m=256, tile_n=256, cta_group=2))):
         A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 80 + s)
@@ -169,7 +182,7 @@ def test_error_statuses_on_device_calls(pkg, cuda):
     assert pkg.gemm_raw(pkg.F16, None, dA.data_ptr(), None, D.data_ptr(), *args) == pkg.INVALID_POINTER
     assert pkg.gemm_raw(pkg.F16, dA.data_ptr() + 2, dA.data_ptr(), None, D.data_ptr(), *args) == pkg.INVALID_POINTER
     assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 1.0, 128, 128, 64, p) == pkg.INVALID_POINTER  # beta without C
-    assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 0.0, 128, 100, 64, p) == pkg.INVALID_SHAPE
+    assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 0.0, 128, 102, 64, p) == pkg.INVALID_SHAPE
     bad = pkg.default_params(128, 128, 64, pkg.F16, tile_n=128, num_stages=0)
     assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), 1.0, 0.0, 128, 128, 64, bad) == pkg.INVALID_CONFIG
     assert pkg.gemm_raw(pkg.F16, dA.data_ptr(), dA.data_ptr(), None, D.data_ptr(), *args) == pkg.OK

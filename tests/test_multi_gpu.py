@@ -42,7 +42,8 @@ def _worker(rank, world, port, q):
         # (2) exchange fused into the epilogue, three steps in a row (alternating slot areas)
         ex = shard.PushExchange(pkg, m, n)
         out = torch.empty((m // world, n), dtype=torch.float32, device="cuda")
-        for tile in (dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=128, tile_n=128), dict(tile_m=256, tile_n=128, cta_group=2)):
+        for tile in (dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=128, tile_n=128), dict(tile_m=256, tile_n=128, cta_group=2),
+                     dict(tile_m=256, tile_n=256, cta_group=2, split_k=4), dict(tile_m=128, tile_n=256, split_k=3)):
             out.fill_(float("nan"))
             ex.gemm_reduce_scatter(dA, dB, out, pkg.default_params(m, n, ks.size, pkg.F16, **tile))
             torch.cuda.synchronize()

@@ -1,0 +1,41 @@
+"""CPU: the sweep harness's candidate generation, JSONL record and resume logic (no timing here)."""
+import importlib
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def tune_mod():
+    from __graft_entry__ import load_package
+    load_package()
+    return importlib.import_module("cuda_kernel_opt_b200.tune")
+
+
+def test_candidates_are_valid_or_filtered(pkg):
+    t = tune_mod()
+    for shape in ((8192, 8192, 8192), (16, 28672, 8192), (2048, 2048, 262144), (1024, 1024, 1024)):
+        cands = t.candidates(*shape)
+        assert len(cands) >= 8 and len({t.key_of(c) for c in cands}) == len(cands)
+        valid = [c for c in cands if pkg.validate(*shape, pkg.F16, pkg.default_params(*shape, pkg.F16, **c)) == pkg.OK]
+        assert len(valid) >= len(cands) // 2, shape
+    assert any(c.get("split_k", 1) > 1 for c in t.candidates(2048, 2048, 262144))      # too few tiles: split-K offered
+    assert not any(c.get("split_k", 1) > 1 for c in t.candidates(8192, 8192, 8192))
+
+
+def test_record_resume_and_best(tmp_path):
+    t = tune_mod()
+    path = str(tmp_path / "tune.jsonl")
+    rows = [{"shape": [64, 64, 64], "dtype": "f16", "params": {"tile_n": 64}, "ms": 2.0, "tflops": 1.0, "gbs": 1.0, "status": 0},
+            {"shape": [64, 64, 64], "dtype": "f16", "params": {"tile_n": 16}, "ms": 1.0, "tflops": 2.0, "gbs": 2.0, "status": 0},
+            {"shape": [64, 64, 64], "dtype": "f16", "params": {"tile_n": 32}, "ms": 0.5, "tflops": 4.0, "gbs": 4.0, "status": 5},
+            {"shape": [128, 64, 64], "dtype": "f16", "params": {"tile_n": 8}, "ms": 0.1, "tflops": 9.0, "gbs": 9.0, "status": 0}]
+    with open(path, "w") as f:
+        for r in rows:
+            f.write(json.dumps(r) + "\n")
+    assert len(t.load(path)) == 4
+    assert t.best(path, 64, 64, 64) == {"tile_n": 16}            # fastest with a clean device status
+    assert t.best(path, 64, 64, 64, "bf16") is None
+    assert t.best(str(tmp_path / "missing.jsonl"), 64, 64, 64) is None
