@@ -314,7 +314,10 @@ struct b200_session {
     int64_t max_m, max_n, max_k;
     void *dA, *dB;
     float *dC, *dD;
-    cudaStream_t stream;
+    cudaStream_t stream;      // uploads
+    cudaStream_t compute;     // launches
+    cudaStream_t download;    // results
+    cudaEvent_t up[16], done[16], b_ready;
 };
 
 extern "C" {
@@ -440,6 +443,13 @@ int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_sessio
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dC), static_cast<size_t>(max_m) * max_n * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dD), static_cast<size_t>(max_m) * max_n * 4);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->compute, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->download, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->b_ready, cudaEventDisableTiming);
+    for (int i = 0; i < 16 && e == cudaSuccess; ++i) {
+        e = cudaEventCreateWithFlags(&s->up[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->done[i], cudaEventDisableTiming);
+    }
     if (e != cudaSuccess) {
         b200_session_destroy(s);
         return fail_cuda(e);
@@ -451,6 +461,13 @@ int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_sessio
 void b200_session_destroy(b200_session *s) {
     if (!s) return;
     if (s->stream) cudaStreamDestroy(s->stream);
+    if (s->compute) cudaStreamDestroy(s->compute);
+    if (s->download) cudaStreamDestroy(s->download);
+    if (s->b_ready) cudaEventDestroy(s->b_ready);
+    for (int i = 0; i < 16; ++i) {
+        if (s->up[i]) cudaEventDestroy(s->up[i]);
+        if (s->done[i]) cudaEventDestroy(s->done[i]);
+    }
     cudaFree(s->dA);
     cudaFree(s->dB);
     cudaFree(s->dC);
@@ -463,15 +480,55 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
     if (!s || !hA || !hBt || !hD) return B200_INVALID_POINTER;
     if (M > s->max_m || N > s->max_n || K > s->max_k) return B200_INVALID_SHAPE;
     if (beta != 0.0f && !hC) return B200_INVALID_POINTER;
-    cudaError_t e = cudaMemcpyAsync(s->dA, hA, static_cast<size_t>(M) * K * 2, cudaMemcpyHostToDevice, s->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(s->dB, hBt, static_cast<size_t>(N) * K * 2, cudaMemcpyHostToDevice, s->stream);
-    if (e == cudaSuccess && beta != 0.0f)
-        e = cudaMemcpyAsync(s->dC, hC, static_cast<size_t>(M) * N * 4, cudaMemcpyHostToDevice, s->stream);
+    // Row blocks of A / C / D are pipelined over three streams: while block i is multiplied, block
+    // i+1 is uploaded and block i-1 is downloaded (the two copy directions use different engines).
+    // B^T goes first, every block needs it. Block boundaries fall on tile rows, so the result is
+    // bit-identical to one launch over the whole problem.
+    b200_gemm_params local;
+    if (!p) {
+        default_params(M, N, K, &local);
+        p = &local;
+    }
+    const int64_t tile_m = p->tile_m > 0 ? p->tile_m : 128;
+    int64_t block_rows = ((M + 7) / 8 + tile_m - 1) / tile_m * tile_m;
+    if (block_rows < 2 * tile_m) block_rows = 2 * tile_m;
+    int blocks = static_cast<int>((M + block_rows - 1) / block_rows);
+    if (blocks > 16) {
+        block_rows = ((M + 15) / 16 + tile_m - 1) / tile_m * tile_m;
+        blocks = static_cast<int>((M + block_rows - 1) / block_rows);
+    }
+    const char *hA8 = static_cast<const char *>(hA);
+    char *dA8 = static_cast<char *>(s->dA);
+    cudaError_t e = cudaMemcpyAsync(s->dB, hBt, static_cast<size_t>(N) * K * 2, cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(s->b_ready, s->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s->compute, s->b_ready, 0);
     if (e != cudaSuccess) return fail_cuda(e);
-    const int st = gemm_impl(dtype, s->dA, s->dB, beta != 0.0f ? s->dC : nullptr, s->dD, alpha, beta, M, N, K, p, nullptr, 0,
-                             s->stream);
-    if (st != B200_OK) return st;
-    e = cudaMemcpyAsync(hD, s->dD, static_cast<size_t>(M) * N * 4, cudaMemcpyDeviceToHost, s->stream);
+    for (int b = 0; b < blocks; ++b) {
+        const int64_t r0 = b * block_rows;
+        const int64_t rows = (M - r0 < block_rows) ? (M - r0) : block_rows;
+        e = cudaMemcpyAsync(dA8 + static_cast<size_t>(r0) * K * 2, hA8 + static_cast<size_t>(r0) * K * 2,
+                            static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, s->stream);
+        if (e == cudaSuccess && beta != 0.0f)
+            e = cudaMemcpyAsync(s->dC + static_cast<size_t>(r0) * N, hC + static_cast<size_t>(r0) * N,
+                                static_cast<size_t>(rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
+        if (e == cudaSuccess) e = cudaEventRecord(s->up[b], s->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->compute, s->up[b], 0);
+        if (e != cudaSuccess) return fail_cuda(e);
+        const int st = gemm_impl(dtype, dA8 + static_cast<size_t>(r0) * K * 2, s->dB,
+                                 beta != 0.0f ? s->dC + static_cast<size_t>(r0) * N : nullptr, s->dD + static_cast<size_t>(r0) * N,
+                                 alpha, beta, rows, N, K, p, nullptr, 0, s->compute);
+        if (st != B200_OK) {
+            cudaDeviceSynchronize();
+            return st;
+        }
+        e = cudaEventRecord(s->done[b], s->compute);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[b], 0);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(hD + static_cast<size_t>(r0) * N, s->dD + static_cast<size_t>(r0) * N,
+                                static_cast<size_t>(rows) * N * 4, cudaMemcpyDeviceToHost, s->download);
+        if (e != cudaSuccess) return fail_cuda(e);
+    }
+    e = cudaStreamSynchronize(s->download);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
     if (e != cudaSuccess) return fail_cuda(e);
     return B200_OK;
