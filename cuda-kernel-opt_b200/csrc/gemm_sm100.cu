@@ -360,183 +360,216 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         }
         __syncwarp();
     } else if (warp < P) {
-        // ------------------------------------------------------------------ producers, general form (sub-tile barriers)
-        // The warp runs its loops converged; one elected lane issues. In a two-CTA pair only the
-        // leader arms the full barriers (with the bytes of both CTAs); the peer's copies complete
-        // the leader's barriers through their cluster addresses.
+        // ------------------------------------------------------------------ producers, general form
+        // Sub-tile barriers (shift synchronisation): the A stage buffer is loaded in row boxes, the
+        // B^T buffer in column sub-tiles, each group with its own full barrier; the first a_priv /
+        // b_priv groups are private, the rest share a residual barrier. Same lean structure as
+        // above: converged warp, one elected issuing lane, running addresses.
         const bool do_a = (P == 1) || (warp == 0);
         const bool do_b = (P == 1) || (warp == 1);
         if (do_a || do_b) {
-            int s = 0;
-            uint32_t ph = 0;
-            uint32_t it = 0;
-            bool ok = true;
-            long long t_wait = 0, t_issue_a = 0;
-            const long long t_begin = clock64();
-            const uint32_t a_priv_bytes = static_cast<uint32_t>(c.kblocks * c.a_box_rows * kSwizzleBytes) * CG;
-            const uint32_t a_res_bytes = a_priv_bytes * static_cast<uint32_t>(c.a_boxes - c.a_priv);
-            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
             const bool issuer = elect_one();
+            const bool arm = issuer && rank == 0;
+            const bool issue = issuer && !(dbg & 2);
+            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
+            const uint32_t a_box_bytes = static_cast<uint32_t>(c.a_box_rows * kSwizzleBytes);
+            const uint32_t a_kb_bytes = static_cast<uint32_t>(c.cta_rows_a * kSwizzleBytes);
+            const uint32_t a_priv_tx = (dbg & 2) ? 0u : static_cast<uint32_t>(c.kblocks * CG) * a_box_bytes;
+            const uint32_t a_res_tx = a_priv_tx * static_cast<uint32_t>(c.a_boxes - c.a_priv);
+            const uint32_t b_box_bytes = static_cast<uint32_t>(b_box_rows * kSwizzleBytes);
+            const uint32_t b_priv_tx = (dbg & 2) ? 0u : static_cast<uint32_t>(c.kblocks * c.chunk_n * kSwizzleBytes);
+            const uint32_t b_res_tx = b_priv_tx * static_cast<uint32_t>(c.b_res_chunks);
+            const uint32_t b_sub_bytes = b_box_bytes * static_cast<uint32_t>(c.kblocks);  // one private sub-tile in this CTA
+            const uint32_t b_all_tx = (dbg & 2) ? 0u : static_cast<uint32_t>(c.kblocks * c.tile_n * kSwizzleBytes);
+            int s = 0;
+            uint32_t ph = 0, it = 0;
+            uint32_t stage = base, sb = bars, sbl = bars_leader;
+            bool ok = true;
+            long long t_wait = 0;
+            const long long t_begin = PROF ? clock64() : 0;
             for (int u = group; ok && u < c.num_units; u += num_groups) {
                 const Unit w = decode_unit(c, u);
-                const int a_row0 = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
-                for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg, ++it) {
-                    const int k0 = seg * c.kblocks * kBoxK;
-                    const uint32_t stage = base + static_cast<uint32_t>(s * c.stage_bytes);
-                    const uint32_t sb_off = static_cast<uint32_t>(s) * stage_bar_bytes;
-                    const uint32_t sb = bars + sb_off;            // this CTA's barriers (empty: waited here)
-                    const uint32_t sbl = bars_leader + sb_off;    // the leader's barriers (full: completed there)
+                const int a_row = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
+                int k = w.seg_begin * c.kblocks * kBoxK;
+                for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
                     if (do_a) {
-                        const long long tw = prof ? clock64() : 0;
-                        ok = __all_sync(0xffffffffu, wait_bar(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s));
-                        if (prof) t_wait += clock64() - tw;
+                        const long long tw = PROF ? clock64() : 0;
+                        ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
+                        if (PROF) t_wait += clock64() - tw;
                         if (!ok) break;
-                        const long long ti = prof ? clock64() : 0;
+                        uint32_t box_dst = stage;
+                        int box_row = a_row;
                         for (int j = 0; j < c.a_bars; ++j) {
-                            const int first = j < c.a_priv ? j : c.a_priv;
-                            const int nbox = j < c.a_priv ? 1 : c.a_boxes - c.a_priv;
-                            uint32_t bytes = j < c.a_priv ? a_priv_bytes : a_res_bytes;
-                            if (merged && P == 1) bytes += static_cast<uint32_t>(c.kblocks * c.tile_n * kSwizzleBytes);
-                            if (dbg & 2) bytes = 0;
-                            if (issuer && rank == 0) mbar_arrive_expect_tx(sb + 8u * j, bytes);
+                            const bool priv = j < c.a_priv;
+                            const int nbox = priv ? 1 : c.a_boxes - c.a_priv;
+                            uint32_t tx = priv ? a_priv_tx : a_res_tx;
+                            if (merged && P == 1) tx += b_all_tx;
+                            if (arm) mbar_arrive_expect_tx(sb + 8u * j, tx);
+                            const uint32_t bar = ((CG == 2) ? sbl : sb) + 8u * j;
+                            uint32_t kb_dst = box_dst;
+                            int kk = k;
                             for (int kb = 0; kb < c.kblocks; ++kb) {
-                                for (int b = first; b < first + nbox; ++b) {
-                                    const uint32_t dst = stage + static_cast<uint32_t>(
-                                        (kb * c.cta_rows_a + b * c.a_box_rows) * kSwizzleBytes);
-                                    if (issuer && !(dbg & 2)) {
-                                        if constexpr (CG == 2) tma_load_2d_pair(dst, &g.map_a, sbl + 8u * j, k0 + kb * kBoxK, a_row0 + b * c.a_box_rows);
-                                        else tma_load_2d(dst, &g.map_a, sb + 8u * j, k0 + kb * kBoxK, a_row0 + b * c.a_box_rows);
+                                uint32_t d = kb_dst;
+                                int r = box_row;
+                                for (int b = 0; b < nbox; ++b) {
+                                    if (issue) {
+                                        if constexpr (CG == 2) tma_load_2d_pair(d, &g.map_a, bar, kk, r);
+                                        else tma_load_2d(d, &g.map_a, bar, kk, r);
                                     }
+                                    d += a_box_bytes;
+                                    r += c.a_box_rows;
                                 }
+                                kb_dst += a_kb_bytes;
+                                kk += kBoxK;
                             }
+                            box_dst += a_box_bytes;
+                            box_row += c.a_box_rows;
                         }
-                        if (prof) t_issue_a += clock64() - ti;
                     }
                     if (do_b) {
-                        const uint32_t stage_b = stage + static_cast<uint32_t>(c.a_stage_bytes);
-                        for (int t = 0; ok && t < c.b_bars; ++t) {
+                        uint32_t sub = stage + static_cast<uint32_t>(c.a_stage_bytes);
+                        int sub_row = w.n0;
+                        for (int t = 0; t < c.b_bars; ++t) {
                             if (!(merged && do_a)) {  // merged + same warp: the stage was acquired above
-                                const long long tw = prof ? clock64() : 0;
-                                ok = __all_sync(0xffffffffu, wait_bar(sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u,
-                                                                      c.budget, abort_flag, 200 + s * 32 + t));
-                                if (prof) t_wait += clock64() - tw;
+                                const long long tw = PROF ? clock64() : 0;
+                                ok = wait_all(sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u, c.budget, abort_flag,
+                                              200 + s * 32 + t);
+                                if (PROF) t_wait += clock64() - tw;
                                 if (!ok) break;
                             }
-                            {
-                                const int off_t = t * c.chunk_n;  // the residual follows the private sub-tiles
-                                const int w_t = t < c.b_priv ? c.chunk_n : c.b_res_chunks * c.chunk_n;
-                                const int rows_t = w_t / CG;
-                                const int nbox = rows_t / b_box_rows;
-                                const uint32_t bar_off = merged ? 0u : full_b_off + 8u * t;
-                                if (issuer && rank == 0 && !(merged && P == 1))
-                                    mbar_arrive_expect_tx(sb + bar_off, (dbg & 2) ? 0u : static_cast<uint32_t>(c.kblocks * w_t * kSwizzleBytes));
-                                const uint32_t sub = stage_b + static_cast<uint32_t>((off_t / CG) * c.kblocks * kSwizzleBytes);
-                                const int b_row0 = w.n0 + off_t + static_cast<int>(rank) * rows_t;
-                                for (int kb = 0; kb < c.kblocks; ++kb) {
-                                    for (int b = 0; b < nbox; ++b) {
-                                        const uint32_t dst = sub + static_cast<uint32_t>((kb * rows_t + b * b_box_rows) * kSwizzleBytes);
-                                        if (issuer && !(dbg & 2)) {
-                                            if constexpr (CG == 2) tma_load_2d_pair(dst, &g.map_b, sbl + bar_off, k0 + kb * kBoxK, b_row0 + b * b_box_rows);
-                                            else tma_load_2d(dst, &g.map_b, sb + bar_off, k0 + kb * kBoxK, b_row0 + b * b_box_rows);
-                                        }
+                            const bool priv = t < c.b_priv;
+                            const int nbox = priv ? 1 : c.b_res_chunks;       // boxes of b_box_rows rows per K block
+                            const uint32_t bar_off = merged ? 0u : full_b_off + 8u * t;
+                            if (arm && !(merged && P == 1)) mbar_arrive_expect_tx(sb + bar_off, priv ? b_priv_tx : b_res_tx);
+                            const uint32_t bar = ((CG == 2) ? sbl : sb) + bar_off;
+                            const int row0 = sub_row + static_cast<int>(rank) * nbox * b_box_rows;
+                            uint32_t d = sub;
+                            int kk = k;
+                            for (int kb = 0; kb < c.kblocks; ++kb) {
+                                int r = row0;
+                                for (int b = 0; b < nbox; ++b) {
+                                    if (issue) {
+                                        if constexpr (CG == 2) tma_load_2d_pair(d, &g.map_b, bar, kk, r);
+                                        else tma_load_2d(d, &g.map_b, bar, kk, r);
                                     }
+                                    d += b_box_bytes;
+                                    r += b_box_rows;
                                 }
+                                kk += kBoxK;
                             }
+                            sub += b_sub_bytes;
+                            sub_row += c.chunk_n;
                         }
+                        if (!ok) break;
                     }
+                    ++it;
+                    k += c.kblocks * kBoxK;
+                    stage += static_cast<uint32_t>(c.stage_bytes);
+                    sb += stage_bar_bytes;
+                    sbl += stage_bar_bytes;
                     if (++s == c.stages) {
                         s = 0;
                         ph ^= 1u;
+                        stage = base;
+                        sb = bars;
+                        sbl = bars_leader;
                     }
                 }
             }
-            if (prof && lane == 0) {
+            if (PROF && prof && lane == 0) {
                 prof[warp == 0 ? 0 : 3] = t_wait;
                 prof[warp == 0 ? 1 : 4] = clock64() - t_begin;
                 prof[warp == 0 ? 2 : 5] = it;
-                if (warp == 0) prof[13] = t_issue_a;
             }
         }
     } else if (warp == mma_warp) {
-        // ------------------------------------------------------------------ MMA issue
+        // ------------------------------------------------------------------ MMA issue, general form
+        // One MMA group per B^T sub-tile, in load order: the first sub-tile's MMAs start as soon as
+        // A and that sub-tile have landed. Each sub-tile frees its own part of the stage.
         if (rank == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            uint32_t it = 0;
-            uint32_t tl = 0;
-            bool ok = true;
-            long long t_full = 0, t_acc = 0, t_mma = 0, t_commit = 0;
-            const long long t_begin = clock64();
             const bool issuer = elect_one();
+            const bool issue = issuer && !(dbg & 1);
+            const uint64_t a_desc0 = umma_desc_sw128(base);
+            const uint64_t b_desc0 = umma_desc_sw128(base + static_cast<uint32_t>(c.a_stage_bytes));
+            const uint64_t stage_step = static_cast<uint64_t>(c.stage_bytes >> 4);
+            const uint64_t a_kb_step = static_cast<uint64_t>((c.cta_rows_a * kSwizzleBytes) >> 4);
+            const uint64_t b_box_step = static_cast<uint64_t>((b_box_rows * kSwizzleBytes) >> 4);   // one box of a K block
+            const uint64_t b_sub_step = b_box_step * static_cast<uint64_t>(c.kblocks);             // one private sub-tile
+            int s = 0;
+            uint32_t ph = 0, it = 0, tl = 0;
+            uint32_t sb = bars;
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            bool ok = true;
+            long long t_full = 0, t_acc = 0;
+            const long long t_begin = PROF ? clock64() : 0;
             for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
                 const Unit w = decode_unit(c, u);
                 const uint32_t acc = tl & 1u;
                 const uint32_t aph = (tl >> 1) & 1u;
-                const long long ta = prof ? clock64() : 0;
-                ok = __all_sync(0xffffffffu, wait_bar(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc)));
-                if (prof) t_acc += clock64() - ta;
+                const long long ta = PROF ? clock64() : 0;
+                ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_base = tmem_base + acc * static_cast<uint32_t>(c.acc_cols);
-                for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg, ++it) {
-                    const uint32_t stage = base + static_cast<uint32_t>(s * c.stage_bytes);
-                    const uint32_t stage_b = stage + static_cast<uint32_t>(c.a_stage_bytes);
-                    const uint32_t sb = bars + static_cast<uint32_t>(s) * stage_bar_bytes;
-                    const long long tf = prof ? clock64() : 0;
-                    for (int j = 0; ok && j < c.a_bars; ++j)
-                        ok = __all_sync(0xffffffffu, wait_bar(sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j));
-                    if (prof) t_full += clock64() - tf;
+                uint32_t later_seg = 0;
+                for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
+                    const long long tf = PROF ? clock64() : 0;
+                    for (int j = 0; ok && j < c.a_bars; ++j) ok = wait_all(sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j);
+                    if (PROF) t_full += clock64() - tf;
                     if (!ok) break;
-                    const uint32_t first_seg = (seg == w.seg_begin) ? 0u : 1u;
+                    uint64_t sub_desc = b_desc;
+                    uint32_t d_addr = d_base;
                     for (int t = 0; t < c.b_bars; ++t) {
                         if (!merged) {
-                            const long long tb = prof ? clock64() : 0;
-                            ok = __all_sync(0xffffffffu, wait_bar(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t));
-                            if (prof) t_full += clock64() - tb;
+                            const long long tb = PROF ? clock64() : 0;
+                            ok = wait_all(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
+                            if (PROF) t_full += clock64() - tb;
                             if (!ok) break;
                         }
                         tc_fence_after_sync();
-                        const long long tm = prof ? clock64() : 0;
-                        {
-                            const int off_t = t * c.chunk_n;
-                            const int w_t = t < c.b_priv ? c.chunk_n : c.b_res_chunks * c.chunk_n;
-                            const int rows_t = w_t / CG;
-                            const uint32_t idesc = t < c.b_priv ? c.idesc_chunk : c.idesc_res;
-                            const uint32_t sub = stage_b + static_cast<uint32_t>((off_t / CG) * c.kblocks * kSwizzleBytes);
-                            for (int kb = 0; kb < c.kblocks; ++kb) {
-                                const uint64_t adesc = umma_desc_sw128(stage + static_cast<uint32_t>(kb * c.cta_rows_a * kSwizzleBytes));
-                                const uint64_t bdesc = umma_desc_sw128(sub + static_cast<uint32_t>(kb * rows_t * kSwizzleBytes));
+                        const bool priv = t < c.b_priv;
+                        const uint32_t idesc = priv ? c.idesc_chunk : c.idesc_res;
+                        const uint64_t b_kb_step = priv ? b_box_step : b_box_step * static_cast<uint64_t>(c.b_res_chunks);
+                        uint64_t da = a_desc, db = sub_desc;
+                        for (int kb = 0; kb < c.kblocks; ++kb) {
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    // +32 bytes per 16-element K step inside the 128-byte swizzle row
-                                    if (issuer && !(dbg & 1))
-                                        umma_f16<CG>(d_base + static_cast<uint32_t>(off_t), adesc + static_cast<uint64_t>(2 * i),
-                                                     bdesc + static_cast<uint64_t>(2 * i), idesc, (first_seg | kb | i) ? 1u : 0u);
-                                }
+                            for (int i = 0; i < 4; ++i) {
+                                // +32 bytes per 16-element K step inside the 128-byte swizzle row
+                                if (issue)
+                                    umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc,
+                                                 (later_seg | static_cast<uint32_t>(kb) | static_cast<uint32_t>(i)) ? 1u : 0u);
                             }
-                            if (!merged && issuer) commit_to<CG>(sb + empty_b_off + 8u * t);
+                            da += a_kb_step;
+                            db += b_kb_step;
                         }
-                        if (prof) t_mma += clock64() - tm;
+                        if (!merged && issuer) commit_to<CG>(sb + empty_b_off + 8u * t);
+                        sub_desc += b_sub_step;
+                        d_addr += static_cast<uint32_t>(c.chunk_n);
                     }
                     if (!ok) break;
-                    const long long tc2 = prof ? clock64() : 0;
                     if (issuer) commit_to<CG>(sb + empty_a_off);
-                    if (prof) t_commit += clock64() - tc2;
+                    later_seg = 1;
+                    ++it;
+                    a_desc += stage_step;
+                    b_desc += stage_step;
+                    sb += stage_bar_bytes;
                     if (++s == c.stages) {
                         s = 0;
                         ph ^= 1u;
+                        a_desc = a_desc0;
+                        b_desc = b_desc0;
+                        sb = bars;
                     }
                 }
                 if (!ok) break;
                 if (issuer) commit_to<CG>(tmem_full0 + 8u * acc);
             }
-            if (prof && lane == 0) {
+            if (PROF && prof && lane == 0) {
                 prof[6] = t_full;
                 prof[7] = t_acc;
                 prof[8] = clock64() - t_begin;
                 prof[9] = it;
-                prof[14] = t_mma;
-                prof[15] = t_commit;
             }
         }
         __syncwarp();
