@@ -128,6 +128,8 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
         p.bar_step_rows_b = p.tile_n
     if "bar_step_rows_a" not in overrides:
         p.bar_step_rows_a = p.tile_m
+    if "epilogue" not in overrides and lib().b200_gemm_smem_bytes(dtype, C.byref(p)) < 0 and "num_stages" in overrides:
+        p.epilogue = 0                  # an explicit depth wins over the default TMA-store staging
     if "num_stages" not in overrides:   # a default depth chosen for another tile may not fit this one
         while p.num_stages > 1 and lib().b200_gemm_smem_bytes(dtype, C.byref(p)) < 0:
             p.num_stages -= 1
