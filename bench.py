@@ -92,7 +92,8 @@ class ClockSampler(threading.Thread):
             return
         try:
             self.sm.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
-            self.power.append(self.nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+            if len(self.sm) % 8 == 1:
+                self.power.append(self.nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
             try:
                 self.bits |= self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
             except Exception:
@@ -103,7 +104,7 @@ class ClockSampler(threading.Thread):
     def run(self):
         while not self.stop_flag:
             self.sample()
-            time.sleep(0.001)
+            time.sleep(0.0005)
 
     def summary(self):
         sm = sorted(self.sm)
@@ -283,7 +284,7 @@ def run_ours(args):
     assert st == pkg.OK, f"invalid configuration {p.as_dict()}: {pkg.status_string(st)}"
     ws_bytes = pkg.workspace_bytes(m_loc, n_loc, k_loc, p)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-    launches_per_step = 1 + (1 if p.split_k > 1 else 0) + (1 if fused else 0)
+    launches_per_step = 1 + (1 if (p.split_k > 1 or ws_bytes > 0) else 0) + (1 if fused else 0)
     push = shard.PushExchange(pkg, M, N) if fused else None
     D_rows = torch.empty((M // world, N), dtype=torch.float32, device=dev) if fused else None
     if fused:

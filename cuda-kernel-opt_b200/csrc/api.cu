@@ -129,7 +129,8 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
             if (N % tn) continue;
             const int64_t tiles = rows * (N / tn);
             const int64_t waves = (tiles + 147) / 148;
-            const double eff = double(tiles) / double(waves * 148) * (tn >= 128 ? 1.0 : tn / 128.0);
+            // narrow tiles cost tensor-core efficiency, which only matters when the shape is not HBM-bound
+            const double eff = double(tiles) / double(waves * 148) * ((tn >= 128 || (M <= 128 && tn >= 32)) ? 1.0 : tn / 128.0);
             if (eff > best_eff + 1e-9) {
                 best_eff = eff;
                 best_n = tn;
@@ -194,6 +195,14 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bt) | reinterpret_cast<uintptr_t>(D) |
          reinterpret_cast<uintptr_t>(C)) & 15u)
         return B200_INVALID_POINTER;
+    const int64_t n_tiles = ((M + p.tile_m - 1) / p.tile_m) * ((N + p.tile_n - 1) / p.tile_n);
+    const TailSplit tail = make_tail_split(user->tail_split && !(push && push->world > 0), n_tiles, p.grid / p.cta_group,
+                                           (K + p.seg_k - 1) / p.seg_k, p.split_k);
+    if (tail.s > 1) {
+        const size_t need = static_cast<size_t>(tail.s) * tail.r * p.tile_m * p.tile_n * sizeof(float);
+        if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
+        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
+    }
     if (p.split_k > 1) {
         const size_t need = static_cast<size_t>(p.split_k) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
         if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
@@ -229,6 +238,10 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.num_tiles = a.tiles_m * a.tiles_n;
     a.split_k = p.split_k;
     a.num_units = a.num_tiles * p.split_k;
+    a.tail_full = tail.full;
+    a.tail_r = tail.r;
+    a.tail_s = tail.s;
+    if (tail.s > 1) a.num_units = tail.full + tail.r * tail.s;
     a.num_segs = static_cast<int>((K + p.seg_k - 1) / p.seg_k);
     a.tile_m = p.tile_m;
     a.tile_n = p.tile_n;
@@ -290,6 +303,9 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     } else if (p.split_k > 1) {
         const int re = launch_splitk_reduce(a.partial, C, D, alpha, beta, M * N, p.split_k, stream);
         if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
+    } else if (tail.s > 1) {
+        const int re = launch_tail_reduce(a, stream);
+        if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
     }
     return B200_OK;
 }
@@ -347,9 +363,16 @@ int64_t b200_gemm_smem_bytes(int dtype, const b200_gemm_params *p) {
 }
 
 int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p) {
-    (void)K;
-    if (!p || p->split_k <= 1) return 0;
-    return static_cast<int64_t>(p->split_k) * M * N * static_cast<int64_t>(sizeof(float));
+    if (!p) return 0;
+    if (p->split_k > 1) return static_cast<int64_t>(p->split_k) * M * N * static_cast<int64_t>(sizeof(float));
+    if (p->tail_split) {
+        const Plan plan = make_plan(*p, p->num_sms > 0 ? p->num_sms : 148);
+        if (plan.status != B200_OK) return 0;
+        const int64_t n_tiles = ((M + plan.tile_m - 1) / plan.tile_m) * ((N + plan.tile_n - 1) / plan.tile_n);
+        const TailSplit t = make_tail_split(1, n_tiles, plan.grid / plan.cta_group, (K + plan.seg_k - 1) / plan.seg_k, plan.split_k);
+        if (t.s > 1) return static_cast<int64_t>(t.s) * t.r * plan.tile_m * plan.tile_n * static_cast<int64_t>(sizeof(float));
+    }
+    return 0;
 }
 
 int b200_gemm_f16(const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M, int64_t N,

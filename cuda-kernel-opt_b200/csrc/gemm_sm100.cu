@@ -39,6 +39,7 @@ constexpr int kMaxThreads = 544;  // (8 producer + 1 MMA + 8 epilogue warps) * 3
 
 struct Unit {
     int m0, n0, slice, seg_begin, seg_end;
+    int tail_idx;  // >= 0: a K slice of tail tile tail_idx, written to the workspace; -1: not a tail unit
 };
 
 // Launch constants the role loops need, copied once from the kernel parameter into registers.
@@ -47,6 +48,7 @@ struct Unit {
 // those loads sat on the critical path of the single-thread producer and MMA loops.
 struct Cfg {
     int num_units, num_tiles, tiles_m, tiles_n, tile_group_m, tile_m, tile_n, num_segs, split_k;
+    int tail_full, tail_r, tail_s;
     int kblocks, stages, stage_bytes, a_stage_bytes, cta_rows_a;
     int a_box_rows, a_boxes, a_priv, a_bars, chunk_n, b_priv, b_res_chunks, b_bars;
     int acc_cols, mma_m, epi_mode, epi_warps, M, N;
@@ -59,16 +61,28 @@ struct Cfg {
 // a group so concurrently running CTAs share B^T column panels in L2; the last group may be short.
 __device__ __forceinline__ Unit decode_unit(const Cfg &c, int u) {
     Unit w;
-    const int t = u % c.num_tiles;
-    w.slice = u / c.num_tiles;
+    int t, slices;
+    if (c.tail_s > 1 && u >= c.tail_full) {
+        // last wave: tail tile (u - full) mod r, K slice (u - full) / r
+        const int tl = u - c.tail_full;
+        w.tail_idx = tl % c.tail_r;
+        t = c.tail_full + w.tail_idx;
+        w.slice = tl / c.tail_r;
+        slices = c.tail_s;
+    } else {
+        w.tail_idx = -1;
+        t = u % c.num_tiles;
+        w.slice = u / c.num_tiles;
+        slices = c.split_k;
+    }
     const int group_tile_count = c.tile_group_m * c.tiles_n;
     const int group_first_row = (t / group_tile_count) * c.tile_group_m;
     const int group_rows = min(c.tiles_m - group_first_row, c.tile_group_m);
     const int in_group = t % group_tile_count;
     w.m0 = (group_first_row + in_group % group_rows) * c.tile_m;
     w.n0 = (in_group / group_rows) * c.tile_n;
-    w.seg_begin = static_cast<int>(static_cast<long long>(w.slice) * c.num_segs / c.split_k);
-    w.seg_end = static_cast<int>(static_cast<long long>(w.slice + 1) * c.num_segs / c.split_k);
+    w.seg_begin = static_cast<int>(static_cast<long long>(w.slice) * c.num_segs / slices);
+    w.seg_end = static_cast<int>(static_cast<long long>(w.slice + 1) * c.num_segs / slices);
     return w;
 }
 
@@ -136,7 +150,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     Cfg c;
     c.num_units = g.num_units; c.num_tiles = g.num_tiles; c.tiles_m = g.tiles_m; c.tiles_n = g.tiles_n;
     c.tile_group_m = g.tile_group_m; c.tile_m = g.tile_m; c.tile_n = g.tile_n; c.num_segs = g.num_segs;
-    c.split_k = g.split_k; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
+    c.split_k = g.split_k; c.tail_full = g.tail_full; c.tail_r = g.tail_r; c.tail_s = g.tail_s; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
     c.a_stage_bytes = g.a_stage_bytes; c.cta_rows_a = g.cta_rows_a; c.a_box_rows = g.a_box_rows;
     c.a_boxes = g.a_boxes; c.a_priv = g.a_priv; c.a_bars = g.a_bars; c.chunk_n = g.chunk_n; c.b_priv = g.b_priv;
     c.b_res_chunks = g.b_res_chunks; c.b_bars = g.b_bars; c.acc_cols = g.acc_cols; c.mma_m = g.mma_m;
@@ -620,6 +634,14 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 out = g.push_slot[owner];
                 row_off = (static_cast<size_t>(push_rank) * push_rows + static_cast<size_t>(row - owner * push_rows)) * c.N + w.n0;
             }
+            const bool tail = w.tail_idx >= 0;
+            if (tail) {
+                // a K slice of a tail tile: raw accumulator into the workspace, tile-local layout
+                out = g_partial;
+                row_off = (static_cast<size_t>(w.slice * c.tail_r + w.tail_idx) * c.tile_m + static_cast<size_t>(row - w.m0)) * c.tile_n;
+            }
+            const float a_u = tail ? 1.0f : alpha;
+            const float b_u = tail ? 0.0f : beta;
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                 if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
@@ -637,7 +659,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 }
                 tmem_ld_wait();
                 const int nvec = wide ? 8 : 4;
-                if (c.epi_mode == 0 || !wide) {
+                if (c.epi_mode == 0 || !wide || tail) {
                     if (row_ok) {
                         float4 *dst = reinterpret_cast<float4 *>(out + row_off + c0);
                         const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
@@ -645,16 +667,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         for (int j = 0; j < 8; ++j) {
                             if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
                                 float4 v;
-                                v.x = alpha * __uint_as_float(r[4 * j + 0]);
-                                v.y = alpha * __uint_as_float(r[4 * j + 1]);
-                                v.z = alpha * __uint_as_float(r[4 * j + 2]);
-                                v.w = alpha * __uint_as_float(r[4 * j + 3]);
-                                if (beta != 0.0f) {
+                                v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                                v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                                v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                                v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                                if (b_u != 0.0f) {
                                     const float4 cv = __ldg(csrc + j);
-                                    v.x += beta * cv.x;
-                                    v.y += beta * cv.y;
-                                    v.z += beta * cv.z;
-                                    v.w += beta * cv.w;
+                                    v.x += b_u * cv.x;
+                                    v.y += b_u * cv.y;
+                                    v.z += b_u * cv.z;
+                                    v.w += b_u * cv.w;
                                 }
                                 dst[j] = v;
                             }
@@ -669,16 +691,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         float4 v;
-                        v.x = alpha * __uint_as_float(r[4 * j + 0]);
-                        v.y = alpha * __uint_as_float(r[4 * j + 1]);
-                        v.z = alpha * __uint_as_float(r[4 * j + 2]);
-                        v.w = alpha * __uint_as_float(r[4 * j + 3]);
-                        if (beta != 0.0f && row_ok && w.n0 + c0 + 4 * j < c.N) {
+                        v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                        v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                        v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                        v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                        if (b_u != 0.0f && row_ok && w.n0 + c0 + 4 * j < c.N) {
                             const float4 cv = __ldg(csrc + j);
-                            v.x += beta * cv.x;
-                            v.y += beta * cv.y;
-                            v.z += beta * cv.z;
-                            v.w += beta * cv.w;
+                            v.x += b_u * cv.x;
+                            v.y += b_u * cv.y;
+                            v.z += b_u * cv.z;
+                            v.w += b_u * cv.w;
                         }
                         const uint32_t addr = buf + static_cast<uint32_t>(lane) * 128u + static_cast<uint32_t>((j ^ (lane & 7)) * 16);
                         asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
@@ -885,6 +907,81 @@ int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int sp
     if (blocks < 1) blocks = 1;
     splitk_reduce_push_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4 *>(partial), n4, split_k,
                                                           static_cast<int>(n / 4), d);
+    return static_cast<int>(cudaGetLastError());
+}
+
+// Second step of the tail split. One block column per tail tile; the tile's position comes from
+// the same grouped order as decode_unit. Slices are summed in ascending order.
+struct TailReduceArgs {
+    const float *partial;
+    const float *C;
+    float *D;
+    float alpha, beta;
+    int M, N, tile_m, tile_n, tiles_m, tiles_n, tile_group_m, full, r, s;
+};
+
+__global__ void tail_reduce_kernel(const __grid_constant__ TailReduceArgs a) {
+    const int idx = blockIdx.y;  // tail tile
+    const int t = a.full + idx;
+    const int group_tile_count = a.tile_group_m * a.tiles_n;
+    const int group_first_row = (t / group_tile_count) * a.tile_group_m;
+    const int group_rows = min(a.tiles_m - group_first_row, a.tile_group_m);
+    const int in_group = t % group_tile_count;
+    const int m0 = (group_first_row + in_group % group_rows) * a.tile_m;
+    const int n0 = (in_group / group_rows) * a.tile_n;
+    const int n4 = a.tile_n / 4;
+    const long long tile_elems4 = static_cast<long long>(a.tile_m) * n4;
+    const float4 *p4 = reinterpret_cast<const float4 *>(a.partial);
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < tile_elems4;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = m0 + static_cast<int>(i / n4);
+        const int col = n0 + static_cast<int>(i % n4) * 4;
+        if (row >= a.M || col >= a.N) continue;
+        float4 sum = p4[static_cast<long long>(idx) * tile_elems4 + i];
+        for (int k = 1; k < a.s; ++k) {
+            const float4 v = p4[(static_cast<long long>(k) * a.r + idx) * tile_elems4 + i];
+            sum.x += v.x;
+            sum.y += v.y;
+            sum.z += v.z;
+            sum.w += v.w;
+        }
+        const size_t o = static_cast<size_t>(row) * a.N + col;
+        float4 out;
+        out.x = a.alpha * sum.x;
+        out.y = a.alpha * sum.y;
+        out.z = a.alpha * sum.z;
+        out.w = a.alpha * sum.w;
+        if (a.beta != 0.0f) {
+            const float4 c = *reinterpret_cast<const float4 *>(a.C + o);
+            out.x += a.beta * c.x;
+            out.y += a.beta * c.y;
+            out.z += a.beta * c.z;
+            out.w += a.beta * c.w;
+        }
+        *reinterpret_cast<float4 *>(a.D + o) = out;
+    }
+}
+
+int launch_tail_reduce(const GemmArgs &g, cudaStream_t stream) {
+    TailReduceArgs a;
+    a.partial = g.partial;
+    a.C = g.C;
+    a.D = g.D;
+    a.alpha = g.alpha;
+    a.beta = g.beta;
+    a.M = g.M;
+    a.N = g.N;
+    a.tile_m = g.tile_m;
+    a.tile_n = g.tile_n;
+    a.tiles_m = g.tiles_m;
+    a.tiles_n = g.tiles_n;
+    a.tile_group_m = g.tile_group_m;
+    a.full = g.tail_full;
+    a.r = g.tail_r;
+    a.s = g.tail_s;
+    const int per_tile = (g.tile_m * g.tile_n / 4 + 255) / 256;
+    dim3 grid(static_cast<unsigned>(per_tile < 16 ? per_tile : 16), static_cast<unsigned>(g.tail_r), 1);
+    tail_reduce_kernel<<<grid, 256, 0, stream>>>(a);
     return static_cast<int>(cudaGetLastError());
 }
 

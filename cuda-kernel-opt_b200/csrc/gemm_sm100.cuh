@@ -21,6 +21,7 @@ struct alignas(64) GemmArgs {
     int tiles_m, tiles_n, num_tiles, num_units;
     int num_segs;       // K / seg_k
     int split_k;
+    int tail_full, tail_r, tail_s;  // tail split (plan.h): whole tiles, tiles of the last wave, K slices each
     // plan
     int tile_m, tile_n, cta_rows_a, mma_m;
     int kblocks, stages, tile_group_m;
@@ -60,6 +61,8 @@ int launch_push_reduce(const float *slots, const int *flags, int world, int epoc
 // Second step of split-K when the rows go to their owner GPUs instead of a local D.
 int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int split_k, float *const *slots, int *const *flags,
                               unsigned int *done, int world, int rank, int epoch, cudaStream_t stream);
+// Second step of the tail split: D tile = alpha * sum of its K slices + beta * C for the r tail tiles.
+int launch_tail_reduce(const GemmArgs &args, cudaStream_t stream);
 int prepare_kernels();  // opt-in shared memory size; once per device
 
 }  // namespace b200

@@ -50,6 +50,31 @@ struct Plan {
     int grid = 0;
 };
 
+// Tail split: with T tiles on S slots (CTAs or CTA pairs) the last wave holds r = T mod S tiles.
+// If r <= S / 2 each of them is cut into s = floor(S / r) K slices so the wave takes 1/s of a tile
+// time; the slices meet in the workspace. s == 1 means "not worth it / off".
+struct TailSplit {
+    int full = 0;    // tiles processed whole (a multiple of S)
+    int r = 0;       // tiles of the last wave
+    int s = 1;       // K slices per tail tile
+};
+
+inline TailSplit make_tail_split(int enabled, int64_t tiles, int slots, int64_t num_segs, int split_k) {
+    TailSplit t;
+    t.full = static_cast<int>(tiles);
+    if (!enabled || split_k > 1 || slots < 1 || tiles <= 0) return t;
+    const int r = static_cast<int>(tiles % slots);
+    if (r == 0) return t;
+    int s = slots / r;
+    if (s > 8) s = 8;
+    if (s > num_segs) s = static_cast<int>(num_segs);
+    if (s < 2) return t;
+    t.full = static_cast<int>(tiles - r);
+    t.r = r;
+    t.s = s;
+    return t;
+}
+
 inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 inline int pow2_at_least(int x) {

@@ -126,6 +126,19 @@ def test_b200_extensions(pkg):
     assert pkg.workspace_bytes(512, 256, 4096, P(pkg)) == 0
 
 
+def test_tail_split_planning(pkg):
+    """Tiles mod slots decides: 4096^3 in 256x256 pair tiles is 256 tiles on 74 pairs = 3 waves + 34,
+    so each of the 34 is cut in 2; 8192^3 leaves 62 of 74 (no gain); a full wave leaves nothing."""
+    pair = dict(tile_m=256, tile_n=256, cta_group=2, bar_step_rows_a=256, bar_step_rows_b=256, num_stages=6, tail_split=1)
+    assert pkg.workspace_bytes(4096, 4096, 4096, P(pkg, **pair)) == 2 * 34 * 256 * 256 * 4
+    assert pkg.workspace_bytes(8192, 8192, 8192, P(pkg, **pair)) == 0
+    assert pkg.workspace_bytes(256 * 74, 256, 4096, P(pkg, **pair)) == 0
+    assert pkg.workspace_bytes(4096, 4096, 4096, P(pkg, **dict(pair, tail_split=0))) == 0
+    one = dict(tile_m=128, tile_n=128, tail_split=1)
+    assert pkg.workspace_bytes(128 * 3, 128 * 50, 64, P(pkg, **one)) == 0        # one K segment cannot be split
+    assert pkg.workspace_bytes(128 * 3, 128 * 50, 1024, P(pkg, **one)) == 8 * 2 * 128 * 128 * 4   # 150 tiles on 148: 2 left, 8 slices each (the cap)
+
+
 def test_default_params_are_valid(pkg):
     for (m, n, k) in ((1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (16, 28672, 8192), (2048, 2048, 262144)):
         for dt in (pkg.F16, pkg.BF16):

@@ -174,6 +174,26 @@ def test_split_k(pkg, cuda, oracle):
     assert st == pkg.WORKSPACE_TOO_SMALL
 
 
+def test_tail_split(pkg, cuda, oracle):
+    """Tiles of a partly filled last wave are cut along K over the idle CTAs (workspace + second kernel)."""
+    sms = pkg.num_sms()
+    cases = [  # m, n, k, overrides: 1-CTA tiles so that (tiles mod SMs) is small but not zero
+        (128 * 10, 128 * (sms // 10 + 2), 1024, dict(tile_m=128, tile_n=128)),
+        (256 * 5, 256 * (sms // 10 + 1), 2048, dict(tile_m=256, tile_n=256, cta_group=2)),
+        (200, 128 * (sms + 3), 512, dict(tile_m=128, tile_n=128, segment_dim_k=128, num_stages=3)),
+    ]
+    for m, n, k, ov in cases:
+        p = pkg.default_params(m, n, k, pkg.F16, tail_split=1, **ov)
+        assert pkg.workspace_bytes(m, n, k, p) > 0, (m, n, k)          # the case really has a tail to split
+        A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 190 + m)
+        got = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.5, 1.0, tail_split=1, **ov)
+        want = oracle.gemm(A, Bt, Cm, 1.5, 1.0)
+        ok, msg = tolerance_ok(got, want, k, 3.0)
+        assert ok, (m, n, k, msg)
+    # a full last wave, or a tail too large to gain, needs no workspace and takes the normal path
+    assert pkg.workspace_bytes(128 * sms, 128, 512, pkg.default_params(128 * sms, 128, 512, pkg.F16, tile_m=128, tile_n=128, tail_split=1)) == 0
+
+
 def test_error_statuses_on_device_calls(pkg, cuda):
     dA = cuda.zeros((128, 64), dtype=cuda.float16, device="cuda")
     D = cuda.zeros((128, 128), dtype=cuda.float32, device="cuda")
