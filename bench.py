@@ -387,7 +387,7 @@ def run_ours(args):
         same = bool(torch.equal(hD.to(dev), D)) if p.split_k == 1 else None
         e2e = {"value": ev_, "unit": unit, "h2d_bytes_per_step": int(2 * (m_loc * k_loc + n_loc * k_loc)),
                "d2h_bytes_per_step": int(4 * m_loc * n_loc), "steps": e_steps, "ms_per_step": dt * 1e3,
-               "call": "b200_session_gemm_host (pinned host A, B^T -> device, GEMM, D -> pinned host, synchronised; row blocks pipelined over three streams)",
+               "call": "b200_session_gemm_host (pinned host A, B^T -> device, GEMM, D -> pinned host, synchronised; a 4 x 4 grid of D blocks pipelined over upload / compute / download streams)",
                "result_equals_device_run": same}
         sess.close()
         del hA, hB, hD

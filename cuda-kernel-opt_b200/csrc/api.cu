@@ -88,9 +88,9 @@ int device_info(const DeviceInfo **out) {
 }
 
 int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const void *ptr, uint64_t inner,
-              uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+              uint64_t outer, uint32_t box_inner, uint32_t box_outer, uint64_t pitch_elems = 0) {
     const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {inner * static_cast<uint64_t>(elem_bytes)};
+    const cuuint64_t strides[1] = {(pitch_elems ? pitch_elems : inner) * static_cast<uint64_t>(elem_bytes)};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = g_encode(map, type, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -167,7 +167,7 @@ struct PushTarget {  // split-K over GPUs with the exchange fused into the epilo
 
 int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M,
               int64_t N, int64_t K, const b200_gemm_params *user, void *workspace, size_t workspace_bytes,
-              cudaStream_t stream, const PushTarget *push = nullptr) {
+              cudaStream_t stream, const PushTarget *push = nullptr, int64_t ld_cd = 0) {
     if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
     b200_gemm_params local;
     if (!user) {
@@ -203,6 +203,8 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
         if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
     }
+    if (ld_cd && ld_cd != N && (p.split_k > 1 || tail.s > 1 || (push && push->world > 0) || ld_cd < N || ld_cd % 4))
+        return B200_INVALID_CONFIG;  // the second-step kernels assume a dense D
     if (p.split_k > 1) {
         const size_t need = static_cast<size_t>(p.split_k) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
         if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
@@ -222,7 +224,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if (p.mma_m != 128 || p.split_k > 1 || pushing) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
     if (epi_mode) {
         st = encode_2d(&a.map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
-                       kEpiBoxCols, 32);
+                       kEpiBoxCols, 32, static_cast<uint64_t>(ld_cd));
         if (st != B200_OK) return st;
     }
     a.C = C;
@@ -233,6 +235,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.M = static_cast<int>(M);
     a.N = static_cast<int>(N);
     a.K = static_cast<int>(K);
+    a.ld_cd = static_cast<int>(ld_cd ? ld_cd : N);
     a.tiles_m = static_cast<int>((M + p.tile_m - 1) / p.tile_m);
     a.tiles_n = static_cast<int>((N + p.tile_n - 1) / p.tile_n);
     a.num_tiles = a.tiles_m * a.tiles_n;
@@ -505,53 +508,73 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
     if (!s || !hA || !hBt || !hD) return B200_INVALID_POINTER;
     if (M > s->max_m || N > s->max_n || K > s->max_k) return B200_INVALID_SHAPE;
     if (beta != 0.0f && !hC) return B200_INVALID_POINTER;
-    // Row blocks of A / C / D are pipelined over three streams: while block i is multiplied, block
-    // i+1 is uploaded and block i-1 is downloaded (the two copy directions use different engines).
-    // B^T goes first, every block needs it. Block boundaries fall on tile rows, so the result is
-    // bit-identical to one launch over the whole problem.
+    // D is computed in a grid of up to 4 x 4 blocks, pipelined over three streams: A row blocks and
+    // B^T row panels are uploaded alternately, a block (i, j) is multiplied as soon as A_i and B_j
+    // are on the device, and its result is downloaded while later uploads and products run (the
+    // two copy directions use different engines). Block edges fall on tile edges, so the result
+    // is bit-identical to one launch over the whole problem.
     b200_gemm_params local;
     if (!p) {
         default_params(M, N, K, &local);
         p = &local;
     }
-    const int64_t tile_m = p->tile_m > 0 ? p->tile_m : 128;
-    int64_t block_rows = ((M + 7) / 8 + tile_m - 1) / tile_m * tile_m;
-    if (block_rows < 2 * tile_m) block_rows = 2 * tile_m;
-    int blocks = static_cast<int>((M + block_rows - 1) / block_rows);
-    if (blocks > 16) {
-        block_rows = ((M + 15) / 16 + tile_m - 1) / tile_m * tile_m;
-        blocks = static_cast<int>((M + block_rows - 1) / block_rows);
-    }
-    const char *hA8 = static_cast<const char *>(hA);
-    char *dA8 = static_cast<char *>(s->dA);
-    cudaError_t e = cudaMemcpyAsync(s->dB, hBt, static_cast<size_t>(N) * K * 2, cudaMemcpyHostToDevice, s->stream);
-    if (e == cudaSuccess) e = cudaEventRecord(s->b_ready, s->stream);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(s->compute, s->b_ready, 0);
-    if (e != cudaSuccess) return fail_cuda(e);
-    for (int b = 0; b < blocks; ++b) {
-        const int64_t r0 = b * block_rows;
-        const int64_t rows = (M - r0 < block_rows) ? (M - r0) : block_rows;
-        e = cudaMemcpyAsync(dA8 + static_cast<size_t>(r0) * K * 2, hA8 + static_cast<size_t>(r0) * K * 2,
-                            static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, s->stream);
-        if (e == cudaSuccess && beta != 0.0f)
-            e = cudaMemcpyAsync(s->dC + static_cast<size_t>(r0) * N, hC + static_cast<size_t>(r0) * N,
-                                static_cast<size_t>(rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
-        if (e == cudaSuccess) e = cudaEventRecord(s->up[b], s->stream);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->compute, s->up[b], 0);
-        if (e != cudaSuccess) return fail_cuda(e);
-        const int st = gemm_impl(dtype, dA8 + static_cast<size_t>(r0) * K * 2, s->dB,
-                                 beta != 0.0f ? s->dC + static_cast<size_t>(r0) * N : nullptr, s->dD + static_cast<size_t>(r0) * N,
-                                 alpha, beta, rows, N, K, p, nullptr, 0, s->compute);
-        if (st != B200_OK) {
-            cudaDeviceSynchronize();
-            return st;
+    const int64_t tile_m = p->tile_m > 0 ? p->tile_m : 128, tile_n = p->tile_n > 0 ? p->tile_n : 128;
+    auto block_of = [](int64_t extent, int64_t tile, int parts) {
+        int64_t b = ((extent + parts - 1) / parts + tile - 1) / tile * tile;
+        if (b < 2 * tile) b = 2 * tile;
+        return b;
+    };
+    const int64_t brows = block_of(M, tile_m, 4), bcols = block_of(N, tile_n, 4);
+    const int R = static_cast<int>((M + brows - 1) / brows), Cn = static_cast<int>((N + bcols - 1) / bcols);
+    const char *hA8 = static_cast<const char *>(hA), *hB8 = static_cast<const char *>(hBt);
+    char *dA8 = static_cast<char *>(s->dA), *dB8 = static_cast<char *>(s->dB);
+    cudaError_t e = cudaSuccess;
+    int block_id = 0;
+    const int steps = R > Cn ? R : Cn;
+    for (int t = 0; t < steps; ++t) {
+        if (t < R) {
+            const int64_t r0 = t * brows, rows = (M - r0 < brows) ? (M - r0) : brows;
+            e = cudaMemcpyAsync(dA8 + static_cast<size_t>(r0) * K * 2, hA8 + static_cast<size_t>(r0) * K * 2,
+                                static_cast<size_t>(rows) * K * 2, cudaMemcpyHostToDevice, s->stream);
+            if (e == cudaSuccess && beta != 0.0f)
+                e = cudaMemcpyAsync(s->dC + static_cast<size_t>(r0) * N, hC + static_cast<size_t>(r0) * N,
+                                    static_cast<size_t>(rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
+            if (e != cudaSuccess) return fail_cuda(e);
         }
-        e = cudaEventRecord(s->done[b], s->compute);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[b], 0);
-        if (e == cudaSuccess)
-            e = cudaMemcpyAsync(hD + static_cast<size_t>(r0) * N, s->dD + static_cast<size_t>(r0) * N,
-                                static_cast<size_t>(rows) * N * 4, cudaMemcpyDeviceToHost, s->download);
+        if (t < Cn) {
+            const int64_t c0 = t * bcols, cols = (N - c0 < bcols) ? (N - c0) : bcols;
+            e = cudaMemcpyAsync(dB8 + static_cast<size_t>(c0) * K * 2, hB8 + static_cast<size_t>(c0) * K * 2,
+                                static_cast<size_t>(cols) * K * 2, cudaMemcpyHostToDevice, s->stream);
+            if (e != cudaSuccess) return fail_cuda(e);
+        }
+        e = cudaEventRecord(s->up[t], s->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->compute, s->up[t], 0);
         if (e != cudaSuccess) return fail_cuda(e);
+        // blocks that became computable with this step: row t with columns 0..min(t, Cn-1), column t with rows 0..t-1
+        for (int pass = 0; pass < 2; ++pass) {
+            const int count = pass == 0 ? ((t < R) ? ((t < Cn ? t : Cn - 1) + 1) : 0) : ((t < Cn) ? (t < R ? t : R) : 0);
+            for (int q = 0; q < count; ++q) {
+                const int bi = pass == 0 ? t : q, bj = pass == 0 ? q : t;
+                const int64_t r0 = bi * brows, rows = (M - r0 < brows) ? (M - r0) : brows;
+                const int64_t c0 = bj * bcols, cols = (N - c0 < bcols) ? (N - c0) : bcols;
+                const size_t off = static_cast<size_t>(r0) * N + c0;
+                const int st = gemm_impl(dtype, dA8 + static_cast<size_t>(r0) * K * 2, dB8 + static_cast<size_t>(c0) * K * 2,
+                                         beta != 0.0f ? s->dC + off : nullptr, s->dD + off, alpha, beta, rows, cols, K, p, nullptr,
+                                         0, s->compute, nullptr, N);
+                if (st != B200_OK) {
+                    cudaDeviceSynchronize();
+                    return st;
+                }
+                e = cudaEventRecord(s->done[block_id], s->compute);
+                if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[block_id], 0);
+                if (e == cudaSuccess)
+                    e = cudaMemcpy2DAsync(hD + off, static_cast<size_t>(N) * 4, s->dD + off, static_cast<size_t>(N) * 4,
+                                          static_cast<size_t>(cols) * 4, static_cast<size_t>(rows), cudaMemcpyDeviceToHost,
+                                          s->download);
+                if (e != cudaSuccess) return fail_cuda(e);
+                ++block_id;
+            }
+        }
     }
     e = cudaStreamSynchronize(s->download);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);

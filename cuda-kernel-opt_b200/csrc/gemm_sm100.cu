@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int tmem_cols = g.tmem_cols;
     const int P = g.producer_warps;
     const int push_world = g.push_world, push_rank = g.push_rank, push_rows = g.push_rows;
+    const int ld_cd = g.ld_cd;
     const int dbg = g.debug_flags;  // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage)
     const float g_alpha = g.alpha, g_beta = g.beta;
     const float *const gC = g.C;
@@ -626,7 +627,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const int row = w.m0 + static_cast<int>(rank) * c.cta_rows_a + row_in_cta;
             const bool row_ok = lane_has_row && row < c.M;
             float *out = to_partial ? g_partial + static_cast<size_t>(w.slice) * c.M * c.N : gD;
-            size_t row_off = static_cast<size_t>(row) * c.N + w.n0;
+            size_t row_off = static_cast<size_t>(row) * (to_partial ? c.N : ld_cd) + w.n0;
             if (push_world > 0) {
                 // the 128 rows this CTA drains belong to one owner (rows per owner is a multiple of 128)
                 const int cta_row0 = w.m0 + static_cast<int>(rank) * c.cta_rows_a;

@@ -18,6 +18,7 @@ struct alignas(64) GemmArgs {
     float *partial;     // split-K workspace: split_k slabs of M x N fp32
     float alpha, beta;
     int M, N, K;
+    int ld_cd;          // row pitch of C and D in elements (N unless D is a column block of a wider matrix)
     int tiles_m, tiles_n, num_tiles, num_units;
     int num_segs;       // K / seg_k
     int split_k;
