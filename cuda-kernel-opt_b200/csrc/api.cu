@@ -290,6 +290,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.prof_blocks = g_prof_blocks.load();
     a.debug_flags = user->diagnostic;
     a.l2_hint = user->l2_hint;
+    a.k_order = user->k_order;
 
     const int le = launch_gemm(p, a, stream);
     if (le != 0) return fail_cuda(static_cast<cudaError_t>(le));

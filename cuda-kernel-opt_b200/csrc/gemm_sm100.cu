@@ -259,13 +259,22 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             uint32_t ph = 0, it = 0;
             uint32_t stage = base, sb = bars, sbl = bars_leader;
             bool ok = true;
+            int tile_no = 0;
+            const bool k_serpentine = g.k_order == 1;
             long long t_wait = 0;
             const long long t_begin = PROF ? clock64() : 0;
             for (int u = group; ok && u < c.num_units; u += num_groups) {
                 const Unit w = decode_unit(c, u);
                 const int a_row = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
                 const int b_row = w.n0 + static_cast<int>(rank) * (c.tile_n / CG);
-                int k = w.seg_begin * c.kblocks * kBoxK;
+                // Serpentine K: every other tile of this CTA walks its K segments downwards, so the
+                // operand panels a wave touched last are the first the next wave asks for (they are
+                // still in L2). The MMA warp is indifferent: it sums whatever the stages bring.
+                const int seg_k_elems = c.kblocks * kBoxK;
+                const bool down = k_serpentine && (tile_no & 1);
+                int k = (down ? w.seg_end - 1 : w.seg_begin) * seg_k_elems;
+                const int k_next = down ? -2 * seg_k_elems : 0;   // after a segment k has advanced by one segment
+                ++tile_no;
                 for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
                     const long long tw = PROF ? clock64() : 0;
                     ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
@@ -286,6 +295,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         k += kBoxK;
                     }
                     ++it;
+                    k += k_next;
                     stage += static_cast<uint32_t>(c.stage_bytes);
                     sb += stage_bar_bytes;
                     sbl += stage_bar_bytes;

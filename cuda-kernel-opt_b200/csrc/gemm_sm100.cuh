@@ -39,6 +39,7 @@ struct alignas(64) GemmArgs {
     int prof_blocks;
     int debug_flags;
     int l2_hint;
+    int k_order;
     // split-K across GPUs with the reduce-scatter fused into the epilogue ("push" mode, world > 0):
     // the fp32 tile rows owned by GPU o are stored straight into o's slot area over NVLink
     // (plain peer stores), slot [source rank][rows per owner][N]; the last CTA to finish raises

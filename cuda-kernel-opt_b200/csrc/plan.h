@@ -119,6 +119,7 @@ inline Plan make_plan(const b200_gemm_params &q, int num_sms_device) {
     p.split_k = q.split_k == 0 ? 1 : q.split_k;
     if (q.epilogue != 0 && q.epilogue != 1) return p;
     if (q.l2_hint < 0 || q.l2_hint > 3) return p;
+    if (q.k_order != 0 && q.k_order != 1) return p;
     p.epi_mode = q.epilogue;
 
     // Sub-tile split of the A stage buffer (rows per barrier step). 0 or the full extent = off.

@@ -78,6 +78,9 @@ typedef struct b200_gemm_params {
                       2 = A evict_last, 3 = both evict_last */
     int diagnostic; /* must be 0. Bit 0 issues no MMA, bit 1 no operand load: pipeline ceilings for
                        profiling; the output is garbage */
+    int k_order;    /* 0 = every tile sums K ascending; 1 = serpentine: every other tile of a CTA walks K downwards,
+                       so consecutive waves meet their shared operand panels while they are still in L2.
+                       Changes the fp32 summation order of those tiles (not the tolerance) */
     int tail_split; /* 1 = when the tiles do not fill the last wave of the persistent grid, split the tiles of
                        that wave along K over the idle CTAs (partials in the workspace, summed by a small
                        second kernel): needs b200_gemm_workspace_bytes of workspace. 0 = off */
