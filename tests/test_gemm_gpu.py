@@ -124,6 +124,51 @@ def test_tunable_sweep(pkg, cuda, oracle, cfg):
     assert ok, (m, n, k, msg)
 
 
+def test_randomised_shapes_and_tunables(pkg, cuda, oracle):
+    """Seeded random walk over everything the C ABI accepts: ragged shapes, both tile families, sub-tile
+    barriers, split-K, tail split, both epilogues, L2 hints, K order, partial grids."""
+    import random
+    rnd = random.Random(20240229)
+    ran = 0
+    for it in range(400):
+        if ran >= 80:
+            break
+        cg = rnd.choice([1, 1, 2])
+        tile_m = 256 if cg == 2 else rnd.choice([128, 128, 64])
+        tile_n = rnd.choice([32, 64, 96, 128, 192, 256]) if cg == 2 else rnd.choice([16, 48, 64, 112, 128, 224, 256])
+        ov = dict(tile_m=tile_m, tile_n=tile_n, cta_group=cg, segment_dim_k=rnd.choice([64, 64, 128, 256]), num_stages=rnd.randint(1, 8),
+                  tile_group_m=rnd.randint(1, 9), num_producer_warps=rnd.choice([1, 2, 4, 8]), num_consumer_warps=rnd.choice([4, 8]),
+                  epilogue=rnd.choice([0, 1]), l2_hint=rnd.randint(0, 3), k_order=rnd.choice([0, 1]), num_sms=rnd.choice([0, 0, 37 * cg, 10 * cg]))
+        mode = rnd.random()
+        if mode < 0.35:
+            steps = [s_ for s_ in (16 * cg, 32 * cg, 64, 128) if tile_n % s_ == 0 and tile_n // s_ <= 16]
+            step_b = rnd.choice(steps or [tile_n])
+            ov.update(bar_step_rows_b=step_b, bar_steps_b=rnd.randint(0, tile_n // step_b))
+            if rnd.random() < 0.5:
+                rows = tile_m // cg
+                step_a = rnd.choice([s_ for s_ in (16, 32, 64) if rows % s_ == 0])
+                ov.update(bar_step_rows_a=step_a, bar_steps_a=rnd.randint(0, rows // step_a))
+        elif mode < 0.5:
+            ov["split_k"] = rnd.randint(2, 6)
+        elif mode < 0.6:
+            ov["tail_split"] = 1
+        dtype = rnd.choice([pkg.F16, pkg.BF16])
+        m = rnd.choice([1, 16, 100, 128, 200, 256, 384, 520, 1024])
+        n = 4 * rnd.randint(4, 300)
+        k = 8 * rnd.randint(1, 160)
+        alpha, beta = rnd.choice([(1.0, 0.0), (1.0, 1.0), (0.5, -2.0)])
+        p = pkg.default_params(m, n, k, dtype, **ov)
+        if pkg.validate(m, n, k, dtype, p) != pkg.OK:
+            continue
+        ran += 1
+        A, Bt, Cm = inputs(pkg, dtype, m, n, k, 1000 + it)
+        got = run_gemm(pkg, cuda, dtype, A, Bt, Cm, alpha, beta, **ov)
+        want = oracle.gemm(A, Bt, Cm if beta else None, alpha, beta, dtype)
+        ok, msg = tolerance_ok(got, want, k, abs(alpha) + abs(beta) + 1.0)
+        assert ok, (m, n, k, dtype, alpha, beta, p.as_dict(), msg)
+    assert ran >= 60
+
+
 def test_bf16_and_scalars(pkg, cuda, oracle):
     A, Bt, Cm = inputs(pkg, pkg.BF16, 384, 512, 768, 61)
     for alpha, beta in ((1.0, 0.0), (0.5, 2.0), (-1.25, 0.75), (0.0, 1.0)):
