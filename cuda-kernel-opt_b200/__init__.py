@@ -37,7 +37,7 @@ class Params(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "tile_m", "tile_n", "segment_dim_k", "bar_steps_a", "bar_steps_b", "bar_step_rows_a", "bar_step_rows_b",
         "tile_group_m", "num_stages", "num_producer_warps", "num_consumer_warps", "num_sms", "cta_group", "split_k",
-        "epilogue", "l2_hint", "diagnostic", "k_order", "tail_split")]
+        "epilogue", "l2_hint", "diagnostic", "k_order", "tail_split", "swap_ab", "cluster_reduce")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
@@ -111,14 +111,23 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
     override itself asks for the two-CTA pair, so that a partial override stays a valid whole."""
     p = Params()
     tile_keys = {"tile_m", "tile_n", "cta_group"} & set(overrides)
-    want_pair = overrides.get("cta_group", 0) == 2 or overrides.get("tile_m", 0) == 256
-    st = lib().b200_gemm_default_params(M if (not tile_keys or want_pair) else min(M, 128), N, K, dtype, C.byref(p))
+    want_pair = overrides.get("cta_group", 0) == 2 or overrides.get("tile_m", 0) == 256 and not overrides.get("swap_ab")
+    want_swap = overrides.get("swap_ab")
+    if want_swap is None and (tile_keys or overrides.get("tail_split") or overrides.get("epilogue")):
+        want_swap = 0          # tile_m / tile_n change meaning with swap_ab: an override names the plain form
+    base_m = M if (not tile_keys or want_pair) else min(M, 128)
+    if want_swap == 0 and not want_pair:
+        base_m = max(base_m, 128) if M <= 128 else base_m   # the skinny default without swapped roles
+    st = lib().b200_gemm_default_params(base_m, N, K, dtype, C.byref(p))
     if st != OK:
         raise B200Error(st, "b200_gemm_default_params")
     if tile_keys and not want_pair and M > 128:
         p.l2_hint = 0          # the skinny-shape hint of the reduced-M base does not apply
     if want_pair and p.cta_group != 2:
         p.tile_m, p.tile_n, p.cta_group, p.num_stages, p.l2_hint = 256, 256, 2, 6, 3
+    if want_swap == 1 and not p.swap_ab:
+        p.tile_m, p.tile_n, p.cta_group, p.epilogue = min(256, -(-M // 16) * 16), 128, 1, 0
+        p.num_stages, p.num_producer_warps = 8, 1
     for k, v in overrides.items():
         if not hasattr(p, k):
             raise AttributeError(k)

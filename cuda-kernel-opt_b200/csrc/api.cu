@@ -108,8 +108,32 @@ int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const 
 // 128 x 256 tile); small or skinny ones a one-CTA tile with the widest N that divides.
 void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
     std::memset(p, 0, sizeof(*p));
-    (void)K;
     const bool pair = (M > 128) && (N % 256 == 0);
+    if (M <= 32) {
+        // Decode shapes: the weights are the whole traffic. Swapped roles stage 128 weight rows and
+        // only 16 or 32 activation rows per K block; 128-deep K segments halve the barrier round
+        // trips per byte. One SM sustains a few tens of GB/s of TMA loads at DRAM latency, so when
+        // there are few tiles their K range is split over a cluster to put more SMs to work.
+        p->swap_ab = 1;
+        p->tile_m = M <= 16 ? 16 : 32;
+        p->tile_n = 128;
+        p->cta_group = 1;
+        p->segment_dim_k = 128;
+        p->num_stages = 5;
+        p->num_producer_warps = 1;
+        p->l2_hint = 1;
+        p->bar_step_rows_a = p->tile_m;
+        p->bar_step_rows_b = p->tile_n;
+        p->tile_group_m = 8;
+        p->num_consumer_warps = 4;
+        p->split_k = 1;
+        const int64_t tiles = (N + 127) / 128;
+        if (K >= 4096 && tiles <= 74) {
+            p->split_k = tiles <= 37 ? 4 : 2;
+            p->cluster_reduce = 1;
+        }
+        return;
+    }
     if (pair) {
         p->tile_m = 256;
         p->tile_n = 256;
@@ -182,6 +206,12 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     st = check_shape(p, M, N, K);
     if (st != B200_OK) return st;
     const bool pushing = push && push->world > 0;
+    if (p.swap && pushing) return B200_INVALID_CONFIG;
+    // Swapped roles: the kernel sees the transposed problem (its M operand is B^T, its N operand A)
+    // and writes its accumulator transposed, so C and D keep their row-major m x n layout.
+    const int64_t kM = p.swap ? N : M, kN = p.swap ? M : N;
+    const void *const opA = p.swap ? Bt : A;
+    const void *const opB = p.swap ? A : Bt;
     if (pushing) {
         if (push->world > 8 || push->rank < 0 || push->rank >= push->world || !push->slots || !push->flags || !push->done)
             return B200_INVALID_CONFIG;
@@ -195,7 +225,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bt) | reinterpret_cast<uintptr_t>(D) |
          reinterpret_cast<uintptr_t>(C)) & 15u)
         return B200_INVALID_POINTER;
-    const int64_t n_tiles = ((M + p.tile_m - 1) / p.tile_m) * ((N + p.tile_n - 1) / p.tile_n);
+    const int64_t n_tiles = ((kM + p.tile_m - 1) / p.tile_m) * ((kN + p.tile_n - 1) / p.tile_n);
     const TailSplit tail = make_tail_split(user->tail_split && !(push && push->world > 0), n_tiles, p.grid / p.cta_group,
                                            (K + p.seg_k - 1) / p.seg_k, p.split_k);
     if (tail.s > 1) {
@@ -203,9 +233,10 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
         if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
     }
-    if (ld_cd && ld_cd != N && (p.split_k > 1 || tail.s > 1 || (push && push->world > 0) || ld_cd < N || ld_cd % 4))
+    const int ws_split = p.cluster_reduce ? 1 : p.split_k;  // K slices that meet in the workspace
+    if (ld_cd && ld_cd != N && (ws_split > 1 || tail.s > 1 || (push && push->world > 0) || ld_cd < N || ld_cd % 4))
         return B200_INVALID_CONFIG;  // the second-step kernels assume a dense D
-    if (p.split_k > 1) {
+    if (ws_split > 1) {
         const size_t need = static_cast<size_t>(p.split_k) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
         if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
@@ -214,14 +245,14 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     GemmArgs a;
     std::memset(&a, 0, sizeof(a));
     const CUtensorMapDataType in_type = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    st = encode_2d(&a.map_a, in_type, 2, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M), kBoxK,
+    st = encode_2d(&a.map_a, in_type, 2, opA, static_cast<uint64_t>(K), static_cast<uint64_t>(kM), kBoxK,
                    static_cast<uint32_t>(p.a_box_rows));
     if (st != B200_OK) return st;
-    st = encode_2d(&a.map_b, in_type, 2, Bt, static_cast<uint64_t>(K), static_cast<uint64_t>(N), kBoxK,
+    st = encode_2d(&a.map_b, in_type, 2, opB, static_cast<uint64_t>(K), static_cast<uint64_t>(kN), kBoxK,
                    static_cast<uint32_t>(p.chunk_n / p.cta_group));
     if (st != B200_OK) return st;
     int epi_mode = p.epi_mode;
-    if (p.mma_m != 128 || p.split_k > 1 || pushing) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
+    if (p.mma_m != 128 || ws_split > 1 || pushing) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
     if (epi_mode) {
         st = encode_2d(&a.map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
                        kEpiBoxCols, 32, static_cast<uint64_t>(ld_cd));
@@ -232,15 +263,17 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.partial = static_cast<float *>(workspace);
     a.alpha = alpha;
     a.beta = beta;
-    a.M = static_cast<int>(M);
-    a.N = static_cast<int>(N);
+    a.M = static_cast<int>(kM);
+    a.N = static_cast<int>(kN);
     a.K = static_cast<int>(K);
+    a.swap_ab = p.swap;
     a.ld_cd = static_cast<int>(ld_cd ? ld_cd : N);
-    a.tiles_m = static_cast<int>((M + p.tile_m - 1) / p.tile_m);
-    a.tiles_n = static_cast<int>((N + p.tile_n - 1) / p.tile_n);
+    a.tiles_m = static_cast<int>((kM + p.tile_m - 1) / p.tile_m);
+    a.tiles_n = static_cast<int>((kN + p.tile_n - 1) / p.tile_n);
     a.num_tiles = a.tiles_m * a.tiles_n;
-    a.split_k = p.split_k;
-    a.num_units = a.num_tiles * p.split_k;
+    a.split_k = ws_split;
+    a.cl_split = p.cluster_reduce ? p.split_k : 0;
+    a.num_units = a.num_tiles * ws_split;
     a.tail_full = tail.full;
     a.tail_r = tail.r;
     a.tail_s = tail.s;
@@ -275,7 +308,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.idesc_res = umma_idesc(p.tile_m, p.b_res_chunks * p.chunk_n, dtype == B200_BF16);
     a.wait_budget_cycles = static_cast<long long>(g_wait_budget_ns.load() * 2ull);  // SM clock is below 2 GHz
 
-    if (pushing && p.split_k == 1) {
+    if (pushing && ws_split == 1) {
         for (int o = 0; o < push->world; ++o) {
             a.push_slot[o] = static_cast<float *>(push->slots[o]);
             a.push_flag[o] = static_cast<int *>(push->flags[o]);
@@ -294,7 +327,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
 
     const int le = launch_gemm(p, a, stream);
     if (le != 0) return fail_cuda(static_cast<cudaError_t>(le));
-    if (p.split_k > 1 && pushing) {
+    if (ws_split > 1 && pushing) {
         float *slots[8];
         int *flags[8];
         for (int o = 0; o < push->world; ++o) {
@@ -304,7 +337,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
         const int re = launch_splitk_reduce_push(a.partial, M, N, p.split_k, slots, flags, static_cast<unsigned int *>(push->done),
                                                  push->world, push->rank, push->epoch, stream);
         if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
-    } else if (p.split_k > 1) {
+    } else if (ws_split > 1) {
         const int re = launch_splitk_reduce(a.partial, C, D, alpha, beta, M * N, p.split_k, stream);
         if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
     } else if (tail.s > 1) {
@@ -368,7 +401,7 @@ int64_t b200_gemm_smem_bytes(int dtype, const b200_gemm_params *p) {
 
 int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p) {
     if (!p) return 0;
-    if (p->split_k > 1) return static_cast<int64_t>(p->split_k) * M * N * static_cast<int64_t>(sizeof(float));
+    if (p->split_k > 1 && !p->cluster_reduce) return static_cast<int64_t>(p->split_k) * M * N * static_cast<int64_t>(sizeof(float));
     if (p->tail_split) {
         const Plan plan = make_plan(*p, p->num_sms > 0 ? p->num_sms : 148);
         if (plan.status != B200_OK) return 0;

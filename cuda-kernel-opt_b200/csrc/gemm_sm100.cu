@@ -52,6 +52,7 @@ struct Cfg {
     int kblocks, stages, stage_bytes, a_stage_bytes, cta_rows_a;
     int a_box_rows, a_boxes, a_priv, a_bars, chunk_n, b_priv, b_res_chunks, b_bars;
     int acc_cols, mma_m, epi_mode, epi_warps, M, N;
+    int cl_split, cl_rank;  // cluster reduce: K slices per tile (= cluster size) and this CTA's slice
     uint32_t idesc_chunk, idesc_res;
     long long budget;
 };
@@ -69,6 +70,11 @@ __device__ __forceinline__ Unit decode_unit(const Cfg &c, int u) {
         t = c.tail_full + w.tail_idx;
         w.slice = tl / c.tail_r;
         slices = c.tail_s;
+    } else if (c.cl_split > 1) {
+        w.tail_idx = -1;
+        t = u;
+        w.slice = c.cl_rank;
+        slices = c.cl_split;
     } else {
         w.tail_idx = -1;
         t = u % c.num_tiles;
@@ -156,11 +162,14 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     c.b_res_chunks = g.b_res_chunks; c.b_bars = g.b_bars; c.acc_cols = g.acc_cols; c.mma_m = g.mma_m;
     c.epi_mode = g.epi_mode; c.epi_warps = g.epi_warps; c.M = g.M; c.N = g.N;
     c.idesc_chunk = g.idesc_chunk; c.idesc_res = g.idesc_res; c.budget = g.wait_budget_cycles;
+    c.cl_split = (CG == 1 && g.cl_split > 1) ? g.cl_split : 1;
+    c.cl_rank = 0;
     const int off_bars = g.off_bars, off_tmem_ptr = g.off_tmem_ptr, off_epi = g.off_epi;
     const int tmem_cols = g.tmem_cols;
     const int P = g.producer_warps;
     const int push_world = g.push_world, push_rank = g.push_rank, push_rows = g.push_rows;
     const int ld_cd = g.ld_cd;
+    const bool swap_ab = g.swap_ab != 0;
     const int dbg = g.debug_flags;  // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage)
     const float g_alpha = g.alpha, g_beta = g.beta;
     const float *const gC = g.C;
@@ -183,8 +192,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int lane = tid & 31;
     const int mma_warp = P;
     const uint32_t rank = (CG == 2) ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
-    const int group = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-    const int num_groups = static_cast<int>(gridDim.x) / CG;
+    const bool clustered = (CG == 2) || c.cl_split > 1;
+    if (CG == 1 && c.cl_split > 1) c.cl_rank = __shfl_sync(0xffffffffu, static_cast<int>(cluster_ctarank()), 0);
+    const int group = static_cast<int>(blockIdx.x) / (CG * c.cl_split);   // CTAs that share a tile share a group
+    const int num_groups = static_cast<int>(gridDim.x) / (CG * c.cl_split);
 
     // Barrier map, per stage: [full A x a_bars][full B x b_bars][empty A][pad x (a_bars-1)][empty B x b_bars];
     // after the stages: tmem_full[2], tmem_empty[2].
@@ -194,6 +205,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const uint32_t empty_b_off = 8u * static_cast<uint32_t>(2 * c.a_bars + c.b_bars);
     const uint32_t tmem_full0 = bars + static_cast<uint32_t>(c.stages) * stage_bar_bytes;
     const uint32_t tmem_empty0 = tmem_full0 + 16u;
+    const uint32_t part_full = tmem_full0 + 32u;   // cluster reduce: every slice of the tile sits in its CTA's shared memory
+    const uint32_t part_empty = tmem_full0 + 40u;  // ... and every CTA of the cluster has read this CTA's slice
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -209,6 +222,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         mbar_init(tmem_full0 + 8, 1);
         mbar_init(tmem_empty0, c.epi_warps * CG);
         mbar_init(tmem_empty0 + 8, c.epi_warps * CG);
+        mbar_init(part_full, c.epi_warps * c.cl_split);
+        mbar_init(part_empty, c.epi_warps * c.cl_split);
         fence_mbar_init();
     }
     if (warp == 0 && lane == 0) {
@@ -222,7 +237,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     }
     tc_fence_before_sync();
     __syncthreads();
-    if constexpr (CG == 2) {
+    if (clustered) {
         cluster_arrive();
         cluster_wait();
     }
@@ -251,8 +266,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
             const bool arm = issuer && rank == 0;
             const int hint = g.l2_hint;
-            const uint64_t pol_a = l2_policy(hint >= 1 ? 2 : 0);
-            const uint64_t pol_b = l2_policy(hint == 1 ? 1 : (hint == 3 ? 2 : 0));
+            // the hint names the caller's operands; with swapped roles map_a holds B^T and map_b holds A
+            const int kind_a = hint >= 1 ? 2 : 0;
+            const int kind_b = hint == 1 ? 1 : (hint == 3 ? 2 : 0);
+            const uint64_t pol_a = l2_policy(swap_ab ? kind_b : kind_a);
+            const uint64_t pol_b = l2_policy(swap_ab ? kind_a : kind_b);
             const bool issue_a = issuer && do_a && !(dbg & 2);
             const bool issue_b = issuer && do_b && !(dbg & 2);
             int s = 0;
@@ -654,6 +672,64 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const float a_u = tail ? 1.0f : alpha;
             const float b_u = tail ? 0.0f : beta;
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
+            if (c.cl_split > 1) {
+                // ---- K slices of this tile live in the CTAs of the cluster (transposed drain only).
+                // A: raw accumulator -> this CTA's shared memory as [column][row]; tell every CTA.
+                const uint32_t pbuf = base + static_cast<uint32_t>(off_epi);
+                ok = wait_bar(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+                    uint32_t r[32];
+                    if (col_end - c0 >= 32) {
+                        tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
+                    } else {
+                        uint32_t r16[16];
+                        tmem_ld_32x16(t_row + static_cast<uint32_t>(c0), r16);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = r16[j];
+#pragma unroll
+                        for (int j = 16; j < 32; ++j) r[j] = 0;
+                    }
+                    tmem_ld_wait();
+                    if (lane_has_row) {
+                        const uint32_t dst = pbuf + static_cast<uint32_t>(c0 * 128 + row_in_cta) * 4u;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c0 + j < col_end)
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + static_cast<uint32_t>(j) * 512u), "r"(r[j]) : "memory");
+                    }
+                }
+                tc_fence_before_sync();
+                fence_acq_rel_cluster();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty0 + 8u * acc);  // accumulator slot back to the MMA thread
+                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane)));
+                // B: when all slices are staged, this CTA sums its share of the tile's columns over the
+                // cluster in slice order (the order of the workspace form) and writes D.
+                ok = wait_bar(part_full, tl & 1u, c.budget, abort_flag, 701);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_acq_rel_cluster();
+                const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
+                const int my_end = min(c.tile_n, (c.cl_rank + 1) * per);
+                for (int col = c.cl_rank * per + half; col < my_end; col += halves) {
+                    const int gcol = w.n0 + col;
+                    if (gcol >= c.N) break;
+                    const uint32_t src = pbuf + static_cast<uint32_t>(col * 128 + row_in_cta) * 4u;
+                    float sum = ld_shared_cluster_f32(mapa_shared(src, 0u));
+                    for (int sl = 1; sl < c.cl_split; ++sl) sum += ld_shared_cluster_f32(mapa_shared(src, static_cast<uint32_t>(sl)));
+                    if (row_ok) {
+                        const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row);
+                        float v = alpha * sum;
+                        if (beta != 0.0f) v += beta * __ldg(gC + off);
+                        gD[off] = v;
+                    }
+                }
+                __syncwarp();
+                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane)));
+                continue;
+            }
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                 if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
                 uint32_t r[32];
@@ -670,7 +746,25 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 }
                 tmem_ld_wait();
                 const int nvec = wide ? 8 : 4;
-                if (c.epi_mode == 0 || !wide || tail) {
+                if (swap_ab) {
+                    // Transposed drain: this thread's row is a column of D and register j its row
+                    // w.n0 + c0 + j, so for every j the 32 lanes store 32 consecutive floats.
+                    if (row_ok) {
+                        const size_t pitch = to_partial ? static_cast<size_t>(c.M) : static_cast<size_t>(ld_cd);
+                        const size_t off0 = static_cast<size_t>(w.n0 + c0) * pitch + static_cast<size_t>(row);
+                        float *dst = out + off0;
+                        const float *csrc = gC + off0;
+                        const int valid = min(4 * nvec, c.N - (w.n0 + c0));
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < valid) {
+                                float v = a_u * __uint_as_float(r[j]);
+                                if (b_u != 0.0f) v += b_u * __ldg(csrc + static_cast<size_t>(j) * pitch);
+                                dst[static_cast<size_t>(j) * pitch] = v;
+                            }
+                        }
+                    }
+                } else if (c.epi_mode == 0 || !wide || tail) {
                     if (row_ok) {
                         float4 *dst = reinterpret_cast<float4 *>(out + row_off + c0);
                         const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
@@ -748,7 +842,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if constexpr (CG == 2) {
+    if (clustered) {
+        // no CTA leaves while a peer may still arrive on its barriers or read its shared memory
         cluster_arrive();
         cluster_wait();
     }
@@ -1034,16 +1129,24 @@ int prepare_kernels() {
 
 int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(p.grid), 1, 1);
+    int grid = p.grid;
+    if (p.cluster_reduce) {
+        // whole clusters only, and no more of them than there are tiles
+        grid -= grid % p.split_k;
+        if (grid > args.num_tiles * p.split_k) grid = args.num_tiles * p.split_k;
+        if (grid < p.split_k) grid = p.split_k;
+    }
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
     cfg.blockDim = dim3(static_cast<unsigned>(p.threads), 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(p.smem_bytes);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     cfg.attrs = nullptr;
     cfg.numAttrs = 0;
-    if (p.cta_group == 2) {
+    const int cluster = p.cta_group == 2 ? 2 : (p.cluster_reduce ? p.split_k : 1);
+    if (cluster > 1) {
         attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
@@ -1051,6 +1154,20 @@ int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
     }
     const bool simple = (p.a_bars == 1 && p.b_bars == 1 && p.a_boxes == 1 && p.b_priv == 0 && p.b_res_chunks == 1);
     const KernelFn fn = pick_kernel(p.cta_group, simple, args.prof != nullptr);
+    if (p.cluster_reduce) {
+        // A persistent grid wants every cluster resident at once: ask how many clusters of this
+        // size the device holds (it depends on how the SMs are grouped) and cap the grid there.
+        static int max_clusters[16][9];  // per device and cluster size; 0 = not asked yet, -1 = unknown
+        int dev = 0;
+        cudaGetDevice(&dev);
+        int &mc = max_clusters[dev & 15][cluster];
+        if (mc == 0) {
+            int n = 0;
+            mc = (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess && n > 0) ? n : -1;
+            cudaGetLastError();
+        }
+        if (mc > 0 && grid > mc * cluster) cfg.gridDim = dim3(static_cast<unsigned>(mc * cluster), 1, 1);
+    }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, args);
     return static_cast<int>(e);
 }

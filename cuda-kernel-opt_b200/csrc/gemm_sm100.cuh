@@ -40,6 +40,9 @@ struct alignas(64) GemmArgs {
     int debug_flags;
     int l2_hint;
     int k_order;
+    int cl_split;       // > 1: cluster size; the CTAs of a cluster take the K slices of one tile and reduce through
+                        // distributed shared memory (split_k is 1 then: no workspace)
+    int swap_ab;        // 1: M/N above are those of the transposed problem and the tile is stored transposed (D[col][row])
     // split-K across GPUs with the reduce-scatter fused into the epilogue ("push" mode, world > 0):
     // the fp32 tile rows owned by GPU o are stored straight into o's slot area over NVLink
     // (plain peer stores), slot [source rank][rows per owner][N]; the last CTA to finish raises

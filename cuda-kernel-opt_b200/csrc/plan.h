@@ -48,6 +48,9 @@ struct Plan {
     int split_k = 1;
     int tile_group_m = 1;
     int grid = 0;
+    int swap = 0;                         // 1: the kernel computes D^T = B^T * A^T (tile_m spans N, tile_n spans M)
+    int cluster_reduce = 0;               // 1: the split_k slices of a tile run in one thread-block cluster and meet
+                                          //    in distributed shared memory (no workspace, no second kernel)
 };
 
 // Tail split: with T tiles on S slots (CTAs or CTA pairs) the last wave holds r = T mod S tiles.
@@ -84,9 +87,26 @@ inline int pow2_at_least(int x) {
 }
 
 // Validates tunables that do not depend on the problem shape and lays out shared memory.
-inline Plan make_plan(const b200_gemm_params &q, int num_sms_device) {
+inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     Plan p;
     p.status = B200_INVALID_CONFIG;
+    b200_gemm_params q = user;
+    if (user.swap_ab != 0 && user.swap_ab != 1) return p;
+    if (user.swap_ab) {
+        // Swapped operand roles: plan the transposed problem. The caller's tile_n (columns of D, rows of
+        // B^T) becomes the 64/128-row side of the MMA, tile_m its N side; sub-tile barriers follow
+        // their operands; the drain is plain stores (a transposed tile has no row-major TMA box).
+        if ((user.cta_group != 0 && user.cta_group != 1) || user.tail_split) return p;
+        if (user.epilogue != 0 && user.epilogue != 1) return p;
+        q.tile_m = user.tile_n;
+        q.tile_n = user.tile_m;
+        q.bar_steps_a = user.bar_steps_b;
+        q.bar_steps_b = user.bar_steps_a;
+        q.bar_step_rows_a = user.bar_step_rows_b;
+        q.bar_step_rows_b = user.bar_step_rows_a;
+        q.epilogue = 0;
+        p.swap = 1;
+    }
     const int cg = q.cta_group == 0 ? 1 : q.cta_group;
     if (cg != 1 && cg != 2) return p;
     p.cta_group = cg;
@@ -121,6 +141,13 @@ inline Plan make_plan(const b200_gemm_params &q, int num_sms_device) {
     if (q.l2_hint < 0 || q.l2_hint > 3) return p;
     if (q.k_order != 0 && q.k_order != 1) return p;
     p.epi_mode = q.epilogue;
+    if (user.cluster_reduce != 0 && user.cluster_reduce != 1) return p;
+    if (user.cluster_reduce) {
+        // K slices as the CTAs of a cluster: portable cluster sizes, a transposed accumulator of at
+        // most 64 columns (32 KiB of fp32 per CTA) staged in shared memory for the peers to read.
+        if (!p.swap || (p.split_k != 2 && p.split_k != 4 && p.split_k != 8) || q.tile_n > 64) return p;
+        p.cluster_reduce = 1;
+    }
 
     // Sub-tile split of the A stage buffer (rows per barrier step). 0 or the full extent = off.
     int step_a = q.bar_step_rows_a;
@@ -173,7 +200,9 @@ inline Plan make_plan(const b200_gemm_params &q, int num_sms_device) {
     if ((p.a_box_rows % 8) || ((p.chunk_n / cg) % 8)) return p;
     p.off_epi = p.stages * p.stage_bytes;
     p.epi_bytes = p.epi_mode ? p.epi_warps * 2 * 32 * kEpiBoxCols * 4 : 0;  // two 32x32 fp32 boxes per warp
-    p.num_barriers = p.stages * 2 * (p.a_bars + p.b_bars) /* full + empty */ + 4 /* tmem full/empty x2 */;
+    if (p.cluster_reduce) p.epi_bytes = p.tile_n * 128 * 4;                 // this CTA's partial tile, [column][row]
+    p.num_barriers = p.stages * 2 * (p.a_bars + p.b_bars) /* full + empty */ + 4 /* tmem full/empty x2 */ +
+                     2 /* partial tile full / empty (cluster reduce) */;
     p.off_bars = p.off_epi + p.epi_bytes;
     p.off_tmem_ptr = p.off_bars + p.num_barriers * 8;
     const int used = p.off_tmem_ptr + 16;

@@ -84,6 +84,16 @@ typedef struct b200_gemm_params {
     int tail_split; /* 1 = when the tiles do not fill the last wave of the persistent grid, split the tiles of
                        that wave along K over the idle CTAs (partials in the workspace, summed by a small
                        second kernel): needs b200_gemm_workspace_bytes of workspace. 0 = off */
+    int swap_ab;    /* 1 = operand roles swapped inside the kernel for skinny M (decode shapes): the rows of B^T feed
+                       the 64/128-row side of the MMA and the few rows of A its N side, so a stage holds
+                       tile_n rows of weights and only tile_m rows of activations, and the accumulator is
+                       written to D transposed (coalesced along N). Then tile_n is 64 or 128 and tile_m a
+                       multiple of 16 in [16, 256]; the bar_step fields follow their operands; needs
+                       cta_group = 1 and tail_split = 0, and drains with plain stores. Same results as 0 */
+    int cluster_reduce; /* 1 (with swap_ab = 1, split_k 2, 4 or 8, tile_m <= 64) = the split_k slices of a tile run
+                       as the CTAs of one thread-block cluster and are summed through distributed shared
+                       memory, in slice order: no workspace, no second kernel, same bits as the workspace
+                       form. 0 = slices meet in the workspace */
 } b200_gemm_params;
 
 /* Fills *p with the tuned default for the shape (what the reference's harness hard-codes per

@@ -103,7 +103,7 @@ def test_barrier_granularities(pkg):
 def test_shared_memory_filter(pkg):
     """The harness only runs configurations that fit (port_2.cu:1229-1231); here they are refused."""
     fits = P(pkg, tile_m=128, tile_n=256, bar_step_rows_b=256, num_stages=4)
-    assert pkg.smem_bytes(pkg.F16, fits) == 4 * (128 + 256) * 64 * 2 + (4 * 4 + 4) * 8 + 16 + 1024
+    assert pkg.smem_bytes(pkg.F16, fits) == 4 * (128 + 256) * 64 * 2 + (4 * 4 + 6) * 8 + 16 + 1024
     too_deep = P(pkg, tile_m=128, tile_n=256, bar_step_rows_b=256, num_stages=6)   # 288 KiB of stages
     assert pkg.smem_bytes(pkg.F16, too_deep) == -1
     assert pkg.validate(4096, 4096, 4096, pkg.F16, too_deep) == pkg.INVALID_CONFIG
@@ -124,6 +124,44 @@ def test_b200_extensions(pkg):
     p = P(pkg, split_k=4)
     assert pkg.workspace_bytes(512, 256, 4096, p) == 4 * 512 * 256 * 4
     assert pkg.workspace_bytes(512, 256, 4096, P(pkg)) == 0
+
+
+def test_swapped_roles_and_cluster_reduce_domain(pkg):
+    """swap_ab: tile_n is the 64/128-row side, tile_m the multiple-of-16 side; cluster_reduce needs
+    swap_ab, a portable cluster size and a narrow accumulator, and then no workspace."""
+    ok = lambda M=16, N=4096, K=4096, **ov: pkg.validate(M, N, K, pkg.BF16, P(pkg, **ov))
+    sw = dict(swap_ab=1, tile_m=16, tile_n=128, bar_step_rows_a=16, bar_step_rows_b=128)
+    assert ok(**sw) == pkg.OK
+    assert ok(**dict(sw, tile_m=48, bar_step_rows_a=48)) == pkg.OK
+    assert ok(**dict(sw, tile_m=256, bar_step_rows_a=256, num_stages=3)) == pkg.OK
+    assert ok(**dict(sw, tile_n=64, bar_step_rows_b=64)) == pkg.OK
+    assert ok(**dict(sw, tile_n=256, bar_step_rows_b=256)) == pkg.INVALID_CONFIG       # the MMA's M side is 64 or 128
+    assert ok(**dict(sw, tile_m=24, bar_step_rows_a=24)) == pkg.INVALID_CONFIG          # its N side a multiple of 16
+    assert ok(**dict(sw, cta_group=2)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sw, tail_split=1)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sw, swap_ab=2)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sw, split_k=3)) == pkg.OK
+    for s_ in (2, 4, 8):
+        assert ok(**dict(sw, split_k=s_, cluster_reduce=1)) == pkg.OK
+    assert ok(**dict(sw, split_k=3, cluster_reduce=1)) == pkg.INVALID_CONFIG            # cluster sizes 2, 4, 8
+    assert ok(**dict(sw, split_k=1, cluster_reduce=1)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sw, tile_m=80, bar_step_rows_a=80, split_k=2, cluster_reduce=1)) == pkg.INVALID_CONFIG  # > 64 columns
+    assert ok(tile_m=128, tile_n=128, split_k=2, cluster_reduce=1) == pkg.INVALID_CONFIG    # needs swap_ab
+    assert pkg.workspace_bytes(16, 4096, 4096, P(pkg, **dict(sw, split_k=4))) == 4 * 16 * 4096 * 4
+    assert pkg.workspace_bytes(16, 4096, 4096, P(pkg, **dict(sw, split_k=4, cluster_reduce=1))) == 0
+    # the partial tile of a cluster reduce is staged in shared memory: 128 rows x tile_m fp32
+    a = pkg.smem_bytes(pkg.BF16, P(pkg, **dict(sw, tile_m=64, bar_step_rows_a=64, num_stages=8, split_k=2)))
+    b = pkg.smem_bytes(pkg.BF16, P(pkg, **dict(sw, tile_m=64, bar_step_rows_a=64, num_stages=8, split_k=2, cluster_reduce=1)))
+    assert b - a == 64 * 128 * 4
+    # decode-shape defaults use the swapped form, and a cluster over K when there are few tiles
+    d = pkg.default_params(16, 28672, 8192, pkg.BF16)
+    assert (d.swap_ab, d.tile_m, d.tile_n, d.split_k) == (1, 16, 128, 1) and pkg.validate(16, 28672, 8192, pkg.BF16, d) == pkg.OK
+    d = pkg.default_params(16, 3584, 8192, pkg.BF16)
+    assert (d.swap_ab, d.split_k, d.cluster_reduce) == (1, 4, 1) and pkg.validate(16, 3584, 8192, pkg.BF16, d) == pkg.OK
+    d = pkg.default_params(128, 28672, 8192, pkg.BF16)
+    assert d.swap_ab == 0
+    d = pkg.default_params(16, 28672, 8192, pkg.BF16, tile_n=64)                           # a tile override names the plain form
+    assert d.swap_ab == 0 and pkg.validate(16, 28672, 8192, pkg.BF16, d) == pkg.OK
 
 
 def test_tail_split_planning(pkg):

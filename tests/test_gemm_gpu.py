@@ -169,6 +169,58 @@ def test_randomised_shapes_and_tunables(pkg, cuda, oracle):
     assert ran >= 60
 
 
+def test_swapped_roles_and_cluster_reduce(pkg, cuda, oracle):
+    """swap_ab = 1 (B^T on the MMA's M side, D written transposed) and cluster_reduce = 1 (the K slices of a
+    tile summed through distributed shared memory) against the oracle: skinny and ragged shapes, scalars,
+    both dtypes, every cluster size; the cluster form equals the workspace form bit for bit; the
+    decode-shape defaults take this path."""
+    import random
+    rnd = random.Random(77)
+    ran = 0
+    for it in range(300):
+        if ran >= 60:
+            break
+        tile_m = rnd.choice([16, 16, 32, 48, 64, 128, 256])
+        ov = dict(swap_ab=1, tile_m=tile_m, tile_n=rnd.choice([128, 128, 64]), segment_dim_k=rnd.choice([64, 128, 256]),
+                  num_stages=rnd.randint(1, 8), tile_group_m=rnd.randint(1, 9), num_producer_warps=rnd.choice([1, 2]),
+                  num_consumer_warps=rnd.choice([4, 8]), l2_hint=rnd.randint(0, 3), num_sms=rnd.choice([0, 0, 37, 16]))
+        mode = rnd.random()
+        if mode < 0.25:
+            ov["split_k"] = rnd.randint(2, 6)
+        elif mode < 0.7 and tile_m <= 64:
+            ov.update(split_k=rnd.choice([2, 4, 8]), cluster_reduce=1)
+        elif mode < 0.85:
+            step = rnd.choice([s_ for s_ in (16, 32, 64) if tile_m % s_ == 0 and tile_m // s_ <= 16] or [tile_m])
+            ov.update(bar_step_rows_a=step, bar_steps_a=rnd.randint(0, tile_m // step))
+        dtype = rnd.choice([pkg.F16, pkg.BF16])
+        m = rnd.choice([1, 3, 16, 17, 32, 50, 64, 100, 300])
+        n = 4 * rnd.randint(4, 500)
+        k = 8 * rnd.randint(1, 180)
+        alpha, beta = rnd.choice([(1.0, 0.0), (1.0, 1.0), (0.5, -2.0)])
+        p = pkg.default_params(m, n, k, dtype, **ov)
+        if pkg.validate(m, n, k, dtype, p) != pkg.OK:
+            continue
+        ran += 1
+        A, Bt, Cm = inputs(pkg, dtype, m, n, k, 3000 + it)
+        got = run_gemm(pkg, cuda, dtype, A, Bt, Cm, alpha, beta, **ov)
+        want = oracle.gemm(A, Bt, Cm if beta else None, alpha, beta, dtype)
+        ok, msg = tolerance_ok(got, want, k, abs(alpha) + abs(beta) + 1.0)
+        assert ok, (m, n, k, dtype, alpha, beta, p.as_dict(), msg)
+        if ov.get("cluster_reduce"):
+            same = run_gemm(pkg, cuda, dtype, A, Bt, Cm, alpha, beta, **dict(ov, cluster_reduce=0))
+            assert np.array_equal(got, same), ("cluster reduce differs from the workspace form", m, n, k, p.as_dict())
+    assert ran >= 45
+    # the defaults of the decode shapes: swapped, and a cluster over K when the tiles are few
+    for m, n, k in ((16, 3584, 8192), (32, 7168, 4096), (8, 28672, 1024)):
+        p = pkg.default_params(m, n, k, pkg.BF16)
+        assert p.swap_ab == 1
+        A, Bt, Cm = inputs(pkg, pkg.BF16, m, n, k, 3500 + m)
+        got = run_gemm(pkg, cuda, pkg.BF16, A, Bt, Cm, 1.0, 1.0)
+        want = oracle.gemm(A, Bt, Cm, 1.0, 1.0, oracle.BF16)
+        ok, msg = tolerance_ok(got, want, k, 3.0)
+        assert ok, (m, n, k, p.as_dict(), msg)
+
+
 def test_bf16_and_scalars(pkg, cuda, oracle):
     A, Bt, Cm = inputs(pkg, pkg.BF16, 384, 512, 768, 61)
     for alpha, beta in ((1.0, 0.0), (0.5, 2.0), (-1.25, 0.75), (0.0, 1.0)):
