@@ -319,10 +319,11 @@ def run_ours(args):
     sampler = ClockSampler(local)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(args.steps)]
-    # Steps far shorter than a host launch (the decode shapes: tens of microseconds) are issued as
-    # one CUDA graph of the K steps, the way a serving loop issues them, so the device is timed
-    # and not the Python interpreter; --graph 0/1 overrides.
-    use_graph = (bound == "hbm" and not splitk_ranks) if args.graph < 0 else bool(args.graph)
+    # Steps of the order of a host launch (expected device time under 0.3 ms: the decode shapes and the
+    # small squares, not 8192^3) are issued as one CUDA graph of the K steps, the way a serving loop
+    # issues them, so the device is timed and not the Python interpreter; --graph 0/1 overrides.
+    short_step = max(flops_of(m_loc, n_loc, k_loc) / 1.4e15, bytes_of(m_loc, n_loc, k_loc) / 6.0e12) < 0.3e-3
+    use_graph = (short_step and not splitk_ranks) if args.graph < 0 else bool(args.graph)
     graph = None
     if use_graph:
         cap = torch.cuda.Stream(dev)
@@ -513,7 +514,7 @@ def main():
     ap.add_argument("--check", action="store_true", help="split-K workloads: compare fused and NCCL results")
     ap.add_argument("--params", default="", help="JSON overrides of the launch tunables")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--graph", type=int, default=-1, help="1: issue the timed steps as one CUDA graph, 0: one call per step; default: graph for the HBM-bound workloads")
+    ap.add_argument("--graph", type=int, default=-1, help="1: issue the timed steps as one CUDA graph, 0: one call per step; default: graph when a step is expected to take under 0.3 ms")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--wmma-baseline", action="store_true",

@@ -38,10 +38,12 @@ def needs_build() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, defines=()) -> str:
+    """defines: extra -D flags for diagnostic builds (-DB200_TIMELINE: %globaltimer stamps of set-up and
+    role milestones in a 32-slot profile buffer); such a build replaces the library until the next --force."""
     if not force and not needs_build():
         return LIB
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    cmd = [_nvcc()] + NVCC_FLAGS + list(defines) + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a wrapper compiler; nvcc needs the system g++
     if os.path.exists("/usr/bin/g++"):
@@ -55,4 +57,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=[a for a in sys.argv[1:] if a.startswith("-D")]))

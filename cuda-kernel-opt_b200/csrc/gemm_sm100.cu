@@ -35,6 +35,14 @@ __device__ int g_device_status[4];
 
 namespace {
 
+#ifdef B200_TIMELINE
+// Diagnostic build: 32 slots per CTA, slots 16.. hold %globaltimer stamps of set-up and role milestones.
+constexpr int kProfSlots = 32;
+#define B200_TL(slot) do { if (PROF && prof) prof[slot] = static_cast<long long>(global_timer_ns()); } while (0)
+#else
+constexpr int kProfSlots = 16;
+#define B200_TL(slot) do { } while (0)
+#endif
 constexpr int kMaxThreads = 544;  // (8 producer + 1 MMA + 8 epilogue warps) * 32
 
 struct Unit {
@@ -53,6 +61,7 @@ struct Cfg {
     int a_box_rows, a_boxes, a_priv, a_bars, chunk_n, b_priv, b_res_chunks, b_bars;
     int acc_cols, mma_m, epi_mode, epi_warps, M, N;
     int cl_split, cl_rank;  // cluster reduce: K slices per tile (= cluster size) and this CTA's slice
+    int cl_seg_begin, cl_seg_end;
     uint32_t idesc_chunk, idesc_res;
     long long budget;
 };
@@ -61,25 +70,43 @@ struct Cfg {
 // (get_tile_offset_cd, port_0.cu:201-210): tile_group_m tile rows are walked column-major inside
 // a group so concurrently running CTAs share B^T column panels in L2; the last group may be short.
 __device__ __forceinline__ Unit decode_unit(const Cfg &c, int u) {
+    // The roles that call this are single dependent instruction chains, where an integer
+    // division costs on the order of a hundred cycles: the common cases avoid them.
     Unit w;
-    int t, slices;
+    int t;
     if (c.tail_s > 1 && u >= c.tail_full) {
         // last wave: tail tile (u - full) mod r, K slice (u - full) / r
         const int tl = u - c.tail_full;
         w.tail_idx = tl % c.tail_r;
         t = c.tail_full + w.tail_idx;
         w.slice = tl / c.tail_r;
-        slices = c.tail_s;
+        w.seg_begin = static_cast<int>(static_cast<unsigned>(w.slice) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.tail_s));
+        w.seg_end = static_cast<int>(static_cast<unsigned>(w.slice + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.tail_s));
     } else if (c.cl_split > 1) {
         w.tail_idx = -1;
         t = u;
         w.slice = c.cl_rank;
-        slices = c.cl_split;
+        w.seg_begin = c.cl_seg_begin;   // the same K slice for every tile of this CTA
+        w.seg_end = c.cl_seg_end;
+    } else if (c.split_k == 1) {
+        w.tail_idx = -1;
+        t = u;
+        w.slice = 0;
+        w.seg_begin = 0;
+        w.seg_end = c.num_segs;
     } else {
         w.tail_idx = -1;
         t = u % c.num_tiles;
         w.slice = u / c.num_tiles;
-        slices = c.split_k;
+        // slice <= 64 and num_segs < 2^24: the products fit 32 bits
+        w.seg_begin = static_cast<int>(static_cast<unsigned>(w.slice) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.split_k));
+        w.seg_end = static_cast<int>(static_cast<unsigned>(w.slice + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.split_k));
+    }
+    if (c.tiles_m == 1) {
+        // one row of tiles (the skinny shapes): the grouped order is the plain column order
+        w.m0 = 0;
+        w.n0 = t * c.tile_n;
+        return w;
     }
     const int group_tile_count = c.tile_group_m * c.tiles_n;
     const int group_first_row = (t / group_tile_count) * c.tile_group_m;
@@ -87,18 +114,17 @@ __device__ __forceinline__ Unit decode_unit(const Cfg &c, int u) {
     const int in_group = t % group_tile_count;
     w.m0 = (group_first_row + in_group % group_rows) * c.tile_m;
     w.n0 = (in_group / group_rows) * c.tile_n;
-    w.seg_begin = static_cast<int>(static_cast<long long>(w.slice) * c.num_segs / slices);
-    w.seg_end = static_cast<int>(static_cast<long long>(w.slice + 1) * c.num_segs / slices);
     return w;
 }
 
 // Bounded mbarrier wait. Returns false when the budget ran out here or elsewhere in the block.
+template <bool CLUSTER_ACQUIRE = false>
 __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
                                        int bar_id) {
     const long long t0 = clock64();
     uint32_t spins = 0;
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
 #ifdef B200_WAIT_SLEEP
         __nanosleep(B200_WAIT_SLEEP);
 #endif
@@ -122,6 +148,14 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, long lon
                                          int bar_id) {
     if (mbar_try_wait(bar, parity)) return true;
     return wait_slow(bar, parity, budget, abort_flag, bar_id);
+}
+
+// Bounded wait whose success is an acquire at cluster scope (data written by other CTAs of the
+// cluster before their release-arrive may be read afterwards).
+__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
+                                                 int bar_id) {
+    if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+    return wait_slow<true>(bar, parity, budget, abort_flag, bar_id);
 }
 
 // All lanes of a converged warp wait; the result is the same in every lane.
@@ -175,7 +209,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const float *const gC = g.C;
     float *const gD = g.D;
     float *const g_partial = g.partial;
-    long long *const prof = (PROF && g.prof && static_cast<int>(blockIdx.x) < g.prof_blocks) ? g.prof + 16 * blockIdx.x : nullptr;
+    long long *const prof = (PROF && g.prof && static_cast<int>(blockIdx.x) < g.prof_blocks) ? g.prof + kProfSlots * blockIdx.x : nullptr;
+
+    if (PROF && prof && threadIdx.x == 0) prof[13] = static_cast<long long>(global_timer_ns());  // kernel entry
 
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -193,7 +229,13 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int mma_warp = P;
     const uint32_t rank = (CG == 2) ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
     const bool clustered = (CG == 2) || c.cl_split > 1;
-    if (CG == 1 && c.cl_split > 1) c.cl_rank = __shfl_sync(0xffffffffu, static_cast<int>(cluster_ctarank()), 0);
+    c.cl_seg_begin = 0;
+    c.cl_seg_end = c.num_segs;
+    if (CG == 1 && c.cl_split > 1) {
+        c.cl_rank = __shfl_sync(0xffffffffu, static_cast<int>(cluster_ctarank()), 0);
+        c.cl_seg_begin = static_cast<int>(static_cast<unsigned>(c.cl_rank) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.cl_split));
+        c.cl_seg_end = static_cast<int>(static_cast<unsigned>(c.cl_rank + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.cl_split));
+    }
     const int group = static_cast<int>(blockIdx.x) / (CG * c.cl_split);   // CTAs that share a tile share a group
     const int num_groups = static_cast<int>(gridDim.x) / (CG * c.cl_split);
 
@@ -208,23 +250,29 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const uint32_t part_full = tmem_full0 + 32u;   // cluster reduce: every slice of the tile sits in its CTA's shared memory
     const uint32_t part_empty = tmem_full0 + 40u;  // ... and every CTA of the cluster has read this CTA's slice
 
-    if (tid == 0) {
-        *abort_flag = 0;
-        for (int s = 0; s < c.stages; ++s) {
-            const uint32_t sb = bars + static_cast<uint32_t>(s) * stage_bar_bytes;
-            const bool one_full = (c.a_bars == 1 && c.b_bars == 1);
-            for (int j = 0; j < c.a_bars; ++j) mbar_init(sb + 8u * j, (one_full && P > 1) ? 2 : 1);
-            for (int t = 0; t < c.b_bars; ++t) mbar_init(sb + full_b_off + 8u * t, 1);
-            mbar_init(sb + empty_a_off, 1);
-            for (int t = 0; t < c.b_bars; ++t) mbar_init(sb + empty_b_off + 8u * t, 1);
+    // Barrier initialisation, one barrier per thread (a single thread took over a microsecond for
+    // the 26 barriers of a five-stage ring). Per stage: the full barriers of A expect both issuing
+    // warps when A and B^T share one barrier; everything else expects one arrival.
+    {
+        const int per_stage = 2 * (c.a_bars + c.b_bars);
+        const int ring = c.stages * per_stage;
+        const bool shared_full = (c.a_bars == 1 && c.b_bars == 1 && P > 1);
+        for (int i = tid; i < ring + 6; i += static_cast<int>(blockDim.x)) {
+            uint32_t count = 1;
+            if (i < ring) {
+                if (shared_full && (i % per_stage) == 0) count = 2;
+            } else {
+                const int j = i - ring;  // tmem_full[2], tmem_empty[2], part_full, part_empty
+                if (j == 2 || j == 3) count = static_cast<uint32_t>(c.epi_warps * CG);
+                if (j >= 4) count = static_cast<uint32_t>(c.epi_warps * c.cl_split);
+            }
+            mbar_init(bars + 8u * static_cast<uint32_t>(i), count);
+            fence_mbar_init();
         }
-        mbar_init(tmem_full0, 1);
-        mbar_init(tmem_full0 + 8, 1);
-        mbar_init(tmem_empty0, c.epi_warps * CG);
-        mbar_init(tmem_empty0 + 8, c.epi_warps * CG);
-        mbar_init(part_full, c.epi_warps * c.cl_split);
-        mbar_init(part_empty, c.epi_warps * c.cl_split);
-        fence_mbar_init();
+        if (tid == 0) {
+            *abort_flag = 0;
+            B200_TL(16);
+        }
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&g.map_a);
@@ -234,6 +282,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     if (warp == mma_warp) {
         tmem_alloc<CG>(base + off_tmem_ptr, static_cast<uint32_t>(tmem_cols));
         tmem_relinquish<CG>();
+        if (lane == 0) B200_TL(17);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -243,6 +292,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+
+    if (PROF && prof && tid == 0) prof[14] = static_cast<long long>(global_timer_ns());  // set-up done, roles start
 
     const int b_box_rows = c.chunk_n / CG;  // B^T rows per TMA box in this CTA
 
@@ -273,6 +324,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint64_t pol_b = l2_policy(swap_ab ? kind_a : kind_b);
             const bool issue_a = issuer && do_a && !(dbg & 2);
             const bool issue_b = issuer && do_b && !(dbg & 2);
+            if (lane == 0 && warp == 0) B200_TL(27);
             int s = 0;
             uint32_t ph = 0, it = 0;
             uint32_t stage = base, sb = bars, sbl = bars_leader;
@@ -292,6 +344,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const bool down = k_serpentine && (tile_no & 1);
                 int k = (down ? w.seg_end - 1 : w.seg_begin) * seg_k_elems;
                 const int k_next = down ? -2 * seg_k_elems : 0;   // after a segment k has advanced by one segment
+                if (tile_no == 0 && lane == 0 && warp == 0) B200_TL(28);
                 ++tile_no;
                 for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
                     const long long tw = PROF ? clock64() : 0;
@@ -299,6 +352,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     if (PROF) t_wait += clock64() - tw;
                     if (!ok) break;
                     if (arm) mbar_arrive_expect_tx(sb, (dbg & 2) ? 0u : my_bytes);
+                    if (it == 0 && lane == 0 && warp == 0) B200_TL(19);
                     uint32_t da = stage, db = stage + static_cast<uint32_t>(c.a_stage_bytes);
                     for (int kb = 0; kb < c.kblocks; ++kb) {
                         if constexpr (CG == 2) {
@@ -366,6 +420,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     ok = wait_all(sb, ph, c.budget, abort_flag, 400 + s);
                     if (PROF) t_full += clock64() - tf;
                     if (!ok) break;
+                    if (it == 0 && lane == 0) B200_TL(20);
                     tc_fence_after_sync();
                     uint64_t da = a_desc, db = b_desc;
                     for (int kb = 0; kb < c.kblocks; ++kb) {
@@ -393,6 +448,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 }
                 if (!ok) break;
                 if (issuer) commit_to<CG>(tmem_full0 + 8u * acc);
+                if (lane == 0) B200_TL(21);
             }
             if (PROF && prof && lane == 0) {
                 prof[6] = t_full;
@@ -651,6 +707,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             ok = __all_sync(0xffffffffu, ok);
             if (prof) t_tfull += clock64() - te;
             if (!ok) break;
+            if (tl == 0 && e == 0 && lane == 0) B200_TL(22);
+            if (e == 0 && lane == 0) B200_TL(26);   // last tile: accumulator ready
             tc_fence_after_sync();
             const int row = w.m0 + static_cast<int>(rank) * c.cta_rows_a + row_in_cta;
             const bool row_ok = lane_has_row && row < c.M;
@@ -676,7 +734,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 // ---- K slices of this tile live in the CTAs of the cluster (transposed drain only).
                 // A: raw accumulator -> this CTA's shared memory as [column][row]; tell every CTA.
                 const uint32_t pbuf = base + static_cast<uint32_t>(off_epi);
-                ok = wait_bar(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
+                ok = wait_bar_cluster(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
@@ -693,40 +751,62 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     }
                     tmem_ld_wait();
                     if (lane_has_row) {
+                        // columns beyond the tile are never read back: store the whole 16 or 32 without tests
                         const uint32_t dst = pbuf + static_cast<uint32_t>(c0 * 128 + row_in_cta) * 4u;
+                        const bool wide32 = col_end - c0 >= 32;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (c0 + j < col_end)
+                            if (j < 16 || wide32)
                                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + static_cast<uint32_t>(j) * 512u), "r"(r[j]) : "memory");
                     }
                 }
+                // The lanes' shared-memory writes are ordered before the arrivals below by the warp
+                // barrier, and the arrivals release at cluster scope (cumulative): no fence needed.
                 tc_fence_before_sync();
-                fence_acq_rel_cluster();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tmem_empty0 + 8u * acc);  // accumulator slot back to the MMA thread
                 if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane)));
+                if (e == 0 && lane == 0) B200_TL(29);
                 // B: when all slices are staged, this CTA sums its share of the tile's columns over the
                 // cluster in slice order (the order of the workspace form) and writes D.
-                ok = wait_bar(part_full, tl & 1u, c.budget, abort_flag, 701);
+                ok = wait_bar_cluster(part_full, tl & 1u, c.budget, abort_flag, 701);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                fence_acq_rel_cluster();
+                if (e == 0 && lane == 0) B200_TL(30);
                 const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
                 const int my_end = min(c.tile_n, (c.cl_rank + 1) * per);
-                for (int col = c.cl_rank * per + half; col < my_end; col += halves) {
-                    const int gcol = w.n0 + col;
-                    if (gcol >= c.N) break;
-                    const uint32_t src = pbuf + static_cast<uint32_t>(col * 128 + row_in_cta) * 4u;
-                    float sum = ld_shared_cluster_f32(mapa_shared(src, 0u));
-                    for (int sl = 1; sl < c.cl_split; ++sl) sum += ld_shared_cluster_f32(mapa_shared(src, static_cast<uint32_t>(sl)));
-                    if (row_ok) {
-                        const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row);
-                        float v = alpha * sum;
-                        if (beta != 0.0f) v += beta * __ldg(gC + off);
-                        gD[off] = v;
+                uint32_t peer[8];  // this thread's row of column 0 in every slice's CTA
+#pragma unroll
+                for (int sl = 0; sl < 8; ++sl)
+                    peer[sl] = mapa_shared(pbuf + static_cast<uint32_t>(row_in_cta) * 4u, static_cast<uint32_t>(sl < c.cl_split ? sl : 0));
+                // four columns per round: their 4 x cl_split remote loads are in flight together
+                for (int col0 = c.cl_rank * per + half; col0 < my_end; col0 += 4 * halves) {
+                    float v[4][8];
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int col = col0 + cc * halves;
+#pragma unroll
+                        for (int sl = 0; sl < 8; ++sl)
+                            if (sl < c.cl_split && col < my_end) v[cc][sl] = ld_shared_cluster_f32(peer[sl] + static_cast<uint32_t>(col) * 512u);
+                    }
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int col = col0 + cc * halves;
+                        const int gcol = w.n0 + col;
+                        if (col < my_end && gcol < c.N && row_ok) {
+                            float sum = v[cc][0];
+#pragma unroll
+                            for (int sl = 1; sl < 8; ++sl)
+                                if (sl < c.cl_split) sum += v[cc][sl];
+                            const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row);
+                            float val = alpha * sum;
+                            if (beta != 0.0f) val += beta * __ldg(gC + off);
+                            gD[off] = val;
+                        }
                     }
                 }
                 __syncwarp();
+                if (e == 0 && lane == 0) B200_TL(31);
                 if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane)));
                 continue;
             }
@@ -745,22 +825,35 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     for (int j = 16; j < 32; ++j) r[j] = 0;
                 }
                 tmem_ld_wait();
+                if (e == 0 && lane == 0) B200_TL(18);
                 const int nvec = wide ? 8 : 4;
                 if (swap_ab) {
                     // Transposed drain: this thread's row is a column of D and register j its row
-                    // w.n0 + c0 + j, so for every j the 32 lanes store 32 consecutive floats.
+                    // w.n0 + c0 + j, so for every j the 32 lanes store 32 consecutive floats. The
+                    // pointers advance by one pitch per register: a handful of instructions per store
+                    // (the epilogue warps run alone on their schedulers, every instruction shows).
                     if (row_ok) {
                         const size_t pitch = to_partial ? static_cast<size_t>(c.M) : static_cast<size_t>(ld_cd);
                         const size_t off0 = static_cast<size_t>(w.n0 + c0) * pitch + static_cast<size_t>(row);
                         float *dst = out + off0;
                         const float *csrc = gC + off0;
                         const int valid = min(4 * nvec, c.N - (w.n0 + c0));
+                        if (b_u == 0.0f) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < valid) {
-                                float v = a_u * __uint_as_float(r[j]);
-                                if (b_u != 0.0f) v += b_u * __ldg(csrc + static_cast<size_t>(j) * pitch);
-                                dst[static_cast<size_t>(j) * pitch] = v;
+                            for (int j = 0; j < 32; ++j) {
+                                if (j < 16 || wide) {
+                                    if (j < valid) *dst = a_u * __uint_as_float(r[j]);
+                                    dst += pitch;
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (j < 16 || wide) {
+                                    if (j < valid) *dst = a_u * __uint_as_float(r[j]) + b_u * __ldg(csrc);
+                                    dst += pitch;
+                                    csrc += pitch;
+                                }
                             }
                         }
                     }
@@ -822,6 +915,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 }
             }
             // accumulator slot drained: hand it back to the MMA thread
+            if (e == 0 && lane == 0) B200_TL(23);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -829,6 +923,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 else mbar_arrive(tmem_empty0 + 8u * acc);
             }
         }
+        if (e == 0 && lane == 0) B200_TL(24);
         if (c.epi_mode && lane == 0) tma_store_wait<0>();
         if (push_world > 0) __threadfence_system();  // this thread's peer stores are ordered before the flag below
         __syncwarp();
@@ -868,6 +963,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         tc_fence_after_sync();
         tmem_dealloc<CG>(tmem_base, static_cast<uint32_t>(tmem_cols));
     }
+    if (PROF && prof && tid == 0) prof[15] = static_cast<long long>(global_timer_ns());  // roles and teardown done
 }
 
 // D = alpha * sum_s partial[s] + beta * C, the second step of split-K. Slices are summed in
