@@ -121,6 +121,10 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
     st = lib().b200_gemm_default_params(base_m, N, K, dtype, C.byref(p))
     if st != OK:
         raise B200Error(st, "b200_gemm_default_params")
+    if want_swap == 0 and p.swap_ab:
+        # the base for this shape is a swapped (cluster) form: fall back to a plain one-CTA tile
+        p.swap_ab, p.cluster_reduce, p.split_k = 0, 0, 1
+        p.tile_m, p.tile_n, p.segment_dim_k, p.num_stages, p.epilogue, p.l2_hint = 128, 128, 64, 6, 1, 1
     if tile_keys and not want_pair and M > 128:
         p.l2_hint = 0          # the skinny-shape hint of the reduced-M base does not apply
     if want_pair and p.cta_group != 2:
@@ -132,6 +136,8 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
         if not hasattr(p, k):
             raise AttributeError(k)
         setattr(p, k, v)
+    if "split_k" in overrides and "cluster_reduce" not in overrides and p.cluster_reduce and p.split_k not in (2, 4, 8):
+        p.cluster_reduce = 0            # not a cluster size: the slices meet in the workspace
     # keep "shift off" consistent when only the tile was overridden
     if "bar_step_rows_b" not in overrides:
         p.bar_step_rows_b = p.tile_n

@@ -109,17 +109,20 @@ int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const 
 void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
     std::memset(p, 0, sizeof(*p));
     const bool pair = (M > 128) && (N % 256 == 0);
-    if (M <= 32) {
+    const int64_t n_tiles128 = (N + 127) / 128;
+    const bool few_tiles = K >= 4096 && n_tiles128 <= 74;
+    if (M <= 64 || (M <= 128 && K >= 4096 && n_tiles128 <= 37)) {
         // Decode shapes: the weights are the whole traffic. Swapped roles stage 128 weight rows and
-        // only 16 or 32 activation rows per K block; 128-deep K segments halve the barrier round
-        // trips per byte. One SM sustains a few tens of GB/s of TMA loads at DRAM latency, so when
-        // there are few tiles their K range is split over a cluster to put more SMs to work.
+        // only the activation rows there are per K block; 128-deep K segments halve the barrier
+        // round trips per byte. One SM sustains a few tens of GB/s of TMA loads at DRAM latency, so
+        // when there are few tiles their K range is split over a cluster to put more SMs to work
+        // (measured: 4 slices beat 2 even at 56 tiles; beyond 64 rows only the smallest N gain).
         p->swap_ab = 1;
-        p->tile_m = M <= 16 ? 16 : 32;
+        p->tile_m = static_cast<int>((M + 15) / 16 * 16);
         p->tile_n = 128;
         p->cta_group = 1;
-        p->segment_dim_k = 128;
-        p->num_stages = 5;
+        p->segment_dim_k = M <= 64 ? 128 : 64;
+        p->num_stages = M <= 32 ? 5 : (M <= 64 ? 4 : 5);
         p->num_producer_warps = 1;
         p->l2_hint = 1;
         p->bar_step_rows_a = p->tile_m;
@@ -127,9 +130,8 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
         p->tile_group_m = 8;
         p->num_consumer_warps = 4;
         p->split_k = 1;
-        const int64_t tiles = (N + 127) / 128;
-        if (K >= 4096 && tiles <= 74) {
-            p->split_k = 4;  // measured: 4 beats 2 even at 56 tiles (224 CTAs on 148 SMs)
+        if (few_tiles) {
+            p->split_k = 4;
             p->cluster_reduce = 1;
         }
         return;

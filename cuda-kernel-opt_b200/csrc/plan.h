@@ -144,8 +144,8 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     if (user.cluster_reduce != 0 && user.cluster_reduce != 1) return p;
     if (user.cluster_reduce) {
         // K slices as the CTAs of a cluster: portable cluster sizes, a transposed accumulator of at
-        // most 64 columns (32 KiB of fp32 per CTA) staged in shared memory for the peers to read.
-        if (!p.swap || (p.split_k != 2 && p.split_k != 4 && p.split_k != 8) || q.tile_n > 64) return p;
+        // most 128 columns (64 KiB of fp32 per CTA) staged in shared memory for the peers to read.
+        if (!p.swap || (p.split_k != 2 && p.split_k != 4 && p.split_k != 8) || q.tile_n > 128) return p;
         p.cluster_reduce = 1;
     }
 

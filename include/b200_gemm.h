@@ -90,7 +90,7 @@ typedef struct b200_gemm_params {
                        written to D transposed (coalesced along N). Then tile_n is 64 or 128 and tile_m a
                        multiple of 16 in [16, 256]; the bar_step fields follow their operands; needs
                        cta_group = 1 and tail_split = 0, and drains with plain stores. Same results as 0 */
-    int cluster_reduce; /* 1 (with swap_ab = 1, split_k 2, 4 or 8, tile_m <= 64) = the split_k slices of a tile run
+    int cluster_reduce; /* 1 (with swap_ab = 1, split_k 2, 4 or 8, tile_m <= 128) = the split_k slices of a tile run
                        as the CTAs of one thread-block cluster and are summed through distributed shared
                        memory, in slice order: no workspace, no second kernel, same bits as the workspace
                        form. 0 = slices meet in the workspace */

@@ -145,7 +145,7 @@ def test_swapped_roles_and_cluster_reduce_domain(pkg):
         assert ok(**dict(sw, split_k=s_, cluster_reduce=1)) == pkg.OK
     assert ok(**dict(sw, split_k=3, cluster_reduce=1)) == pkg.INVALID_CONFIG            # cluster sizes 2, 4, 8
     assert ok(**dict(sw, split_k=1, cluster_reduce=1)) == pkg.INVALID_CONFIG
-    assert ok(**dict(sw, tile_m=80, bar_step_rows_a=80, split_k=2, cluster_reduce=1)) == pkg.INVALID_CONFIG  # > 64 columns
+    assert ok(**dict(sw, tile_m=144, bar_step_rows_a=144, split_k=2, cluster_reduce=1)) == pkg.INVALID_CONFIG  # > 128 columns
     assert ok(tile_m=128, tile_n=128, split_k=2, cluster_reduce=1) == pkg.INVALID_CONFIG    # needs swap_ab
     assert pkg.workspace_bytes(16, 4096, 4096, P(pkg, **dict(sw, split_k=4))) == 4 * 16 * 4096 * 4
     assert pkg.workspace_bytes(16, 4096, 4096, P(pkg, **dict(sw, split_k=4, cluster_reduce=1))) == 0

@@ -187,7 +187,7 @@ def test_swapped_roles_and_cluster_reduce(pkg, cuda, oracle):
         mode = rnd.random()
         if mode < 0.25:
             ov["split_k"] = rnd.randint(2, 6)
-        elif mode < 0.7 and tile_m <= 64:
+        elif mode < 0.7 and tile_m <= 128:
             ov.update(split_k=rnd.choice([2, 4, 8]), cluster_reduce=1)
         elif mode < 0.85:
             step = rnd.choice([s_ for s_ in (16, 32, 64) if tile_m % s_ == 0 and tile_m // s_ <= 16] or [tile_m])
