@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM traffic of one launch of the dominant kernel from an ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum); see profiles/. None where no capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"c3_8192_f16": 1373173160, "c4_m16_bf16": 475586560, "c4_m128_bf16": 475299584}
+NCU_TRAFFIC_BYTES = {"c3_8192_f16": 1373173160, "c4_m16_bf16": 472698283, "c4_m128_bf16": 473866240}
 
 WORKLOADS = {
     # name: (M, N, K, dtype, seed, dist_a, dist_b, bound)
@@ -236,6 +236,10 @@ def run_ours(args):
     splitk_ranks = args.workload.startswith("c5") and world > 1
     nshard = args.workload.startswith("c4")
 
+    # --shard-of G on one GPU: time rank 0's shard of a G-GPU run of an N-sharded workload alone
+    shard_world = args.shard_of if (args.shard_of > 1 and world == 1 and nshard) else world
+    library = args.impl == "library"       # torch.matmul (cuBLAS) in the same harness, for scale only
+
     # ---- placement (see cuda-kernel-opt_b200/shard.py)
     if splitk_ranks:                         # K split over ranks, fp32 partials reduce-scattered by rows
         ks = shard.k_shard(K, world, rank, 64)
@@ -243,9 +247,9 @@ def run_ours(args):
         a_begin, b_begin, a_pitch = ks.begin, ks.begin, K
         scaling, parallelism = "strong", f"split-K x{world} + NCCL reduce-scatter"
     elif nshard:                             # rows of B^T (weights) split over ranks, activations replicated
-        ns = shard.n_shard(N, world, rank, 256)
+        ns = shard.n_shard(N, shard_world, rank, 256)
         m_loc, n_loc, k_loc = M, ns.size, K
-        scaling, parallelism = "strong", f"N-shard x{world}, no collective"
+        scaling, parallelism = "strong", f"N-shard x{shard_world}, no collective" + (" (rank 0's shard alone on one GPU)" if shard_world != world else "")
     elif args.scaling == "strong":           # rows of A split over ranks, B^T replicated
         ms = shard.m_shard(M, world, rank, 256)
         m_loc, n_loc, k_loc = ms.size, N, K
@@ -269,7 +273,7 @@ def run_ours(args):
         del tmp
     else:
         a_row0 = (rank * M if (scaling == "weak") else (shard.m_shard(M, world, rank, 256).begin if not nshard else 0))
-        b_row0 = shard.n_shard(N, world, rank, 256).begin if nshard else 0
+        b_row0 = shard.n_shard(N, shard_world, rank, 256).begin if nshard else 0
         pkg.fill_device(A, seed, 1, int(da[0]), float(da[1]), begin=a_row0 * K)
         pkg.fill_device(Bt, seed, 2, int(db[0]), float(db[1]), begin=b_row0 * K)
     D = torch.empty((m_loc, n_loc), dtype=torch.float32, device=dev)
@@ -300,6 +304,8 @@ def run_ours(args):
         a_i, b_i = As[i % rot], Bts[i % rot]
         if fused:
             return push.gemm_reduce_scatter(a_i, b_i, D_rows, p, workspace=ws if ws_bytes else None)
+        if library:
+            return torch.matmul(a_i, b_i.t())
         pkg.gemm(a_i, b_i, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
         if splitk_ranks:
             return shard.reduce_scatter_rows(D)
@@ -350,7 +356,10 @@ def run_ours(args):
                 push.gemm_reduce_scatter(a_i, b_i, D_rows, p, workspace=ws if ws_bytes else None)
                 e1.record()
             else:
-                pkg.gemm(a_i, b_i, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
+                if library:
+                    torch.matmul(a_i, b_i.t())
+                else:
+                    pkg.gemm(a_i, b_i, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
                 e1.record()                                # end of the GEMM kernel(s) of this step
                 if splitk_ranks:
                     shard.reduce_scatter_rows(D)
@@ -374,6 +383,8 @@ def run_ours(args):
 
     job_flops = flops_of(M, N, K) * (world if scaling == "weak" else 1)
     job_bytes = bytes_of(M, N, K) * (world if scaling == "weak" else 1)
+    if shard_world != world:                 # one shard alone: report the shard's own rate
+        job_flops, job_bytes = flops_of(m_loc, n_loc, k_loc), bytes_of(m_loc, n_loc, k_loc)
     if bound == "tensor":
         value, unit = job_flops / (ms_per_step * 1e-3) / 1e12, "TFLOPS"
     else:
@@ -398,7 +409,7 @@ def run_ours(args):
 
     # ---- end to end: the host-buffer call of the C ABI (H2D of A, B^T, launch, D2H of D, sync)
     e2e = None
-    if not splitk_ranks and not args.no_e2e:
+    if not splitk_ranks and not args.no_e2e and not library:
         hA = torch.empty((m_loc, k_loc), dtype=tdt).pin_memory()
         hB = torch.empty((n_loc, k_loc), dtype=tdt).pin_memory()
         hD = torch.empty((m_loc, n_loc), dtype=torch.float32).pin_memory()
@@ -428,7 +439,7 @@ def run_ours(args):
     # ---- optional: per-role cycle counters of CTA 0 from one extra launch (tracing hook of the library)
     roles = None
     if args.role_counters and rank == 0:
-        prof = torch.zeros((2, 16), dtype=torch.int64, device=dev)
+        prof = torch.zeros((2, pkg.profile_slots()), dtype=torch.int64, device=dev)
         pkg.lib().b200_set_profile_buffer(prof.data_ptr(), 2)
         pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
         torch.cuda.synchronize()
@@ -462,6 +473,8 @@ def run_ours(args):
         else:
             wmma = {"unavailable": "oracle/_ref/ref_wmma_async not built (make -C oracle wmma, needs the reference tree)"}
 
+    if library:
+        e2e = None
     if rank == 0:
         line = {
             "metric": METRIC if args.workload == "c3_8192_f16" else f"{unit} on {args.workload}",
@@ -478,6 +491,10 @@ def run_ours(args):
             "gpu_launches": args.steps * launches_per_step,
             "per_gpu_tflops": (value / world) if unit == "TFLOPS" else None,
         }
+        if library:
+            line["impl"] = "library (torch.matmul, for scale: not this repository's kernel)"
+            line["gpu_launches"] = 0
+            line["config"].pop("params", None)
         if roles:
             line["role_counters"] = roles
         if wmma:
@@ -506,7 +523,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "reference", "library"], default="ours",
+                    help="library: torch.matmul in this harness, a number for scale (single-process workloads only)")
+    ap.add_argument("--shard-of", type=int, default=0, help="one GPU: time rank 0's shard of a G-GPU run of an N-sharded workload")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c3_8192_f16")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--exchange", choices=["nccl", "fused"], default="fused",

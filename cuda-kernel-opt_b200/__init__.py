@@ -27,7 +27,7 @@ EXPORTS = [
     "b200_gemm_default_params", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
     "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
     "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
-    "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
+    "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_profile_slots", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
     "b200_fill_u16_device", "b200_fill_f32_device", "b200_fill_u16_host", "b200_fill_f32_host",
 ]
 
@@ -88,6 +88,8 @@ def lib():
         L.b200_set_wait_budget_ns.restype = None
         L.b200_set_profile_buffer.argtypes = [vp, C.c_int]
         L.b200_set_profile_buffer.restype = None
+        L.b200_profile_slots.argtypes = []
+        L.b200_profile_slots.restype = C.c_int
         L.b200_status_string.argtypes = [C.c_int]
         L.b200_status_string.restype = C.c_char_p
         L.b200_fill_u16_device.argtypes = [vp, i64, i64, u64, u64, C.c_int, f32, C.c_int, vp]
@@ -215,6 +217,11 @@ def device_status(stream=None):
 
 def set_wait_budget_ns(ns: int) -> None:
     lib().b200_set_wait_budget_ns(ns)
+
+
+def profile_slots() -> int:
+    """int64 slots per CTA of the profile buffer (16; 32 in a -DB200_TIMELINE build)."""
+    return lib().b200_profile_slots()
 
 
 def num_sms() -> int:

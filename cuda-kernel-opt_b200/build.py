@@ -38,12 +38,14 @@ def needs_build() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, defines=()) -> str:
+def build(force: bool = False, verbose: bool = False, defines=(), out: str | None = None) -> str:
     """defines: extra -D flags for diagnostic builds (-DB200_TIMELINE: %globaltimer stamps of set-up and
-    role milestones in a 32-slot profile buffer); such a build replaces the library until the next --force."""
-    if not force and not needs_build():
+    role milestones in a 32-slot profile buffer). out: write the library elsewhere (a diagnostic build
+    beside the normal one; load it with B200_GEMM_LIB=<path>)."""
+    if out is None and not defines and not force and not needs_build():
         return LIB
-    cmd = [_nvcc()] + NVCC_FLAGS + list(defines) + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    target = out or LIB
+    cmd = [_nvcc()] + NVCC_FLAGS + list(defines) + (["-Xptxas", "-v"] if verbose else []) + ["-o", target] + [os.path.join(CSRC, s) for s in SOURCES]
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a wrapper compiler; nvcc needs the system g++
     if os.path.exists("/usr/bin/g++"):
@@ -53,8 +55,9 @@ def build(force: bool = False, verbose: bool = False, defines=()) -> str:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building libb200gemm.so")
-    return LIB
+    return target
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=[a for a in sys.argv[1:] if a.startswith("-D")]))
+    _out = sys.argv[sys.argv.index("--out") + 1] if "--out" in sys.argv else None
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=[a for a in sys.argv[1:] if a.startswith("-D")], out=_out))

@@ -634,6 +634,8 @@ void b200_set_profile_buffer(void *device_ptr, int blocks) {
     g_prof_blocks.store(device_ptr ? blocks : 0);
 }
 
+int b200_profile_slots(void) { return profile_slots(); }
+
 const char *b200_status_string(int status) {
     switch (status) {
         case B200_OK: return "ok";

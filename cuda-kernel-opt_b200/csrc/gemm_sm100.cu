@@ -1212,6 +1212,8 @@ KernelFn pick_kernel(int cta_group, bool simple, bool prof) {
 }
 }  // namespace
 
+int profile_slots() { return kProfSlots; }
+
 int prepare_kernels() {
     for (int cg = 1; cg <= 2; ++cg)
         for (int simple = 0; simple < 2; ++simple)

@@ -69,5 +69,6 @@ int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int sp
 // Second step of the tail split: D tile = alpha * sum of its K slices + beta * C for the r tail tiles.
 int launch_tail_reduce(const GemmArgs &args, cudaStream_t stream);
 int prepare_kernels();  // opt-in shared memory size; once per device
+int profile_slots();    // int64 slots per CTA of the profile buffer (16; 32 in a -DB200_TIMELINE build)
 
 }  // namespace b200

@@ -196,12 +196,16 @@ int b200_device_status(void *stream, int info[4]);
 void b200_set_wait_budget_ns(uint64_t ns);
 
 /* Tracing hook: when device_ptr is non-null, the first `blocks` CTAs of every later GEMM launch
- * write 16 int64 cycle counters each (clock64) into it: [0..2] A-producer {cycles waiting for free
+ * write b200_profile_slots() int64 counters each (clock64 cycles) into it: [0..2] A-producer {cycles waiting for free
  * stages, cycles in loop, stages filled}, [3..5] the same for a separate B^T producer, [6..9] MMA
  * thread {cycles waiting for data, cycles waiting for a free accumulator, cycles in loop, stages},
  * [10..12] first epilogue warp {cycles waiting for a finished tile, cycles in loop, tiles}. The
  * reference only times whole launches with CUDA events (matmul_shmem_tc_async.cu:787-795). */
 void b200_set_profile_buffer(void *device_ptr, int blocks);
+/* int64 slots per CTA in that buffer: 16, with [13..15] = %globaltimer (ns) at kernel entry, after
+ * set-up and at exit. A diagnostic build of the library (-DB200_TIMELINE) has 32: [16..31] are
+ * %globaltimer stamps of set-up and role milestones (cuda-kernel-opt_b200/timeline.py prints them). */
+int b200_profile_slots(void);
 
 const char *b200_status_string(int status);
 int b200_last_cuda_error(void); /* cudaError_t of the last failed CUDA call on this thread */
