@@ -16,12 +16,16 @@ def tune_mod():
 
 def test_candidates_are_valid_or_filtered(pkg):
     t = tune_mod()
-    for shape in ((8192, 8192, 8192), (16, 28672, 8192), (2048, 2048, 262144), (1024, 1024, 1024)):
+    for shape in ((8192, 8192, 8192), (16, 28672, 8192), (128, 3584, 8192), (2048, 2048, 262144), (1024, 1024, 1024)):
         cands = t.candidates(*shape)
         assert len(cands) >= 8 and len({t.key_of(c) for c in cands}) == len(cands)
         valid = [c for c in cands if pkg.validate(*shape, pkg.F16, pkg.default_params(*shape, pkg.F16, **c)) == pkg.OK]
         assert len(valid) >= len(cands) // 2, shape
     assert any(c.get("split_k", 1) > 1 for c in t.candidates(2048, 2048, 262144))      # too few tiles: split-K offered
+    skinny = t.candidates(16, 3584, 8192)
+    assert any(c.get("swap_ab") and c.get("cluster_reduce") for c in skinny)            # decode shard: cluster over K offered
+    assert all(pkg.validate(16, 3584, 8192, pkg.BF16, pkg.default_params(16, 3584, 8192, pkg.BF16, **c)) == pkg.OK
+               for c in skinny if c.get("swap_ab"))
     assert not any(c.get("split_k", 1) > 1 for c in t.candidates(8192, 8192, 8192))
 
 
