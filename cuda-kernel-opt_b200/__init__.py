@@ -37,7 +37,7 @@ class Params(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "tile_m", "tile_n", "segment_dim_k", "bar_steps_a", "bar_steps_b", "bar_step_rows_a", "bar_step_rows_b",
         "tile_group_m", "num_stages", "num_producer_warps", "num_consumer_warps", "num_sms", "cta_group", "split_k",
-        "epilogue", "l2_hint", "diagnostic", "k_order", "tail_split", "swap_ab", "cluster_reduce")]
+        "epilogue", "l2_hint", "diagnostic", "k_order", "tail_split", "swap_ab", "cluster_reduce", "overlap_launch")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}

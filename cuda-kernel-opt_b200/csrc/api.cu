@@ -134,6 +134,9 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
             p->split_k = 4;
             p->cluster_reduce = 1;
         }
+        // Few CTAs and a short kernel: let set-up overlap the previous kernel of the stream (measured
+        // -4 % on the 4- and 8-GPU shards of the decode shape; +6 % when all SMs are busy for 70 us).
+        p->overlap_launch = n_tiles128 * p->split_k < 148 ? 1 : 0;
         return;
     }
     if (pair) {
@@ -182,6 +185,9 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
     // drain through swizzled shared memory and TMA stores: 3x shorter per tile than scattered 128-bit
     // stores (6.2 k vs 19 k cycles for 128 x 256 fp32), +2 % on 8192^3
     p->epilogue = 1;
+    // a grid that leaves SMs idle is a short kernel: overlap its set-up with the previous kernel's tail
+    const int64_t ctas = ((M + p->tile_m - 1) / p->tile_m) * ((N + p->tile_n - 1) / p->tile_n) * p->cta_group;
+    p->overlap_launch = ctas < 148 ? 1 : 0;
 }
 
 struct PushTarget {  // split-K over GPUs with the exchange fused into the epilogue; world == 0: off
@@ -326,6 +332,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.debug_flags = user->diagnostic;
     a.l2_hint = user->l2_hint;
     a.k_order = user->k_order;
+    a.overlap_launch = user->overlap_launch ? 1 : 0;
 
     const int le = launch_gemm(p, a, stream);
     if (le != 0) return fail_cuda(static_cast<cudaError_t>(le));

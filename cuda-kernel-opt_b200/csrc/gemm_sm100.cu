@@ -292,6 +292,13 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    if (g.overlap_launch) {
+        // Everything above touched only this CTA's shared and tensor memory, so it may run while the
+        // previous kernel of the stream is still finishing. Let the next kernel do the same, then wait
+        // for the previous one before the first global access (operand loads, C, D, workspace).
+        griddep_launch_dependents();
+        griddep_wait();
+    }
 
     if (PROF && prof && tid == 0) prof[14] = static_cast<long long>(global_timer_ns());  // set-up done, roles start
 
@@ -1238,7 +1245,7 @@ int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
     cfg.blockDim = dim3(static_cast<unsigned>(p.threads), 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(p.smem_bytes);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cfg.attrs = nullptr;
     cfg.numAttrs = 0;
     const int cluster = p.cta_group == 2 ? 2 : (p.cluster_reduce ? p.split_k : 1);
@@ -1251,6 +1258,12 @@ int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
         cfg.numAttrs = 1;
     }
     const bool simple = (p.a_bars == 1 && p.b_bars == 1 && p.a_boxes == 1 && p.b_priv == 0 && p.b_res_chunks == 1);
+    if (args.overlap_launch) {
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs += 1;
+    }
     const KernelFn fn = pick_kernel(p.cta_group, simple, args.prof != nullptr);
     if (p.cluster_reduce) {
         // A persistent grid wants every cluster resident at once: ask how many clusters of this

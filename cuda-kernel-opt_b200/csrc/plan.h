@@ -140,6 +140,7 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     if (q.epilogue != 0 && q.epilogue != 1) return p;
     if (q.l2_hint < 0 || q.l2_hint > 3) return p;
     if (q.k_order != 0 && q.k_order != 1) return p;
+    if (q.overlap_launch != 0 && q.overlap_launch != 1) return p;
     p.epi_mode = q.epilogue;
     if (user.cluster_reduce != 0 && user.cluster_reduce != 1) return p;
     if (user.cluster_reduce) {

@@ -59,6 +59,13 @@ __device__ __forceinline__ void cluster_wait() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Programmatic dependent launch. launch_dependents: the next kernel of the stream, if it was launched
+// with programmatic stream serialisation, may start its CTAs once every CTA of this grid has said
+// so (or exited). wait: returns when the grids this one depends on have completed and their
+// memory is visible; a no-op for a normally launched kernel.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

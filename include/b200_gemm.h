@@ -94,6 +94,12 @@ typedef struct b200_gemm_params {
                        as the CTAs of one thread-block cluster and are summed through distributed shared
                        memory, in slice order: no workspace, no second kernel, same bits as the workspace
                        form. 0 = slices meet in the workspace */
+    int overlap_launch; /* 1 = programmatic dependent launch: the kernel is launched with programmatic stream
+                       serialisation, runs its set-up (barriers, tensor memory, descriptor prefetch) while the
+                       previous kernel of the stream finishes, waits for that kernel (griddepcontrol.wait)
+                       before its first global access, and lets the next such launch start early in the same
+                       way. Results and ordering are those of a normal launch; for chains of short GEMMs
+                       (decode steps), where launch gaps are a visible share of a step. 0 = normal launch */
 } b200_gemm_params;
 
 /* Fills *p with the tuned default for the shape (what the reference's harness hard-codes per

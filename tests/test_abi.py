@@ -140,6 +140,7 @@ def test_swapped_roles_and_cluster_reduce_domain(pkg):
     assert ok(**dict(sw, cta_group=2)) == pkg.INVALID_CONFIG
     assert ok(**dict(sw, tail_split=1)) == pkg.INVALID_CONFIG
     assert ok(**dict(sw, swap_ab=2)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sw, overlap_launch=1)) == pkg.OK and ok(**dict(sw, overlap_launch=2)) == pkg.INVALID_CONFIG
     assert ok(**dict(sw, split_k=3)) == pkg.OK
     for s_ in (2, 4, 8):
         assert ok(**dict(sw, split_k=s_, cluster_reduce=1)) == pkg.OK

@@ -221,6 +221,56 @@ def test_swapped_roles_and_cluster_reduce(pkg, cuda, oracle):
         assert ok, (m, n, k, p.as_dict(), msg)
 
 
+def test_cuda_graph_capture_and_overlapped_launch(pkg, cuda, oracle):
+    """The call is capture-safe: a chain of GEMMs (plain, split-K with workspace, cluster split-K) recorded
+    into one CUDA graph and replayed gives the oracle's results; overlap_launch = 1 (programmatic dependent
+    launch: set-up overlaps the previous kernel) keeps results and ordering, in a graph and outside one."""
+    torch = cuda
+    cases = [(16, 1536, 2048, pkg.BF16, dict()), (300, 512, 1024, pkg.F16, dict()), (64, 768, 4096, pkg.BF16, dict(split_k=3)),
+             (16, 1024, 8192, pkg.BF16, dict(swap_ab=1, tile_m=16, split_k=4, cluster_reduce=1)), (520, 1024, 512, pkg.F16, dict(tile_m=256, tile_n=256, cta_group=2))]
+    for overlap in (0, 1):
+        prepared = []
+        for i, (m, n, k, dtype, ov) in enumerate(cases):
+            A, Bt, Cm = inputs(pkg, dtype, m, n, k, 4000 + i)
+            p = pkg.default_params(m, n, k, dtype, overlap_launch=overlap, **ov)
+            assert pkg.validate(m, n, k, dtype, p) == pkg.OK, p.as_dict()
+            need = pkg.workspace_bytes(m, n, k, p)
+            ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+            dA, dB, dC = to_device(torch, A, dtype), to_device(torch, Bt, dtype), torch.from_numpy(Cm).cuda()
+            D = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+            want = oracle.gemm(A, Bt, Cm, 0.5, 2.0, dtype)
+            prepared.append((dA, dB, dC, D, p, ws if need else None, want, k))
+
+        def chain():
+            for dA, dB, dC, D, p, ws, want, k in prepared:
+                pkg.gemm(dA, dB, dC, D, 0.5, 2.0, p, workspace=ws)
+            for dA, dB, dC, D, p, ws, want, k in prepared:        # the same chain again: write-after-write on every D
+                pkg.gemm(dA, dB, dC, D, 0.5, 2.0, p, workspace=ws)
+
+        def check(tag):
+            st, info = pkg.device_status()
+            assert st == pkg.OK, (tag, st, info)
+            for dA, dB, dC, D, p, ws, want, k in prepared:
+                ok, msg = tolerance_ok(D.cpu().numpy(), want, k, 3.5)
+                assert ok, (tag, overlap, p.as_dict(), msg)
+                D.fill_(float("nan"))
+
+        chain()
+        check("plain launches")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                chain()
+            for D in (x[3] for x in prepared):
+                D.fill_(float("nan"))
+            graph.replay()
+            graph.replay()
+        torch.cuda.synchronize()
+        check("graph replay")
+
+
 def test_bf16_and_scalars(pkg, cuda, oracle):
     A, Bt, Cm = inputs(pkg, pkg.BF16, 384, 512, 768, 61)
     for alpha, beta in ((1.0, 0.0), (0.5, 2.0), (-1.25, 0.75), (0.0, 1.0)):
