@@ -134,9 +134,10 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
             p->split_k = 4;
             p->cluster_reduce = 1;
         }
-        // Few CTAs and a short kernel: let set-up overlap the previous kernel of the stream (measured
-        // -4 % on the 4- and 8-GPU shards of the decode shape; +6 % when all SMs are busy for 70 us).
-        p->overlap_launch = n_tiles128 * p->split_k < 148 ? 1 : 0;
+        // A short kernel: let set-up overlap the previous kernel of the stream (measured -4 % on the
+        // 4- and 8-GPU shards of the decode shape, 117 and 59 MB of weights; +6 % on the whole one,
+        // 470 MB, where all SMs are busy for 70 us).
+        p->overlap_launch = (N * K * 2 <= 160000000) ? 1 : 0;
         return;
     }
     if (pair) {
