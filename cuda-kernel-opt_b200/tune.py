@@ -32,12 +32,14 @@ def candidates(M: int, N: int, K: int) -> list[dict]:
         for seg_k in (64, 128):
             per_stage = (128 + tm) * seg_k * 2
             for stages in sorted({max(2, min(10, 200000 // per_stage)), max(2, min(10, 200000 // per_stage) - 1)}):
-                base = dict(swap_ab=1, tile_m=tm, tile_n=128, segment_dim_k=seg_k, num_stages=stages, l2_hint=1)
+                # every field the shape's default may set is spelled out, so a candidate is what it says
+                base = dict(swap_ab=1, tile_m=tm, tile_n=128, segment_dim_k=seg_k, num_stages=stages, l2_hint=1,
+                            split_k=1, cluster_reduce=0)
                 out.append(base)
                 if n_tiles < 148 and K >= 2048:
                     for s in (2, 4, 8):
                         out.append(dict(base, split_k=s, cluster_reduce=1))
-                        out.append(dict(base, split_k=s))
+                        out.append(dict(base, split_k=s, cluster_reduce=0))
     tiles = []
     if M > 128:
         tiles += [dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=256, tile_n=128, cta_group=2)]
