@@ -24,7 +24,7 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 
 # every symbol include/b200_gemm.h declares
 EXPORTS = [
-    "b200_gemm_default_params", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
+    "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
     "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
     "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_profile_slots", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
@@ -62,6 +62,7 @@ def lib():
         i64, f32, u64, vp, sz = C.c_int64, C.c_float, C.c_uint64, C.c_void_p, C.c_size_t
         PP = C.POINTER(Params)
         L.b200_gemm_default_params.argtypes = [i64, i64, i64, C.c_int, PP]
+        L.b200_gemm_default_params_plain.argtypes = [i64, i64, i64, C.c_int, PP]
         L.b200_gemm_validate.argtypes = [i64, i64, i64, C.c_int, PP]
         L.b200_gemm_smem_bytes.argtypes = [C.c_int, PP]
         L.b200_gemm_smem_bytes.restype = i64
@@ -113,27 +114,26 @@ def default_params(M: int, N: int, K: int, dtype: int = F16, **overrides) -> Par
     override itself asks for the two-CTA pair, so that a partial override stays a valid whole."""
     p = Params()
     tile_keys = {"tile_m", "tile_n", "cta_group"} & set(overrides)
-    want_pair = overrides.get("cta_group", 0) == 2 or overrides.get("tile_m", 0) == 256 and not overrides.get("swap_ab")
+    want_pair = (overrides.get("cta_group", 0) == 2 or overrides.get("tile_m", 0) == 256) and not overrides.get("swap_ab")
     want_swap = overrides.get("swap_ab")
     if want_swap is None and (tile_keys or overrides.get("tail_split") or overrides.get("epilogue")):
         want_swap = 0          # tile_m / tile_n change meaning with swap_ab: an override names the plain form
     base_m = M if (not tile_keys or want_pair) else min(M, 128)
-    if want_swap == 0 and not want_pair:
-        base_m = max(base_m, 128) if M <= 128 else base_m   # the skinny default without swapped roles
-    st = lib().b200_gemm_default_params(base_m, N, K, dtype, C.byref(p))
+    fn = lib().b200_gemm_default_params_plain if want_swap == 0 else lib().b200_gemm_default_params
+    st = fn(base_m, N, K, dtype, C.byref(p))
     if st != OK:
         raise B200Error(st, "b200_gemm_default_params")
-    if want_swap == 0 and p.swap_ab:
-        # the base for this shape is a swapped (cluster) form: fall back to a plain one-CTA tile
-        p.swap_ab, p.cluster_reduce, p.split_k = 0, 0, 1
-        p.tile_m, p.tile_n, p.segment_dim_k, p.num_stages, p.epilogue, p.l2_hint = 128, 128, 64, 6, 1, 1
     if tile_keys and not want_pair and M > 128:
         p.l2_hint = 0          # the skinny-shape hint of the reduced-M base does not apply
     if want_pair and p.cta_group != 2:
         p.tile_m, p.tile_n, p.cta_group, p.num_stages, p.l2_hint = 256, 256, 2, 6, 3
-    if want_swap == 1 and not p.swap_ab:
-        p.tile_m, p.tile_n, p.cta_group, p.epilogue = min(256, -(-M // 16) * 16), 128, 1, 0
+    if want_swap == 1 and (not p.swap_ab or overrides.get("cta_group", p.cta_group) != p.cta_group):
+        pair_swap = overrides.get("cta_group", 0) == 2     # swapped pair: 256 weight rows per tile, tile_m a multiple of 32
+        gran = 32 if pair_swap else 16
+        p.swap_ab, p.tile_m, p.tile_n = 1, min(256, -(-M // gran) * gran), 256 if pair_swap else 128
+        p.cta_group, p.epilogue, p.segment_dim_k = 2 if pair_swap else 1, 0, 64
         p.num_stages, p.num_producer_warps = 8, 1
+        p.split_k, p.cluster_reduce = 1, 0
     for k, v in overrides.items():
         if not hasattr(p, k):
             raise AttributeError(k)

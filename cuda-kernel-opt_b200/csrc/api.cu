@@ -106,12 +106,12 @@ int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const 
 // Tuned defaults. Large problems use the two-CTA pair (256 x 256 tile, each CTA stages 128 rows of
 // A and 128 rows of B^T per K block: half the L2-to-shared traffic per flop of a one-CTA
 // 128 x 256 tile); small or skinny ones a one-CTA tile with the widest N that divides.
-void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
+void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool allow_swap = true) {
     std::memset(p, 0, sizeof(*p));
     const bool pair = (M > 128) && (N % 256 == 0);
     const int64_t n_tiles128 = (N + 127) / 128;
     const bool few_tiles = K >= 4096 && n_tiles128 <= 74;
-    if (M <= 64 || (M <= 128 && K >= 4096 && n_tiles128 <= 37)) {
+    if (allow_swap && (M <= 64 || (M <= 128 && K >= 4096 && n_tiles128 <= 37))) {
         // Decode shapes: the weights are the whole traffic. Swapped roles stage 128 weight rows and
         // only the activation rows there are per K block; 128-deep K segments halve the barrier
         // round trips per byte. One SM sustains a few tens of GB/s of TMA loads at DRAM latency, so
@@ -138,6 +138,25 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p) {
         // 4- and 8-GPU shards of the decode shape, 117 and 59 MB of weights; +6 % on the whole one,
         // 470 MB, where all SMs are busy for 70 us).
         p->overlap_launch = (N * K * 2 <= 160000000) ? 1 : 0;
+        return;
+    }
+    if (allow_swap && M > 64 && M <= 128 && n_tiles128 >= 112) {
+        // 65 - 128 activation rows against many weight rows: the swapped two-CTA pair. Each CTA stages
+        // 128 weight rows and half of the activation rows per K block (measured 2 - 3 % over the plain
+        // 128 x 224 tile at N = 14336 and 28672; below that the plain narrow tiles fill more SMs).
+        p->swap_ab = 1;
+        p->tile_m = static_cast<int>((M + 31) / 32 * 32);
+        p->tile_n = 256;
+        p->cta_group = 2;
+        p->segment_dim_k = 64;
+        p->num_stages = 8;
+        p->num_producer_warps = 1;
+        p->l2_hint = 1;
+        p->bar_step_rows_a = p->tile_m;
+        p->bar_step_rows_b = p->tile_n;
+        p->tile_group_m = 8;
+        p->num_consumer_warps = 4;
+        p->split_k = 1;
         return;
     }
     if (pair) {
@@ -391,6 +410,13 @@ int b200_gemm_default_params(int64_t M, int64_t N, int64_t K, int dtype, b200_ge
     if (!p) return B200_INVALID_POINTER;
     (void)dtype;
     default_params(M, N, K, p);
+    return B200_OK;
+}
+
+int b200_gemm_default_params_plain(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p) {
+    if (!p) return B200_INVALID_POINTER;
+    (void)dtype;
+    default_params(M, N, K, p, false);
     return B200_OK;
 }
 

@@ -43,7 +43,7 @@ constexpr int kProfSlots = 32;
 constexpr int kProfSlots = 16;
 #define B200_TL(slot) do { } while (0)
 #endif
-constexpr int kMaxThreads = 544;  // (8 producer + 1 MMA + 8 epilogue warps) * 32
+constexpr int kMaxThreads = 512;  // (7 producer + 1 MMA + 8 epilogue warps) * 32
 
 struct Unit {
     int m0, n0, slice, seg_begin, seg_end;
@@ -168,14 +168,15 @@ __device__ __forceinline__ bool wait_all(uint32_t bar, uint32_t parity, long lon
 }
 
 template <int CG>
-__device__ __forceinline__ void commit_to(uint32_t bar) {
+__device__ __forceinline__ void commit_to(uint32_t bar, uint16_t pair_mask) {
     if constexpr (CG == 1) {
         umma_commit<1>(bar);
     } else {
-        // Both CTAs of the pair hold a barrier at this offset; complete the two of them.
+        // Both CTAs of the pair hold a barrier at this offset; complete the two of them
+        // (pair_mask: the pair's two ranks in the cluster).
         asm volatile(
             "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
-            "h"(static_cast<uint16_t>(3))
+            "h"(pair_mask)
             : "memory");
     }
 }
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     c.b_res_chunks = g.b_res_chunks; c.b_bars = g.b_bars; c.acc_cols = g.acc_cols; c.mma_m = g.mma_m;
     c.epi_mode = g.epi_mode; c.epi_warps = g.epi_warps; c.M = g.M; c.N = g.N;
     c.idesc_chunk = g.idesc_chunk; c.idesc_res = g.idesc_res; c.budget = g.wait_budget_cycles;
-    c.cl_split = (CG == 1 && g.cl_split > 1) ? g.cl_split : 1;
+    c.cl_split = g.cl_split > 1 ? g.cl_split : 1;
     c.cl_rank = 0;
     const int off_bars = g.off_bars, off_tmem_ptr = g.off_tmem_ptr, off_epi = g.off_epi;
     const int tmem_cols = g.tmem_cols;
@@ -227,12 +228,17 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int lane = tid & 31;
     const int mma_warp = P;
-    const uint32_t rank = (CG == 2) ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
+    // A cluster is CG x cl_split CTAs: pairs of consecutive ranks form the tcgen05 groups (CG == 2),
+    // the pairs (or single CTAs) of a cluster take the K slices of one tile (cl_split > 1).
     const bool clustered = (CG == 2) || c.cl_split > 1;
+    const uint32_t ctarank = clustered ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
+    const uint32_t rank = (CG == 2) ? (ctarank & 1u) : 0u;            // rank inside the pair
+    const uint32_t leader_cta = (CG == 2) ? (ctarank & ~1u) : ctarank;  // cluster rank of the pair's leader
+    const uint16_t pair_mask = static_cast<uint16_t>(3u << leader_cta);
     c.cl_seg_begin = 0;
     c.cl_seg_end = c.num_segs;
-    if (CG == 1 && c.cl_split > 1) {
-        c.cl_rank = __shfl_sync(0xffffffffu, static_cast<int>(cluster_ctarank()), 0);
+    if (c.cl_split > 1) {
+        c.cl_rank = static_cast<int>(ctarank) / CG;
         c.cl_seg_begin = static_cast<int>(static_cast<unsigned>(c.cl_rank) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.cl_split));
         c.cl_seg_end = static_cast<int>(static_cast<unsigned>(c.cl_rank + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.cl_split));
     }
@@ -321,7 +327,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint32_t a_kb_bytes = static_cast<uint32_t>(c.cta_rows_a * kSwizzleBytes);
             const uint32_t b_kb_bytes = static_cast<uint32_t>((c.tile_n / CG) * kSwizzleBytes);
             const uint32_t my_bytes = static_cast<uint32_t>(c.kblocks * CG) * ((do_a ? a_kb_bytes : 0u) + (do_b ? b_kb_bytes : 0u));
-            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
+            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, leader_cta), 0) : bars;
             const bool arm = issuer && rank == 0;
             const int hint = g.l2_hint;
             // the hint names the caller's operands; with swapped roles map_a holds B^T and map_b holds A
@@ -440,7 +446,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         da += a_kb_step;
                         db += b_kb_step;
                     }
-                    if (issuer) commit_to<CG>(sb + empty_a_off);
+                    if (issuer) commit_to<CG>(sb + empty_a_off, pair_mask);
                     ++it;
                     a_desc += stage_step;
                     b_desc += stage_step;
@@ -454,7 +460,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     }
                 }
                 if (!ok) break;
-                if (issuer) commit_to<CG>(tmem_full0 + 8u * acc);
+                if (issuer) commit_to<CG>(tmem_full0 + 8u * acc, pair_mask);
                 if (lane == 0) B200_TL(21);
             }
             if (PROF && prof && lane == 0) {
@@ -477,7 +483,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const bool issuer = elect_one();
             const bool arm = issuer && rank == 0;
             const bool issue = issuer && !(dbg & 2);
-            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, 0), 0) : bars;
+            const uint32_t bars_leader = (CG == 2) ? __shfl_sync(0xffffffffu, mapa_shared(bars, leader_cta), 0) : bars;
             const uint32_t a_box_bytes = static_cast<uint32_t>(c.a_box_rows * kSwizzleBytes);
             const uint32_t a_kb_bytes = static_cast<uint32_t>(c.cta_rows_a * kSwizzleBytes);
             const uint32_t a_priv_tx = (dbg & 2) ? 0u : static_cast<uint32_t>(c.kblocks * CG) * a_box_bytes;
@@ -649,12 +655,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                             da += a_kb_step;
                             db += b_kb_step;
                         }
-                        if (!merged && issuer) commit_to<CG>(sb + empty_b_off + 8u * t);
+                        if (!merged && issuer) commit_to<CG>(sb + empty_b_off + 8u * t, pair_mask);
                         sub_desc += b_sub_step;
                         d_addr += static_cast<uint32_t>(c.chunk_n);
                     }
                     if (!ok) break;
-                    if (issuer) commit_to<CG>(sb + empty_a_off);
+                    if (issuer) commit_to<CG>(sb + empty_a_off, pair_mask);
                     later_seg = 1;
                     ++it;
                     a_desc += stage_step;
@@ -669,7 +675,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     }
                 }
                 if (!ok) break;
-                if (issuer) commit_to<CG>(tmem_full0 + 8u * acc);
+                if (issuer) commit_to<CG>(tmem_full0 + 8u * acc, pair_mask);
             }
             if (PROF && prof && lane == 0) {
                 prof[6] = t_full;
@@ -691,7 +697,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             col_begin = half ? min(mid, c.tile_n) : 0;
             col_end = half ? c.tile_n : min(mid, c.tile_n);
         }
-        const uint32_t tmem_empty_leader = (CG == 2) ? mapa_shared(tmem_empty0, 0) : tmem_empty0;
+        const uint32_t tmem_empty_leader = (CG == 2) ? mapa_shared(tmem_empty0, leader_cta) : tmem_empty0;
         const uint32_t epi_buf = base + static_cast<uint32_t>(off_epi) + static_cast<uint32_t>(e) * 2u * 4096u;
         // row of the tile this thread drains: 128-row atoms map row r to lane r; 64-row atoms use
         // lanes 0-15 of each quarter (row 16 * quarter + lane).
@@ -771,8 +777,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 // barrier, and the arrivals release at cluster scope (cumulative): no fence needed.
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty0 + 8u * acc);  // accumulator slot back to the MMA thread
-                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane)));
+                if (lane == 0) {                                     // accumulator slot back to the MMA thread
+                    if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_leader + 8u * acc);
+                    else mbar_arrive(tmem_empty0 + 8u * acc);
+                }
+                // the peers of this CTA: the CTA with the same rank in its pair, in every slice of the cluster
+                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane * CG) + rank));
                 if (e == 0 && lane == 0) B200_TL(29);
                 // B: when all slices are staged, this CTA sums its share of the tile's columns over the
                 // cluster in slice order (the order of the workspace form) and writes D.
@@ -782,22 +792,21 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (e == 0 && lane == 0) B200_TL(30);
                 const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
                 const int my_end = min(c.tile_n, (c.cl_rank + 1) * per);
-                uint32_t peer[8];  // this thread's row of column 0 in every slice's CTA
+                // this thread's row of column 0, as an address in this CTA; mapa turns it into a peer's
+                const uint32_t my_row0 = pbuf + static_cast<uint32_t>(row_in_cta) * 4u;
+                // two columns per round: their 2 x cl_split remote loads are in flight together
+                for (int col0 = c.cl_rank * per + half; col0 < my_end; col0 += 2 * halves) {
+                    float v[2][8];
 #pragma unroll
-                for (int sl = 0; sl < 8; ++sl)
-                    peer[sl] = mapa_shared(pbuf + static_cast<uint32_t>(row_in_cta) * 4u, static_cast<uint32_t>(sl < c.cl_split ? sl : 0));
-                // four columns per round: their 4 x cl_split remote loads are in flight together
-                for (int col0 = c.cl_rank * per + half; col0 < my_end; col0 += 4 * halves) {
-                    float v[4][8];
-#pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
+                    for (int cc = 0; cc < 2; ++cc) {
                         const int col = col0 + cc * halves;
 #pragma unroll
                         for (int sl = 0; sl < 8; ++sl)
-                            if (sl < c.cl_split && col < my_end) v[cc][sl] = ld_shared_cluster_f32(peer[sl] + static_cast<uint32_t>(col) * 512u);
+                            if (sl < c.cl_split && col < my_end)
+                                v[cc][sl] = ld_shared_cluster_f32(mapa_shared(my_row0 + static_cast<uint32_t>(col) * 512u, static_cast<uint32_t>(sl * CG) + rank));
                     }
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
+                    for (int cc = 0; cc < 2; ++cc) {
                         const int col = col0 + cc * halves;
                         const int gcol = w.n0 + col;
                         if (col < my_end && gcol < c.N && row_ok) {
@@ -814,7 +823,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 }
                 __syncwarp();
                 if (e == 0 && lane == 0) B200_TL(31);
-                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane)));
+                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane * CG) + rank));
                 continue;
             }
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
@@ -1237,9 +1246,10 @@ int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
     int grid = p.grid;
     if (p.cluster_reduce) {
         // whole clusters only, and no more of them than there are tiles
-        grid -= grid % p.split_k;
-        if (grid > args.num_tiles * p.split_k) grid = args.num_tiles * p.split_k;
-        if (grid < p.split_k) grid = p.split_k;
+        const int per_tile = p.split_k * p.cta_group;
+        grid -= grid % per_tile;
+        if (grid > args.num_tiles * per_tile) grid = args.num_tiles * per_tile;
+        if (grid < per_tile) grid = per_tile;
     }
     cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
     cfg.blockDim = dim3(static_cast<unsigned>(p.threads), 1, 1);
@@ -1248,7 +1258,7 @@ int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
     cudaLaunchAttribute attr[2];
     cfg.attrs = nullptr;
     cfg.numAttrs = 0;
-    const int cluster = p.cta_group == 2 ? 2 : (p.cluster_reduce ? p.split_k : 1);
+    const int cluster = p.cta_group * (p.cluster_reduce ? p.split_k : 1);
     if (cluster > 1) {
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);

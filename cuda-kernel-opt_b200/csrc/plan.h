@@ -96,7 +96,7 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
         // Swapped operand roles: plan the transposed problem. The caller's tile_n (columns of D, rows of
         // B^T) becomes the 64/128-row side of the MMA, tile_m its N side; sub-tile barriers follow
         // their operands; the drain is plain stores (a transposed tile has no row-major TMA box).
-        if ((user.cta_group != 0 && user.cta_group != 1) || user.tail_split) return p;
+        if (user.tail_split) return p;
         if (user.epilogue != 0 && user.epilogue != 1) return p;
         q.tile_m = user.tile_n;
         q.tile_n = user.tile_m;
@@ -131,7 +131,9 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     if (q.num_producer_warps != 1 && q.num_producer_warps != 2 && q.num_producer_warps != 4 &&
         q.num_producer_warps != 8)
         return p;                                                      // async.cu:516
-    p.producer_warps = q.num_producer_warps;
+    // Only the first two producer warps issue copies; of eight requested, seven are launched, which keeps
+    // the block at 16 warps (512 threads: 128 registers per thread instead of 96).
+    p.producer_warps = q.num_producer_warps > 7 ? 7 : q.num_producer_warps;
     if (q.num_consumer_warps != 4 && q.num_consumer_warps != 8) return p;  // async.cu:517
     p.epi_warps = q.num_consumer_warps;
     p.threads = (p.producer_warps + 1 + p.epi_warps) * 32;
@@ -147,6 +149,7 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
         // K slices as the CTAs of a cluster: portable cluster sizes, a transposed accumulator of at
         // most 128 columns (64 KiB of fp32 per CTA) staged in shared memory for the peers to read.
         if (!p.swap || (p.split_k != 2 && p.split_k != 4 && p.split_k != 8) || q.tile_n > 128) return p;
+        if (cg * p.split_k > 8) return p;   // pairs x slices must fit a portable cluster
         p.cluster_reduce = 1;
     }
 

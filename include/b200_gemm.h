@@ -105,6 +105,9 @@ typedef struct b200_gemm_params {
 /* Fills *p with the tuned default for the shape (what the reference's harness hard-codes per
  * sweep, port_2.cu:1518-1564). dtype is B200_F16 or B200_BF16. */
 int b200_gemm_default_params(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p);
+/* The same without the swapped forms (swap_ab = 0): the tuned plain tile for the shape, the starting point
+ * for callers that set tile_m / tile_n / epilogue themselves in the reference's meaning. */
+int b200_gemm_default_params_plain(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p);
 
 /* Host-only validation: the reference's asserts (port_2.cu:1112-1123) and its harness's
  * shared-memory filter (port_2.cu:1229-1232) as a status. Touches no GPU. */

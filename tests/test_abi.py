@@ -137,7 +137,7 @@ def test_swapped_roles_and_cluster_reduce_domain(pkg):
     assert ok(**dict(sw, tile_n=64, bar_step_rows_b=64)) == pkg.OK
     assert ok(**dict(sw, tile_n=256, bar_step_rows_b=256)) == pkg.INVALID_CONFIG       # the MMA's M side is 64 or 128
     assert ok(**dict(sw, tile_m=24, bar_step_rows_a=24)) == pkg.INVALID_CONFIG          # its N side a multiple of 16
-    assert ok(**dict(sw, cta_group=2)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sw, cta_group=2)) == pkg.INVALID_CONFIG                             # a pair needs tile_n = 256
     assert ok(**dict(sw, tail_split=1)) == pkg.INVALID_CONFIG
     assert ok(**dict(sw, swap_ab=2)) == pkg.INVALID_CONFIG
     assert ok(**dict(sw, overlap_launch=1)) == pkg.OK and ok(**dict(sw, overlap_launch=2)) == pkg.INVALID_CONFIG
@@ -159,8 +159,14 @@ def test_swapped_roles_and_cluster_reduce_domain(pkg):
     assert (d.swap_ab, d.tile_m, d.tile_n, d.split_k) == (1, 16, 128, 1) and pkg.validate(16, 28672, 8192, pkg.BF16, d) == pkg.OK
     d = pkg.default_params(16, 3584, 8192, pkg.BF16)
     assert (d.swap_ab, d.split_k, d.cluster_reduce) == (1, 4, 1) and pkg.validate(16, 3584, 8192, pkg.BF16, d) == pkg.OK
-    d = pkg.default_params(128, 28672, 8192, pkg.BF16)
-    assert d.swap_ab == 0
+    d = pkg.default_params(128, 28672, 8192, pkg.BF16)                                     # swapped two-CTA pair
+    assert (d.swap_ab, d.cta_group, d.tile_m, d.tile_n) == (1, 2, 128, 256) and pkg.validate(128, 28672, 8192, pkg.BF16, d) == pkg.OK
+    d = pkg.default_params(128, 7168, 8192, pkg.BF16)
+    assert d.swap_ab == 0 and pkg.validate(128, 7168, 8192, pkg.BF16, d) == pkg.OK
+    # a swapped pair: 256 weight rows per tile, activation rows in multiples of 32; slices x 2 must fit a cluster of 8
+    sp = dict(swap_ab=1, cta_group=2, tile_m=64, tile_n=256, bar_step_rows_a=64, bar_step_rows_b=256)
+    assert ok(**sp) == pkg.OK and ok(**dict(sp, tile_m=48, bar_step_rows_a=48)) == pkg.INVALID_CONFIG
+    assert ok(**dict(sp, split_k=4, cluster_reduce=1)) == pkg.OK and ok(**dict(sp, split_k=8, cluster_reduce=1)) == pkg.INVALID_CONFIG
     d = pkg.default_params(16, 28672, 8192, pkg.BF16, tile_n=64)                           # a tile override names the plain form
     assert d.swap_ab == 0 and pkg.validate(16, 28672, 8192, pkg.BF16, d) == pkg.OK
 
