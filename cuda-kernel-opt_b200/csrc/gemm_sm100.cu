@@ -23,6 +23,12 @@
 // Two accumulator slots in tensor memory let the drain of tile i overlap the MMAs of tile i+1,
 // where the reference drains the whole pipeline at every tile (async.cu:339).
 //
+// Skinny (decode) shapes: with swapped roles the kernel computes D^T = B^T * A^T, so B^T fills the
+// 128-row side of the MMA and the few rows of A its N side; the epilogue then writes the
+// accumulator transposed. When a shape has few tiles, the K slices of one tile run as the CTAs
+// (or CTA pairs) of a thread-block cluster and are summed through distributed shared memory in
+// the epilogue (no workspace, no second kernel).
+//
 // Every wait is bounded: when its budget runs out the CTA records {code, block, barrier, phase}
 // in a device status word, raises a block-wide abort flag so all roles leave their loops, frees
 // its tensor memory and returns normally.

@@ -98,8 +98,6 @@ __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
-
 // Load from the shared memory of another CTA of the cluster (address from mapa_shared).
 __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
     float v;
