@@ -25,7 +25,7 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 # every symbol include/b200_gemm.h declares
 EXPORTS = [
     "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
-    "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
+    "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_f16_out_f16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
     "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_profile_slots", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
     "b200_fill_u16_device", "b200_fill_f32_device", "b200_fill_u16_host", "b200_fill_f32_host",
@@ -71,6 +71,8 @@ def lib():
         for fn in (L.b200_gemm_f16, L.b200_gemm_bf16):
             fn.argtypes = [vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp, sz, vp]
             fn.restype = C.c_int
+        L.b200_gemm_f16_out_f16.argtypes = [vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp]
+        L.b200_gemm_f16_out_f16.restype = C.c_int
         L.b200_gemm_splitk_noalloc.argtypes = [C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp]
         L.b200_gemm_splitk_noalloc.restype = C.c_int
         L.b200_gemm_push.argtypes = [C.c_int, vp, vp, i64, i64, i64, PP, C.c_int, C.c_int, C.POINTER(vp), C.POINTER(vp), vp, C.c_int, vp, sz, vp]
@@ -191,10 +193,20 @@ def gemm(A, Bt, Cm=None, D=None, alpha=1.0, beta=0.0, params: Params | None = No
     dtype = BF16 if A.dtype == torch.bfloat16 else F16
     if D is None:
         D = torch.empty((M, N), dtype=torch.float32, device=A.device)
-    assert D.dtype == torch.float32 and D.is_contiguous() and D.shape == (M, N)
+    assert D.dtype in (torch.float32, torch.float16) and D.is_contiguous() and D.shape == (M, N)
     if Cm is not None:
-        assert Cm.dtype == torch.float32 and Cm.is_contiguous() and Cm.shape == (M, N)
+        assert Cm.dtype == D.dtype and Cm.is_contiguous() and Cm.shape == (M, N)
     p = params if params is not None else default_params(M, N, K, dtype)
+    if D.dtype == torch.float16:
+        # fp16 C and D (the reference's DT = DT_ACC = half instances): b200_gemm_f16_out_f16, no workspace forms
+        assert dtype == F16, "fp16 output goes with fp16 operands"
+        sptr = stream if stream is not None else torch.cuda.current_stream(A.device).cuda_stream
+        with torch.cuda.device(A.device):
+            st = lib().b200_gemm_f16_out_f16(A.data_ptr(), Bt.data_ptr(), Cm.data_ptr() if Cm is not None else None, D.data_ptr(),
+                                             alpha, beta, M, N, K, C.byref(p), sptr)
+        if st != OK:
+            raise B200Error(st, "b200_gemm_f16_out_f16")
+        return D
     need = workspace_bytes(M, N, K, p)
     if need and workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=A.device)

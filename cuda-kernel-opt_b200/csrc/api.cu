@@ -219,7 +219,8 @@ struct PushTarget {  // split-K over GPUs with the exchange fused into the epilo
 
 int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D, float alpha, float beta, int64_t M,
               int64_t N, int64_t K, const b200_gemm_params *user, void *workspace, size_t workspace_bytes,
-              cudaStream_t stream, const PushTarget *push = nullptr, int64_t ld_cd = 0) {
+              cudaStream_t stream, const PushTarget *push = nullptr, int64_t ld_cd = 0, bool out_half = false) {
+    // out_half: C and D point to fp16 matrices (passed through the float pointers unread on the host)
     if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
     b200_gemm_params local;
     if (!user) {
@@ -262,6 +263,9 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
     }
     const int ws_split = p.cluster_reduce ? 1 : p.split_k;  // K slices that meet in the workspace
+    // fp16 output leaves through the plain, transposed and cluster drains only: the workspace forms
+    // (split-K, tail split, push) keep fp32 partials and their second kernels write fp32
+    if (out_half && (ws_split > 1 || tail.s > 1 || pushing)) return B200_INVALID_CONFIG;
     if (ld_cd && ld_cd != N && (ws_split > 1 || tail.s > 1 || (push && push->world > 0) || ld_cd < N || ld_cd % 4))
         return B200_INVALID_CONFIG;  // the second-step kernels assume a dense D
     if (ws_split > 1) {
@@ -280,7 +284,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
                    static_cast<uint32_t>(p.chunk_n / p.cta_group));
     if (st != B200_OK) return st;
     int epi_mode = p.epi_mode;
-    if (p.mma_m != 128 || ws_split > 1 || pushing) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
+    if (p.mma_m != 128 || ws_split > 1 || pushing || out_half) epi_mode = 0;  // the TMA-store drain needs 32 consecutive rows per warp
     if (epi_mode) {
         st = encode_2d(&a.map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
                        kEpiBoxCols, 32, static_cast<uint64_t>(ld_cd));
@@ -295,6 +299,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.N = static_cast<int>(kN);
     a.K = static_cast<int>(K);
     a.swap_ab = p.swap;
+    a.out_half = out_half ? 1 : 0;
     a.ld_cd = static_cast<int>(ld_cd ? ld_cd : N);
     a.tiles_m = static_cast<int>((kM + p.tile_m - 1) / p.tile_m);
     a.tiles_n = static_cast<int>((kN + p.tile_n - 1) / p.tile_n);
@@ -458,6 +463,12 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
                    int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes, void *stream) {
     return gemm_impl(B200_BF16, A, Bt, C, D, alpha, beta, M, N, K, p, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_f16_out_f16(const void *A, const void *Bt, const void *C, void *D, float alpha, float beta, int64_t M,
+                          int64_t N, int64_t K, const b200_gemm_params *p, void *stream) {
+    return gemm_impl(B200_F16, A, Bt, static_cast<const float *>(C), static_cast<float *>(D), alpha, beta, M, N, K, p, nullptr, 0,
+                     static_cast<cudaStream_t>(stream), nullptr, 0, true);
 }
 
 int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,

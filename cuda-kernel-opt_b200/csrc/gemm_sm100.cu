@@ -32,6 +32,8 @@
 // Every wait is bounded: when its budget runs out the CTA records {code, block, barrier, phase}
 // in a device status word, raises a block-wide abort flag so all roles leave their loops, frees
 // its tensor memory and returns normally.
+#include <cuda_fp16.h>
+
 #include "gemm_sm100.cuh"
 #include "ptx_sm100.cuh"
 
@@ -211,6 +213,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int push_world = g.push_world, push_rank = g.push_rank, push_rows = g.push_rows;
     const int ld_cd = g.ld_cd;
     const bool swap_ab = g.swap_ab != 0;
+    const bool out_half = g.out_half != 0;   // C and D are fp16 (never with a workspace, tail or push path)
     const int dbg = g.debug_flags;  // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage)
     const float g_alpha = g.alpha, g_beta = g.beta;
     const float *const gC = g.C;
@@ -822,8 +825,13 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                 if (sl < c.cl_split) sum += v[cc][sl];
                             const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row);
                             float val = alpha * sum;
-                            if (beta != 0.0f) val += beta * __ldg(gC + off);
-                            gD[off] = val;
+                            if (out_half) {
+                                if (beta != 0.0f) val += beta * __half2float(reinterpret_cast<const __half *>(gC)[off]);
+                                reinterpret_cast<__half *>(gD)[off] = __float2half_rn(val);
+                            } else {
+                                if (beta != 0.0f) val += beta * __ldg(gC + off);
+                                gD[off] = val;
+                            }
                         }
                     }
                 }
@@ -860,7 +868,22 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         float *dst = out + off0;
                         const float *csrc = gC + off0;
                         const int valid = min(4 * nvec, c.N - (w.n0 + c0));
-                        if (b_u == 0.0f) {
+                        if (out_half) {
+                            __half *dst16 = reinterpret_cast<__half *>(gD) + off0;
+                            const __half *c16 = reinterpret_cast<const __half *>(gC) + off0;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (j < 16 || wide) {
+                                    if (j < valid) {
+                                        float v = a_u * __uint_as_float(r[j]);
+                                        if (b_u != 0.0f) v += b_u * __half2float(*c16);
+                                        *dst16 = __float2half_rn(v);
+                                    }
+                                    dst16 += pitch;
+                                    c16 += pitch;
+                                }
+                            }
+                        } else if (b_u == 0.0f) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 if (j < 16 || wide) {
@@ -876,6 +899,36 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                     dst += pitch;
                                     csrc += pitch;
                                 }
+                            }
+                        }
+                    }
+                } else if (out_half) {
+                    // fp16 C and D: four values per 8-byte store
+                    if (row_ok) {
+                        uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(gD) + row_off + c0);
+                        const uint2 *csrc = reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + row_off + c0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
+                                float4 v;
+                                v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                                v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                                v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                                v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                                if (b_u != 0.0f) {
+                                    const uint2 cv = __ldg(csrc + j);
+                                    const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
+                                    const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
+                                    v.x += b_u * c01.x;
+                                    v.y += b_u * c01.y;
+                                    v.z += b_u * c23.x;
+                                    v.w += b_u * c23.y;
+                                }
+                                const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+                                uint2 o;
+                                o.x = *reinterpret_cast<const uint32_t *>(&h01);
+                                o.y = *reinterpret_cast<const uint32_t *>(&h23);
+                                dst[j] = o;
                             }
                         }
                     }

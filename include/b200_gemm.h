@@ -132,6 +132,14 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
                    int64_t N, int64_t K, const b200_gemm_params *p, void *workspace, size_t workspace_bytes,
                    void *stream);
 
+/* The same product with fp16 C and D (m x n row-major halves): stands in for the reference's DT = DT_ACC = half
+ * instances of the launchers above (matmul_shmem_tc_async.cu:411-478 instantiate both). Accumulation stays
+ * fp32 in tensor memory and the result is rounded to fp16 once (the reference's half instances accumulate in
+ * half), so it is at least as close to the exact product. Needs no workspace: configurations whose K slices
+ * meet in a workspace (split_k > 1 without cluster_reduce, tail_split) are B200_INVALID_CONFIG here. */
+int b200_gemm_f16_out_f16(const void *A, const void *Bt, const void *C, void *D, float alpha, float beta, int64_t M,
+                          int64_t N, int64_t K, const b200_gemm_params *p, void *stream);
+
 /* Split-K GEMM that allocates nothing and needs no workspace from the caller. It has no
  * counterpart in the reference (whose launchers never split K and never need scratch memory).
  *

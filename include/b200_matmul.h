@@ -1,14 +1,14 @@
 // b200_matmul.h - C++ launchers with the reference's own names and argument lists, forwarding
 // to the C ABI (b200_gemm.h). A harness written against the reference launchers compiles against
-// these unchanged, except that they return a status instead of void and take no template
-// instance for DT_ACC = half (fp32 accumulate and output only).
+// these unchanged, except that they return a status instead of void. DT_ACC = half (with DT = half)
+// gives fp16 C and D; the accumulation is fp32 either way.
 //
 //   gemm_shmem_tc_async           15 arguments   matmul_shmem_tc_async.cu:494-510
 //   gemm_shmem_tc_async_opt_port  16 arguments   matmul_shmem_tc_async_opt_port_0.cu:515-532
 //                                 18 arguments   matmul_shmem_tc_async_opt_port_1.cu:889-908
 //                                 20 arguments   matmul_shmem_tc_async_opt_port_2.cu:1088-1109
 //
-// DT is half or __nv_bfloat16 (device pointers), DT_ACC is float. A is m x k row-major, B is
+// DT is half or __nv_bfloat16 (device pointers), DT_ACC is float (or half with DT = half). A is m x k row-major, B is
 // stored transposed (n x k), C and D are m x n. Launches go to the legacy default stream, as the
 // reference's do.
 //
@@ -45,6 +45,14 @@ template <>
 struct InputType<__nv_bfloat16> {
     static constexpr int value = B200_BF16;
 };
+
+// DT_ACC = half (the reference instantiates <half, half> beside <half, float>): fp16 C and D, scalars as half.
+// The plain tile of these launchers never needs a workspace, so every reference configuration maps.
+inline int launch(const half *A, const half *B, const half *C, half *D, half alpha, half beta, int M, int N, int K,
+                  const b200_gemm_params &p) {
+    if (M % p.tile_m || N % p.tile_n || K % p.segment_dim_k) return B200_INVALID_SHAPE;
+    return b200_gemm_f16_out_f16(A, B, C, D, __half2float(alpha), __half2float(beta), M, N, K, &p, nullptr);
+}
 
 template <typename DT>
 inline int launch(const DT *A, const DT *B, const float *C, float *D, float alpha, float beta, int M, int N, int K,
@@ -84,7 +92,7 @@ template <typename DT, typename DT_ACC>
 int gemm_shmem_tc_async(const DT *A, const DT *B /* Transpose */, const DT_ACC *C, DT_ACC *D, DT_ACC alpha, DT_ACC beta,
                         int M, int N, int K, int tile_dim, int segment_dim_k, int num_stages, int num_producer_warps,
                         int num_consumer_warps, int num_sms) {
-    static_assert(sizeof(DT_ACC) == 4, "fp32 accumulate and output only");
+    static_assert(sizeof(DT_ACC) == 4 || (sizeof(DT_ACC) == 2 && sizeof(DT) == 2), "DT_ACC is float, or half with DT = half");
     if (tile_dim != 64 && tile_dim != 128) return B200_INVALID_CONFIG;  // async.cu:511
     const b200_gemm_params p =
         detail::base_params(tile_dim, segment_dim_k, 1, num_stages, num_producer_warps, num_consumer_warps, num_sms);
@@ -96,7 +104,7 @@ template <typename DT, typename DT_ACC>
 int gemm_shmem_tc_async_opt_port(const DT *A, const DT *B /* Transpose */, const DT_ACC *C, DT_ACC *D, DT_ACC alpha,
                                  DT_ACC beta, int M, int N, int K, int tile_dim, int segment_dim_k, int tile_group_m,
                                  int num_stages, int num_producer_warps, int num_consumer_warps, int num_sms) {
-    static_assert(sizeof(DT_ACC) == 4, "fp32 accumulate and output only");
+    static_assert(sizeof(DT_ACC) == 4 || (sizeof(DT_ACC) == 2 && sizeof(DT) == 2), "DT_ACC is float, or half with DT = half");
     if (tile_dim != 64 && tile_dim != 128) return B200_INVALID_CONFIG;
     const b200_gemm_params p = detail::base_params(tile_dim, segment_dim_k, tile_group_m, num_stages, num_producer_warps,
                                                    num_consumer_warps, num_sms);
@@ -109,7 +117,7 @@ int gemm_shmem_tc_async_opt_port(const DT *A, const DT *B /* Transpose */, const
                                  DT_ACC beta, int M, int N, int K, int tile_dim, int segment_dim_k, int bar_steps_a,
                                  int bar_steps_b, int bar_step_rows_a, int bar_step_rows_b, int tile_group_m,
                                  int num_stages, int num_producer_warps, int num_consumer_warps, int num_sms) {
-    static_assert(sizeof(DT_ACC) == 4, "fp32 accumulate and output only");
+    static_assert(sizeof(DT_ACC) == 4 || (sizeof(DT_ACC) == 2 && sizeof(DT) == 2), "DT_ACC is float, or half with DT = half");
     if (tile_dim != 64 && tile_dim != 128) return B200_INVALID_CONFIG;
     // port_1.cu:919 and port_2.cu:1122: the shift-synchronised generations need >= 2 producer warps
     if (num_producer_warps != 2 && num_producer_warps != 4 && num_producer_warps != 8) return B200_INVALID_CONFIG;

@@ -89,6 +89,9 @@ def ref():
         R.ref_count_incorrect.restype = C.c_int
         R.ref_constant_is_correct.argtypes = [vp, C.c_int, f32, f32, f32]
         R.ref_constant_is_correct.restype = C.c_int
+        if hasattr(R, "ref_half_count_incorrect"):
+            R.ref_half_count_incorrect.argtypes = [C.c_int, vp, vp, vp, vp, C.c_int, f32, f32, f32]
+            R.ref_half_count_incorrect.restype = C.c_int
         _ref = R
     return _ref
 
@@ -206,3 +209,14 @@ def ref_constant_is_correct(res, alpha, beta, atol) -> bool:
     n = res.shape[0]
     assert res.shape == (n, n)
     return bool(ref().ref_constant_is_correct(_p(res), n, alpha, beta, atol))
+
+
+def ref_half_count_incorrect(A, Bt, C16, res16, alpha, beta, atol) -> int:
+    """The reference's <half, half> check (accumulation in half): how many elements of the fp16 result res16
+    are off by more than atol. A: (m, n), Bt: (n, n), C16 / res16: (m, n) fp16 bit patterns (uint16)."""
+    _chk(A, np.uint16, "A"); _chk(Bt, np.uint16, "Bt"); _chk(res16, np.uint16, "res")
+    n = Bt.shape[0]
+    assert Bt.shape == (n, n) and A.shape[1] == n and res16.shape == A.shape[:1] + (n,)
+    if C16 is not None:
+        _chk(C16, np.uint16, "C")
+    return int(ref().ref_half_count_incorrect(n, _p(A), _p(Bt), _p(C16), _p(res16), A.shape[0], alpha, beta, atol))

@@ -82,6 +82,23 @@ int ref_count_incorrect(void *h, int dtype, const float *res, int m, float alpha
                  : count_incorrect<half>(h, res, m, alpha, beta, atol);
 }
 
+// The reference's own <half, half> check (every launcher is also instantiated with DT_ACC = half,
+// matmul_shmem_tc_async.cu:411-478): the product accumulated IN HALF (each += rounds to fp16) and
+// compared in half with Abs(half) (matmul_test.h:33, :316-320). A: m x n, Bt: n x n, C and res:
+// m x n, all fp16 bit patterns; C may be null (zeros). Returns the count of elements off by more
+// than atol.
+int ref_half_count_incorrect(int n, const uint16_t *A, const uint16_t *Bt, const uint16_t *C, const uint16_t *res, int m,
+                             float alpha, float beta, float atol) {
+    matmul_test::MatmulTestGemmSquare<half, half> mt(n, 64);
+    std::memcpy(const_cast<half *>(mt.GetA()), A, size_t(m) * n * 2);
+    std::memcpy(const_cast<half *>(mt.GetB()), Bt, size_t(n) * n * 2);
+    if (C) std::memcpy(const_cast<half *>(mt.GetC()), C, size_t(m) * n * 2);
+    else std::memset(const_cast<half *>(mt.GetC()), 0, size_t(m) * n * 2);
+    std::memcpy(mt.GetRes(), res, size_t(m) * n * 2);
+    matmul_test::MatDim dim = {m, n, n};
+    return mt.GetNumIncorrect(mt.GetRes(), dim, __float2half(alpha), __float2half(beta), __float2half(atol));
+}
+
 // The constant-matrix family (A = 1, B = 10, C = 1; matmul_test.h:227-232) judged by the
 // reference's closed form (matmul_test.h:279-288). res is n x n. Returns 1 if correct.
 int ref_constant_is_correct(const float *res, int n, float alpha, float beta, float atol) {

@@ -188,6 +188,44 @@ static int run_performance(int dim, int num_reps) {
     return 0;
 }
 
+// The reference instantiates every launcher for <half, half> as well (matmul_shmem_tc_async.cu:411-478): fp16 C and
+// D, half scalars. Constant matrices at sizes whose result is exact in fp16 (10 * dim + 1 <= 2048).
+static int run_half_output(int dim_max) {
+    const size_t n = size_t(dim_max) * dim_max;
+    half *A, *B, *C, *D;
+    CHECK(cudaMalloc(&A, n * 2)); CHECK(cudaMalloc(&B, n * 2)); CHECK(cudaMalloc(&C, n * 2)); CHECK(cudaMalloc(&D, n * 2));
+    std::vector<half> a(n, __float2half(1.0f)), b(n, __float2half(10.0f)), c(n, __float2half(1.0f)), res(n);
+    CHECK(cudaMemcpy(A, a.data(), n * 2, cudaMemcpyHostToDevice));
+    CHECK(cudaMemcpy(B, b.data(), n * 2, cudaMemcpyHostToDevice));
+    CHECK(cudaMemcpy(C, c.data(), n * 2, cudaMemcpyHostToDevice));
+    cudaDeviceProp prop;
+    CHECK(cudaGetDeviceProperties(&prop, 0));
+    int failed = 0, total = 0;
+    for (int tile = 64; tile <= 128; tile *= 2)
+        for (int dim = tile; dim <= dim_max; dim += tile)
+            for (int variant = 0; variant < 3; ++variant) {
+                CHECK(cudaMemset(D, 0, size_t(dim) * dim * 2));
+                const half one = __float2half(1.0f);
+                int st;
+                if (variant == 0) st = gemm_shmem_tc_async<half, half>(A, B, C, D, one, one, dim, dim, dim, tile, 64, 3, 2, 4, prop.multiProcessorCount);
+                else if (variant == 1) st = gemm_shmem_tc_async_opt_port<half, half>(A, B, C, D, one, one, dim, dim, dim, tile, 64, 2, 3, 2, 8, prop.multiProcessorCount);
+                else st = gemm_shmem_tc_async_opt_port<half, half>(A, B, C, D, one, one, dim, dim, dim, tile, 64, 1, 1, 16, 16, 1, 2, 2, 4, prop.multiProcessorCount);
+                bool ok = st == B200_OK;
+                if (ok) {
+                    CHECK(cudaMemcpy(res.data(), D, size_t(dim) * dim * 2, cudaMemcpyDeviceToHost));
+                    const float want = 10.0f * dim + 1.0f;
+                    for (size_t e = 0; e < size_t(dim) * dim && ok; ++e) ok = __half2float(res[e]) == want;
+                }
+                ++total;
+                if (!ok) { ++failed; printf("half output tile %d dim %d launcher %d: failed (status %d)\n", tile, dim, variant, st); }
+            }
+    int info[4];
+    const int dev = b200_device_status(nullptr, info);
+    printf("half output: %d launches, %d failed, device status %d\n", total, failed, dev);
+    cudaFree(A); cudaFree(B); cudaFree(C); cudaFree(D);
+    return failed == 0 && dev == B200_OK ? 0 : 1;
+}
+
 int main(int argc, char **argv) {
     const char *mode = argc > 1 ? argv[1] : "correctness";
     const int dim = argc > 2 ? atoi(argv[2]) : 1024;
@@ -196,6 +234,7 @@ int main(int argc, char **argv) {
     // ranges of the reference's own calls (port_2.cu:1518-1550), narrowed where `quick`
     Sweep s = {64, 128, 64, 256, 1, quick ? 1 : 2, 1, quick ? 2 : 3, 2, quick ? 2 : 4, 4, 8};
     if (!strcmp(mode, "correctness")) return run_correctness(dim, s, 2, 1.0f, 1.0f, 0.001f);
+    if (!strcmp(mode, "half")) return run_half_output(dim < 192 ? dim : 192);   // 10 * 192 + 1 is exact in fp16
     if (!strcmp(mode, "accuracy")) { s.group_hi = 1; s.stages_lo = 2; s.stages_hi = 2; s.p_hi = 2; return run_accuracy(dim, s, 1.0f, 1.0f, 0.1f); }
     if (!strcmp(mode, "performance")) return run_performance(dim, 2);
     printf("unknown mode %s\n", mode);

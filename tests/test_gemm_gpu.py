@@ -271,6 +271,70 @@ def test_cuda_graph_capture_and_overlapped_launch(pkg, cuda, oracle):
         check("graph replay")
 
 
+def test_fp16_output(pkg, cuda, oracle):
+    """b200_gemm_f16_out_f16 (the reference's DT = DT_ACC = half instances): fp16 C and D, fp32 accumulation,
+    one rounding at the end. Against the oracle's fp32 result rounded to fp16: the stated tolerance plus half a
+    unit in the last place of fp16; exact where the product is exactly representable. Plain tiles, pairs,
+    swapped and cluster forms; workspace forms are refused."""
+    torch = cuda
+    cases = [(256, 512, 1024, dict()), (300, 520, 200, dict(tile_m=128, tile_n=128)), (64, 768, 512, dict(tile_m=64, tile_n=64)),
+             (520, 1024, 512, dict(tile_m=256, tile_n=256, cta_group=2)), (16, 1024, 4096, dict()),
+             (48, 2052, 1024, dict(swap_ab=1, tile_m=48, tile_n=128)), (16, 1024, 8192, dict(swap_ab=1, tile_m=16, split_k=4, cluster_reduce=1)),
+             (100, 1000, 264, dict(num_consumer_warps=8))]
+    for i, (m, n, k, ov) in enumerate(cases):
+        A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 5000 + i)
+        C16 = Cm.astype(np.float16)
+        for alpha, beta in ((1.0, 0.0), (0.5, 2.0)):
+            p = pkg.default_params(m, n, k, pkg.F16, **ov)
+            assert pkg.validate(m, n, k, pkg.F16, p) == pkg.OK, p.as_dict()
+            dA, dB = to_device(torch, A, pkg.F16), to_device(torch, Bt, pkg.F16)
+            dC = torch.from_numpy(C16).cuda()
+            D = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+            pkg.gemm(dA, dB, dC if beta else None, D, alpha, beta, p)
+            st, info = pkg.device_status()
+            assert st == pkg.OK, (st, info)
+            want32 = oracle.gemm(A, Bt, C16.astype(np.float32) if beta else None, alpha, beta, oracle.FP16)
+            got = D.cpu().numpy().astype(np.float32)
+            assert np.isfinite(got).all()
+            err = np.abs(got - want32)
+            bound = 2.0 ** -10 * np.sqrt(k) * (abs(alpha) + abs(beta) + 1.0) + 2.0 ** -11 * np.abs(want32) + 2.0 ** -24
+            assert (err <= bound).all(), (m, n, k, ov, alpha, beta, float(err.max()))
+            rel = np.linalg.norm(got - want32) / np.linalg.norm(want32)
+            assert rel <= 1e-3, rel
+    # The reference's own <half, half> check accumulates in half, so at its accuracy tolerance (0.1) it flags its
+    # own rounding once K grows (it reports counts, it does not fail on them). The kernel's result must get the
+    # count the fp32 oracle rounded to fp16 gets: 0 at K = 64, and the same handful at K = 256.
+    if oracle.have_ref() and hasattr(oracle.ref(), "ref_half_count_incorrect"):
+        for n_ in (64, 128, 256):
+            A, Bt, Cm = inputs(pkg, pkg.F16, n_, n_, n_, 5200 + n_)
+            C16 = Cm.astype(np.float16)
+            D = torch.zeros((n_, n_), dtype=torch.float16, device="cuda")
+            pkg.gemm(to_device(torch, A, pkg.F16), to_device(torch, Bt, pkg.F16), torch.from_numpy(C16).cuda(), D, 1.0, 1.0,
+                     pkg.default_params(n_, n_, n_, pkg.F16, tile_m=64, tile_n=64))
+            got16 = np.ascontiguousarray(D.cpu().numpy()).view(np.uint16)
+            c16 = np.ascontiguousarray(C16).view(np.uint16)
+            want16 = np.ascontiguousarray(oracle.gemm(A, Bt, C16.astype(np.float32), 1.0, 1.0, oracle.FP16).astype(np.float16)).view(np.uint16)
+            n_got = oracle.ref_half_count_incorrect(A, Bt, c16, got16, 1.0, 1.0, 0.1)
+            n_want = oracle.ref_half_count_incorrect(A, Bt, c16, want16, 1.0, 1.0, 0.1)
+            assert abs(n_got - n_want) <= 2 + n_want // 10, (n_, n_got, n_want)
+            if n_ == 64:
+                assert n_got == 0
+    # exactly representable products: the fp16 result is exact
+    m, n, k = 128, 256, 64
+    A = np.full((m, k), 0x3C00, np.uint16)                           # 1.0
+    Bt = np.full((n, k), 0x4000, np.uint16)                          # 2.0
+    D = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    pkg.gemm(to_device(torch, A, pkg.F16), to_device(torch, Bt, pkg.F16), None, D, 1.0, 0.0, pkg.default_params(m, n, k, pkg.F16))
+    assert (D.cpu().numpy() == np.float16(2.0 * k)).all()
+    # K slices that meet in a workspace keep fp32 partials: refused for fp16 output
+    p = pkg.default_params(256, 512, 4096, pkg.F16, tile_m=128, tile_n=128, split_k=2)
+    D = torch.zeros((256, 512), dtype=torch.float16, device="cuda")
+    A, Bt, _ = inputs(pkg, pkg.F16, 256, 512, 4096, 5100)
+    with pytest.raises(pkg.B200Error) as ei:
+        pkg.gemm(to_device(torch, A, pkg.F16), to_device(torch, Bt, pkg.F16), None, D, 1.0, 0.0, p)
+    assert ei.value.status == pkg.INVALID_CONFIG
+
+
 def test_bf16_and_scalars(pkg, cuda, oracle):
     A, Bt, Cm = inputs(pkg, pkg.BF16, 384, 512, 768, 61)
     for alpha, beta in ((1.0, 0.0), (0.5, 2.0), (-1.25, 0.75), (0.0, 1.0)):
@@ -515,6 +579,6 @@ def test_reference_style_cpp_harness(pkg, cuda, oracle, tmp_path):
            f"-Wl,-rpath,{libdir}", f"-Wl,-rpath,{os.path.join(ROOT, 'oracle')}"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
-    for args in (["correctness", "1024", "quick"], ["accuracy", "256"], ["accuracy", "512"]):
+    for args in (["correctness", "1024", "quick"], ["accuracy", "256"], ["accuracy", "512"], ["half", "192"]):
         r = subprocess.run([exe] + args, capture_output=True, text=True, timeout=900)
         assert r.returncode == 0, (args, r.stdout[-3000:], r.stderr[-2000:])

@@ -104,3 +104,22 @@ def test_oracle_equals_reference_where_tree_is_present(oracle):
         D[m // 2, n // 3] += 1e-3
         assert s.count_incorrect(D, 0.75, 1.0, 0.0) == 1
         s.close()
+
+
+def test_reference_half_half_check_and_fp32_accumulation():
+    """The reference's <half, half> instances accumulate in half; the fp16-output entry point accumulates in
+    fp32 and rounds once. On a small problem the reference's own half check accepts the fp32-accumulated,
+    once-rounded result at its accuracy tolerance (0.1, matmul_shmem_tc_async_opt_port_2.cu:1534) and rejects
+    a result that is off by more."""
+    import oracle
+    if not oracle.have_ref() or not hasattr(oracle.ref(), "ref_half_count_incorrect"):
+        import pytest
+        pytest.skip("reference build absent")
+    n = 128
+    A = oracle.fill_u16((n, n), 7, oracle.TENSOR_A)
+    Bt = oracle.fill_u16((n, n), 7, oracle.TENSOR_B)
+    Cm = oracle.fill_f32((n, n), 7, oracle.TENSOR_C).astype(np.float16)
+    want = oracle.gemm(A, Bt, Cm.astype(np.float32), 1.0, 1.0, oracle.FP16).astype(np.float16)
+    assert oracle.ref_half_count_incorrect(A, Bt, Cm.view(np.uint16), want.view(np.uint16), 1.0, 1.0, 0.1) == 0
+    off = (want.astype(np.float32) + 0.5).astype(np.float16)
+    assert oracle.ref_half_count_incorrect(A, Bt, Cm.view(np.uint16), off.view(np.uint16), 1.0, 1.0, 0.1) == n * n
