@@ -133,6 +133,10 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         if (few_tiles) {
             p->split_k = 4;
             p->cluster_reduce = 1;
+        } else if (n_tiles128 > 148) {
+            // an even share of tiles per CTA (224 tiles: 112 CTAs x 2 rather than 76 x 2 + 72 x 1; +1.5 %)
+            const int64_t waves = (n_tiles128 + 147) / 148;
+            p->num_sms = static_cast<int>((n_tiles128 + waves - 1) / waves);
         }
         // A short kernel: let set-up overlap the previous kernel of the stream (measured -4 % on the
         // 4- and 8-GPU shards of the decode shape, 117 and 59 MB of weights; +6 % on the whole one,
