@@ -108,7 +108,9 @@ int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const 
 // 128 x 256 tile); small or skinny ones a one-CTA tile with the widest N that divides.
 void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool allow_swap = true) {
     std::memset(p, 0, sizeof(*p));
-    const bool pair = (M > 128) && (N % 256 == 0);
+    // The two-CTA 256 x 256 tile needs enough tiles to occupy the GPU: below half of the 74 pairs
+    // (1024^2 has 16) narrower one-CTA tiles finish sooner (1024^3: 7.3 against 11.3 us).
+    const bool pair = (M > 128) && (N % 256 == 0) && ((M + 255) / 256) * (N / 256) >= 37;
     const int64_t n_tiles128 = (N + 127) / 128;
     const bool few_tiles = K >= 4096 && n_tiles128 <= 74;
     if (allow_swap && (M <= 64 || (M <= 128 && K >= 4096 && n_tiles128 <= 37))) {
@@ -189,7 +191,10 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
             const int64_t tiles = rows * (N / tn);
             const int64_t waves = (tiles + 147) / 148;
             // narrow tiles cost tensor-core efficiency, which only matters when the shape is not HBM-bound
-            const double eff = double(tiles) / double(waves * 148) * ((tn >= 128 || (M <= 128 && tn >= 32)) ? 1.0 : tn / 128.0);
+            // (nor when the whole problem is less than one wave of 128 x 128 tiles: then it is latency-bound)
+            const bool small = rows * ((N + 127) / 128) < 148;
+            const double eff = double(tiles) / double(waves * 148) *
+                               ((tn >= 128 || (M <= 128 && tn >= 32) || (small && tn >= 64)) ? 1.0 : tn / 128.0);
             if (eff > best_eff + 1e-9) {
                 best_eff = eff;
                 best_n = tn;
@@ -201,7 +206,7 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         p->num_stages = 198000 / stage_bytes > 8 ? 8 : 198000 / stage_bytes;  // leaves room for the TMA-store staging
         p->num_producer_warps = 1;
         // weights stream through once (evict_first), the few activation rows are re-read by every CTA
-        p->l2_hint = (M <= 128) ? 1 : 0;
+        p->l2_hint = (M <= 128) ? 1 : 3;
     }
     p->segment_dim_k = 64;
     p->bar_steps_a = 0;
