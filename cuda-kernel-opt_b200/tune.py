@@ -40,6 +40,16 @@ def candidates(M: int, N: int, K: int) -> list[dict]:
                     for s in (2, 4, 8):
                         out.append(dict(base, split_k=s, cluster_reduce=1))
                         out.append(dict(base, split_k=s, cluster_reduce=0))
+        if M > 32:
+            # the swapped two-CTA pair: 256 weight rows per tile, activation rows in multiples of 32
+            tm2 = -(-M // 32) * 32
+            per_stage = (128 + tm2 // 2) * 128
+            for stages in sorted({max(2, min(10, 200000 // per_stage)), max(2, min(10, 200000 // per_stage) - 2)}):
+                base = dict(swap_ab=1, cta_group=2, tile_m=tm2, tile_n=256, segment_dim_k=64, num_stages=stages, l2_hint=1,
+                            split_k=1, cluster_reduce=0)
+                out.append(base)
+                if -(-N // 256) < 74 and K >= 2048:
+                    out.append(dict(base, split_k=2, cluster_reduce=1))
     tiles = []
     if M > 128:
         tiles += [dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=256, tile_n=128, cta_group=2)]
