@@ -195,3 +195,25 @@ def test_status_strings(pkg):
     seen = {pkg.status_string(i) for i in range(8)}
     assert len(seen) == 8 and "unknown status" not in seen
     assert pkg.status_string(99) == "unknown status"
+
+
+def test_defaults_are_valid_everywhere_and_need_no_workspace(pkg):
+    """b200_gemm_default_params (and its plain twin) over a grid of shapes: always a valid configuration for the
+    shape, never one that needs a caller workspace, swapped forms only where the activations are few."""
+    import itertools
+    Ms = (1, 7, 16, 17, 32, 33, 64, 65, 100, 128, 129, 256, 300, 1000, 1024, 4096, 8192)
+    Ns = (4, 16, 64, 100, 128, 256, 1000, 1024, 3584, 4096, 7168, 14336, 28672, 28676)
+    Ks = (8, 64, 72, 512, 1000, 4096, 8192, 262144)
+    for M, N, K in itertools.product(Ms, Ns, Ks):
+        for dtype in (pkg.F16, pkg.BF16):
+            for plain in (False, True):
+                p = pkg.Params()
+                fn = pkg.lib().b200_gemm_default_params_plain if plain else pkg.lib().b200_gemm_default_params
+                assert fn(M, N, K, dtype, ctypes.byref(p)) == pkg.OK
+                assert pkg.validate(M, N, K, dtype, p) == pkg.OK, (M, N, K, plain, p.as_dict())
+                assert pkg.workspace_bytes(M, N, K, p) == 0, (M, N, K, plain, p.as_dict())
+                assert pkg.smem_bytes(dtype, p) > 0
+                if plain or M > 128:
+                    assert p.swap_ab == 0
+                if M <= 64 and not plain:
+                    assert p.swap_ab == 1 and p.tile_m >= M
