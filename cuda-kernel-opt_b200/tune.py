@@ -116,7 +116,7 @@ def tune(M: int, N: int, K: int, dtype: str = "f16", out: str = "tune.jsonl", ro
     op_bytes = 2 * (M + N) * K
     rot = 1 if op_bytes > 252e6 else min(64, -(-512_000_000 // op_bytes))
     Bs = [Bt] + [Bt.clone() for _ in range(rot - 1)]
-    reps = max(inner, min(rot, 16))
+    reps = max(inner, 8, min(rot, 16))   # enough launches per replay for the first one's launch latency not to count
     side = torch.cuda.Stream()
     graphs = []
     for ov, p, ws, times in todo:
