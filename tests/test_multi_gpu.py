@@ -48,9 +48,26 @@ def _worker(rank, world, port, q):
             ex.gemm_reduce_scatter(dA, dB, out, pkg.default_params(m, n, ks.size, pkg.F16, **tile))
             torch.cuda.synchronize()
             results["fused " + str(tile)] = out.cpu().numpy().copy()
+        # (3) the shards that need no exchange, with default tunables: rows of B^T (columns of D) of a decode
+        # shape per rank (swapped roles, K over a cluster), rows of A of a square per rank
+        m2, n2, k2 = 16, 1024 * world, 4096
+        A2, B2 = pkg.fill_u16_host((m2, k2), seed + 1, 1, dtype=pkg.BF16), pkg.fill_u16_host((n2, k2), seed + 1, 2, dtype=pkg.BF16)
+        ns = shard.n_shard(n2, world, rank, 256)
+        p2 = pkg.default_params(m2, ns.size, k2, pkg.BF16)
+        assert p2.swap_ab == 1 and p2.cluster_reduce == 1
+        got2 = pkg.gemm(to_device(torch, A2, pkg.BF16), to_device(torch, np.ascontiguousarray(B2[ns.begin:ns.end]), pkg.BF16), params=p2)
+        want2 = oracle.gemm(A2, B2, dtype=oracle.BF16)[:, ns.begin:ns.end]
+        m3, n3, k3 = 512 * world, 768, 1024
+        A3, B3 = pkg.fill_u16_host((m3, k3), seed + 2, 1), pkg.fill_u16_host((n3, k3), seed + 2, 2)
+        ms = shard.m_shard(m3, world, rank, 256)
+        got3 = pkg.gemm(to_device(torch, np.ascontiguousarray(A3[ms.begin:ms.end]), pkg.F16), to_device(torch, B3, pkg.F16))
+        want3 = oracle.gemm(A3, B3)[ms.begin:ms.end]
+        torch.cuda.synchronize()
         st, info = pkg.device_status()
         ex.close()
         report = {name: tolerance_ok(got, want, k) for name, got in results.items()}
+        report["N-shard, decode defaults"] = tolerance_ok(got2.cpu().numpy(), want2, k2)
+        report["M-shard, defaults"] = tolerance_ok(got3.cpu().numpy(), want3, k3)
         q.put((rank, st, report))
     finally:
         dist.destroy_process_group()
