@@ -801,10 +801,69 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (e == 0 && lane == 0) B200_TL(30);
                 const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
                 const int my_end = min(c.tile_n, (c.cl_rank + 1) * per);
+                if (c.mma_m == 128) {
+                    // 128-row slices: a warp takes whole columns of the tile (column first + e, then every
+                    // epi_warps-th), a lane four consecutive rows, so a column costs one 16-byte remote load
+                    // per slice and one 16-byte store per lane (the kernel's M is a multiple of 4).
+                    const int row4 = w.m0 + static_cast<int>(rank) * c.cta_rows_a + lane * 4;
+                    const bool rows_ok = row4 < c.M;
+                    const uint32_t my_rows = pbuf + static_cast<uint32_t>(lane) * 16u;
+                    for (int col = c.cl_rank * per + e; col < my_end; col += c.epi_warps) {
+                        const int gcol = w.n0 + col;
+                        if (gcol >= c.N) break;
+                        // slices are added in ascending order, four remote loads in flight at a time
+                        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        const uint32_t src = my_rows + static_cast<uint32_t>(col) * 512u;
+                        for (int base4 = 0; base4 < c.cl_split; base4 += 4) {
+                            float4 v[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                if (base4 + i < c.cl_split) v[i] = ld_shared_cluster_v4(mapa_shared(src, static_cast<uint32_t>((base4 + i) * CG) + rank));
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                if (base4 + i < c.cl_split) {
+                                    sum.x += v[i].x;
+                                    sum.y += v[i].y;
+                                    sum.z += v[i].z;
+                                    sum.w += v[i].w;
+                                }
+                        }
+                        if (rows_ok) {
+                            const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row4);
+                            float4 val = make_float4(alpha * sum.x, alpha * sum.y, alpha * sum.z, alpha * sum.w);
+                            if (out_half) {
+                                if (beta != 0.0f) {
+                                    const uint2 cv = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + off);
+                                    const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
+                                    const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
+                                    val.x += beta * c01.x;
+                                    val.y += beta * c01.y;
+                                    val.z += beta * c23.x;
+                                    val.w += beta * c23.y;
+                                }
+                                const __half2 h01 = __floats2half2_rn(val.x, val.y), h23 = __floats2half2_rn(val.z, val.w);
+                                uint2 o;
+                                o.x = *reinterpret_cast<const uint32_t *>(&h01);
+                                o.y = *reinterpret_cast<const uint32_t *>(&h23);
+                                *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(gD) + off) = o;
+                            } else {
+                                if (beta != 0.0f) {
+                                    const float4 cv = __ldg(reinterpret_cast<const float4 *>(gC + off));
+                                    val.x += beta * cv.x;
+                                    val.y += beta * cv.y;
+                                    val.z += beta * cv.z;
+                                    val.w += beta * cv.w;
+                                }
+                                *reinterpret_cast<float4 *>(gD + off) = val;
+                            }
+                        }
+                    }
+                }
+                // 64-row slices (16 lanes of a quarter hold rows): a thread per row
                 // this thread's row of column 0, as an address in this CTA; mapa turns it into a peer's
                 const uint32_t my_row0 = pbuf + static_cast<uint32_t>(row_in_cta) * 4u;
                 // two columns per round: their 2 x cl_split remote loads are in flight together
-                for (int col0 = c.cl_rank * per + half; col0 < my_end; col0 += 2 * halves) {
+                for (int col0 = c.cl_rank * per + half; c.mma_m != 128 && col0 < my_end; col0 += 2 * halves) {
                     float v[2][8];
 #pragma unroll
                     for (int cc = 0; cc < 2; ++cc) {

@@ -105,6 +105,15 @@ __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
     return v;
 }
 
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {  // 16-byte aligned
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
