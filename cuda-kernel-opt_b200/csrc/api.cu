@@ -113,12 +113,12 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
     const bool pair = (M > 128) && (N % 256 == 0) && ((M + 255) / 256) * (N / 256) >= 37;
     const int64_t n_tiles128 = (N + 127) / 128;
     const bool few_tiles = K >= 4096 && n_tiles128 <= 74;
-    if (allow_swap && (M <= 64 || (M <= 128 && K >= 4096 && n_tiles128 <= 37))) {
+    if (allow_swap && (M <= 64 || (M <= 128 && few_tiles))) {
         // Decode shapes: the weights are the whole traffic. Swapped roles stage 128 weight rows and
         // only the activation rows there are per K block; 128-deep K segments halve the barrier
         // round trips per byte. One SM sustains a few tens of GB/s of TMA loads at DRAM latency, so
         // when there are few tiles their K range is split over a cluster to put more SMs to work
-        // (measured: 4 slices beat 2 even at 56 tiles; beyond 64 rows only the smallest N gain).
+        // (measured: 4 slices beat 2 even at 56 tiles; beyond 64 rows the swapped form is used only with the cluster split).
         p->swap_ab = 1;
         p->tile_m = static_cast<int>((M + 15) / 16 * 16);
         p->tile_n = 128;

@@ -161,8 +161,10 @@ def test_swapped_roles_and_cluster_reduce_domain(pkg):
     assert (d.swap_ab, d.split_k, d.cluster_reduce) == (1, 4, 1) and pkg.validate(16, 3584, 8192, pkg.BF16, d) == pkg.OK
     d = pkg.default_params(128, 28672, 8192, pkg.BF16)                                     # swapped two-CTA pair
     assert (d.swap_ab, d.cta_group, d.tile_m, d.tile_n) == (1, 2, 128, 256) and pkg.validate(128, 28672, 8192, pkg.BF16, d) == pkg.OK
-    d = pkg.default_params(128, 7168, 8192, pkg.BF16)
-    assert d.swap_ab == 0 and pkg.validate(128, 7168, 8192, pkg.BF16, d) == pkg.OK
+    d = pkg.default_params(128, 7168, 8192, pkg.BF16)                                      # few tiles: swapped, cluster over K
+    assert (d.swap_ab, d.split_k, d.cluster_reduce) == (1, 4, 1) and pkg.validate(128, 7168, 8192, pkg.BF16, d) == pkg.OK
+    d = pkg.default_params(128, 10240, 8192, pkg.BF16)                                     # in between: the plain tile
+    assert d.swap_ab == 0 and pkg.validate(128, 10240, 8192, pkg.BF16, d) == pkg.OK
     # a swapped pair: 256 weight rows per tile, activation rows in multiples of 32; slices x 2 must fit a cluster of 8
     sp = dict(swap_ab=1, cta_group=2, tile_m=64, tile_n=256, bar_step_rows_a=64, bar_step_rows_b=256)
     assert ok(**sp) == pkg.OK and ok(**dict(sp, tile_m=48, bar_step_rows_a=48)) == pkg.INVALID_CONFIG
