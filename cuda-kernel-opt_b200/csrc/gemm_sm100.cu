@@ -808,29 +808,41 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     const int row4 = w.m0 + static_cast<int>(rank) * c.cta_rows_a + lane * 4;
                     const bool rows_ok = row4 < c.M;
                     const uint32_t my_rows = pbuf + static_cast<uint32_t>(lane) * 16u;
-                    for (int col = c.cl_rank * per + e; col < my_end; col += c.epi_warps) {
-                        const int gcol = w.n0 + col;
-                        if (gcol >= c.N) break;
-                        // slices are added in ascending order, four remote loads in flight at a time
-                        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                        const uint32_t src = my_rows + static_cast<uint32_t>(col) * 512u;
+                    // two columns per round: up to eight 16-byte remote loads in flight per lane
+                    for (int col0 = c.cl_rank * per + e; col0 < my_end; col0 += 2 * c.epi_warps) {
+                        float4 sum[2];
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc) sum[cc] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        // slices are added in ascending order, four at a time
                         for (int base4 = 0; base4 < c.cl_split; base4 += 4) {
-                            float4 v[4];
+                            float4 v[2][4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                if (base4 + i < c.cl_split) v[i] = ld_shared_cluster_v4(mapa_shared(src, static_cast<uint32_t>((base4 + i) * CG) + rank));
+                            for (int cc = 0; cc < 2; ++cc) {
+                                const int col = col0 + cc * c.epi_warps;
+                                const uint32_t src = my_rows + static_cast<uint32_t>(col) * 512u;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                if (base4 + i < c.cl_split) {
-                                    sum.x += v[i].x;
-                                    sum.y += v[i].y;
-                                    sum.z += v[i].z;
-                                    sum.w += v[i].w;
-                                }
+                                for (int i = 0; i < 4; ++i)
+                                    if (base4 + i < c.cl_split && col < my_end)
+                                        v[cc][i] = ld_shared_cluster_v4(mapa_shared(src, static_cast<uint32_t>((base4 + i) * CG) + rank));
+                            }
+#pragma unroll
+                            for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    if (base4 + i < c.cl_split && col0 + cc * c.epi_warps < my_end) {
+                                        sum[cc].x += v[cc][i].x;
+                                        sum[cc].y += v[cc][i].y;
+                                        sum[cc].z += v[cc][i].z;
+                                        sum[cc].w += v[cc][i].w;
+                                    }
                         }
-                        if (rows_ok) {
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc) {
+                            const int col = col0 + cc * c.epi_warps;
+                            const int gcol = w.n0 + col;
+                            if (!(rows_ok && col < my_end && gcol < c.N)) continue;
                             const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row4);
-                            float4 val = make_float4(alpha * sum.x, alpha * sum.y, alpha * sum.z, alpha * sum.w);
+                            float4 val = make_float4(alpha * sum[cc].x, alpha * sum[cc].y, alpha * sum[cc].z, alpha * sum[cc].w);
                             if (out_half) {
                                 if (beta != 0.0f) {
                                     const uint2 cv = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + off);
