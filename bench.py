@@ -7,9 +7,11 @@ D = A * B^T of the workload's shape. Default workload: the configuration the hea
 quoted on, M = N = K = 8192, fp16 inputs (uniform[-1,1), seed 2), fp32 accumulate and output.
 
 N > 1 is launched by torch.distributed.run, one process per GPU. The default workload shards
-along M with no collective: every rank multiplies its own 8192-row block of A with the replicated
-B^T (weak scaling: the box computes a (8192*N) x 8192 x 8192 product). `--workload c5_splitk`
-is the one workload with a real exchange step (fp32 reduce-scatter over NCCL).
+along M with no collective, as the baseline states it: the 8192 rows of A and D are split into N
+row blocks, one per GPU, B^T is replicated (strong scaling of one 8192^3 product; the line also
+carries the per-GPU rate of a full 8192^3 on every GPU at once). `--scaling weak` gives every GPU
+its own 8192-row block of a (8192*N)-row A instead. `--workload c5_splitk` is the one workload
+with a real exchange step (fp32 reduce-scatter, fused into the GEMM epilogue over NVLink).
 
 Rank 0 prints ONE JSON line. `value` is whole-job throughput with inputs resident in HBM;
 `e2e` is the same metric through the host-buffer call of the C ABI (copies inside the timed
@@ -106,6 +108,15 @@ class ClockSampler(threading.Thread):
             self.sample()
             time.sleep(0.0005)
 
+    def energy_mj(self):
+        """Total energy the GPU has drawn since the driver loaded, in millijoules (read-only NVML counter), or None."""
+        if self.nv is None:
+            return None
+        try:
+            return int(self.nv.nvmlDeviceGetTotalEnergyConsumption(self.h))
+        except Exception:
+            return None
+
     def summary(self):
         sm = sorted(self.sm)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
@@ -143,18 +154,33 @@ def cpu_reference_rate(workload: str, seconds_budget: float, steps: int = 1, war
     use_ref = oracle.have_ref() and N == K          # the reference reads B^T with pitch n: square only
     threads = 1
     if all_threads:
-        threads = max(1, min(os.cpu_count() or 1, 8 if use_ref else 64))
+        threads = max(1, os.cpu_count() or 1)
+        if use_ref:
+            # one instance of the reference's fixture class per thread, each holding A, B, C and the result at
+            # N x N (4 + 12 bytes per element): use every core that memory allows
+            per_instance = 12.5 * N * N
+            try:
+                import psutil
+                threads = max(1, min(threads, int(0.5 * psutil.virtual_memory().available / per_instance)))
+            except Exception:
+                threads = min(threads, 8)
     Bt = oracle.fill_u16((N, K), seed, oracle.TENSOR_B, int(db[0]), float(db[1]), dtype)
     if use_ref:
         rate_guess = 0.6e9                           # flop/s of the scalar loop on one core
         rows = int(max(1, min(M, seconds_budget * rate_guess / (2.0 * N * K) / max(1, steps + warmup))))
         A = oracle.fill_u16((rows * threads, K), seed, oracle.TENSOR_A, int(da[0]), float(da[1]), dtype)
         res = np.zeros((rows, N), np.float32)
-        sessions = []
-        for t in range(threads):
+        sessions = [None] * threads
+
+        def make(t):                                 # the fixture's constructor fills four N x N arrays: in parallel
             s = oracle.RefSession(N, dtype)
             s.load(np.ascontiguousarray(A[t * rows:(t + 1) * rows]), Bt, None)
-            sessions.append(s)
+            sessions[t] = s
+        makers = [threading.Thread(target=make, args=(t,)) for t in range(threads)]
+        for t in makers:
+            t.start()
+        for t in makers:
+            t.join()
 
         def step():
             if threads == 1:
@@ -184,7 +210,7 @@ def cpu_reference_rate(workload: str, seconds_budget: float, steps: int = 1, war
     tflops = flops_of(total_rows, N, K) / dt / 1e12
     for s in (sessions if use_ref else []):
         s.close()
-    info = {"value": tflops, "unit": "TFLOPS", "cores": threads, "kind": kind,
+    info = {"value": tflops, "unit": "TFLOPS", "cores": threads, "host_cores": os.cpu_count(), "kind": kind,
             "sample": f"{total_rows} of {M} rows of D (all {N} columns, K = {K}) per step, "
                       f"{'the reference GetNumIncorrect loop (matmul_test.h:307-326)' if use_ref else 'CPU restatement of that loop'}"}
     return tflops, info, dt * 1e3
@@ -198,7 +224,7 @@ def run_reference_arm(args):
     tflops, info, ms = cpu_reference_rate(args.workload, seconds_budget=40.0, steps=args.steps, warmup=args.warmup, all_threads=True)
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOPS", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16" if dts == "f16" else "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "M": M, "N": N, "K": K, "device": "host CPU", "sample": info["sample"]},
         "cpu_baseline": info,
@@ -375,11 +401,91 @@ def run_ours(args):
         exposed_ms = sum(e1.elapsed_time(e2) for _, e1, e2 in ev) / args.steps
     st, info = pkg.device_status()
     assert st == pkg.OK, f"device status {st} {info}"
+    step_ms = None if graph is not None else [round(e0.elapsed_time(e1), 5) for e0, e1, _ in ev]
     t = torch.tensor([total_ms, kernel_ms, exposed_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, kernel_ms, exposed_ms = (float(x) for x in t.tolist())
     ms_per_step = total_ms / args.steps
+
+    # ---- N > 1, strong scaling of a square workload: the per-GPU rate when every GPU multiplies a full
+    # M x N x K at the same time (what `--scaling weak` times), as an extra key beside the sharded number
+    weak_extra = None
+    if world > 1 and scaling == "strong" and not nshard and not splitk_ranks and not library:
+        A_full = torch.empty((M, K), dtype=tdt, device=dev)
+        pkg.fill_device(A_full, seed, 1, int(da[0]), float(da[1]), begin=0)
+        D_full = torch.empty((M, N), dtype=torch.float32, device=dev)
+        p_full = pkg.default_params(M, N, K, dtype)
+        ws_full = torch.empty(max(pkg.workspace_bytes(M, N, K, p_full), 16), dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            pkg.gemm(A_full, Bt, None, D_full, 1.0, 0.0, p_full, workspace=ws_full)
+        barrier()
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record()
+        for _ in range(args.steps):
+            pkg.gemm(A_full, Bt, None, D_full, 1.0, 0.0, p_full, workspace=ws_full)
+        w1.record()
+        barrier()
+        tw = torch.tensor([w0.elapsed_time(w1) / args.steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+        per_gpu = flops_of(M, N, K) / (float(tw.item()) * 1e-3) / 1e12
+        weak_extra = {"what": f"every GPU multiplies its own {M} x {N} x {K} at the same time (--scaling weak)",
+                      "ms_per_step": float(tw.item()), "per_gpu_tflops": per_gpu, "box_tflops": per_gpu * world}
+        del A_full, D_full, ws_full
+
+    # ---- the loaded state: seconds of back-to-back launches with clock, power and energy readings
+    # (the timed region above is over before the power limit settles or NVML takes a sample under load)
+    sustained = None
+    if args.sustained_seconds > 0 and not short_step and not splitk_ranks and bound == "tensor":
+        def sustained_leg(fn, leg_flops):
+            smp = ClockSampler(local)
+            chunk = max(1, int(0.02 / max(kernel_ms * 1e-3, 1e-5)))
+            marks = []
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            en0 = smp.energy_mj()
+            smp.start()
+            t_host = time.perf_counter()
+            s0.record()
+            n = 0
+            while time.perf_counter() - t_host < args.sustained_seconds:
+                for _ in range(chunk):
+                    fn(n)
+                    n += 1
+                mk = torch.cuda.Event()
+                mk.record()
+                marks.append(mk)
+                if len(marks) > 2:                      # at most two chunks queued ahead of the device
+                    marks.pop(0).synchronize()
+            s1.record()
+            torch.cuda.synchronize()
+            en1 = smp.energy_mj()
+            smp.stop_flag = True
+            smp.join()
+            ms = s0.elapsed_time(s1)
+            c = smp.summary()
+            joules = (en1 - en0) / 1e3 if (en0 is not None and en1 is not None) else None
+            tf = leg_flops * n / (ms * 1e-3) / 1e12
+            return {"seconds": ms / 1e3, "launches": n, "tflops": tf, "ms_per_launch": ms / n,
+                    "sm_mhz_median": c["sm_mhz"], "sm_mhz_min": c["sm_min_mhz"], "reasons": c["reasons"],
+                    "ms_x_mhz": (ms / n) * c["sm_mhz"] if c["sm_mhz"] else None,
+                    "power_w_mean": (joules / (ms / 1e3)) if joules is not None else None,
+                    "joules_per_tflop": (joules / (leg_flops * n / 1e12)) if joules is not None else None}
+
+        if library:
+            sustained = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
+        else:
+            sustained = sustained_leg(lambda i: pkg.gemm(As[i % rot], Bts[i % rot], None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None),
+                                      flops_of(m_loc, n_loc, k_loc))
+            st, info = pkg.device_status()
+            assert st == pkg.OK, f"device status {st} {info}"
+            if world == 1 and rank == 0:
+                # the vendor library in the same harness, same duration, directly after: a number for scale
+                # (joules per TFLOP side by side); it is not on this repository's path
+                sustained["library_for_scale"] = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()),
+                                                                flops_of(m_loc, n_loc, k_loc))
+        sustained["frac_of_sustained_peak"] = sustained["tflops"] / peaks()["bf16_tflops_sustained"]
+        sustained["peak_source"] = f"{peaks()['_source']} cuBLAS bf16 8192^3 sustained"
 
     job_flops = flops_of(M, N, K) * (world if scaling == "weak" else 1)
     job_bytes = bytes_of(M, N, K) * (world if scaling == "weak" else 1)
@@ -393,18 +499,20 @@ def run_ours(args):
     # ---- roofline of the dominant kernel (per GPU): algorithmic work of one launch / its duration
     pk = peaks()
     launch_flops, launch_bytes = flops_of(m_loc, n_loc, k_loc), bytes_of(m_loc, n_loc, k_loc)
+    ncu_traffic = NCU_TRAFFIC_BYTES.get(args.workload) if (m_loc, n_loc, k_loc) == (M, N, K) else None   # captured on the whole shape only
     long_run = total_ms > 1000.0
     if bound == "tensor":
         achieved = launch_flops / (kernel_ms * 1e-3) / 1e12
         peak = pk["bf16_tflops_sustained"] if long_run else pk["bf16_tflops"]
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel": "gemm_sm100_kernel", "kernel_ms": kernel_ms,
+                "traffic": ncu_traffic, "traffic_source": "ncu capture of one launch of this workload, profiles/ (not a value of this run)",
+                "kernel": "gemm_sm100_kernel", "kernel_ms": kernel_ms,
                 "peak_source": f"{pk['_source']} cuBLAS bf16 8192^3, {'sustained' if long_run else 'burst'}",
                 "frac_of_nominal_2250": achieved / NOMINAL_TFLOPS, "algorithmic_flops_per_launch": launch_flops}
     else:
         achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel": "gemm_sm100_kernel", "kernel_ms": kernel_ms,
+                "traffic": ncu_traffic, "kernel": "gemm_sm100_kernel", "kernel_ms": kernel_ms,
                 "peak_source": f"{pk['_source']} copy bandwidth", "algorithmic_bytes_per_launch": launch_bytes}
 
     # ---- end to end: the host-buffer call of the C ABI (H2D of A, B^T, launch, D2H of D, sync)
@@ -458,12 +566,11 @@ def run_ours(args):
 
     # ---- optional reported baseline: the reference's own WMMA kernel recompiled for sm_100a
     wmma = None
-    if args.wmma_baseline and rank == 0 and world == 1 and M == N == K:
-        exe = os.path.join(ROOT, "oracle", "_ref", "ref_wmma_async")
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_wmma_async")
+    want_wmma = args.wmma_baseline == 1 or (args.wmma_baseline < 0 and os.path.exists(exe) and not library)
+    if want_wmma and rank == 0 and world == 1 and M == N == K:
         if os.path.exists(exe):
             import subprocess
-            del A, Bt, D
-            torch.cuda.empty_cache()
             r = subprocess.run([exe, str(M), "128", "64", "1", "3", "4", "8", "2"], capture_output=True, text=True, timeout=600)
             try:
                 wmma = json.loads(r.stdout.strip().splitlines()[-1])
@@ -495,6 +602,13 @@ def run_ours(args):
             line["impl"] = "library (torch.matmul, for scale: not this repository's kernel)"
             line["gpu_launches"] = 0
             line["config"].pop("params", None)
+        if step_ms is not None:
+            line["step_ms"] = step_ms
+        if sustained:
+            line["sustained"] = sustained
+        if weak_extra:
+            line["weak_scaling"] = weak_extra
+        line["host_cores"] = os.cpu_count()
         if roles:
             line["role_counters"] = roles
         if wmma:
@@ -527,7 +641,12 @@ def main():
                     help="library: torch.matmul in this harness, a number for scale (single-process workloads only)")
     ap.add_argument("--shard-of", type=int, default=0, help="one GPU: time rank 0's shard of a G-GPU run of an N-sharded workload")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c3_8192_f16")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
+                    help="N > 1, square workloads: strong = the workload's M rows split over the GPUs (the baseline's "
+                         "configuration), weak = every GPU gets M rows of its own")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="after the timed steps, this many seconds of back-to-back launches with clock, power and energy "
+                         "readings (0 = skip)")
     ap.add_argument("--exchange", choices=["nccl", "fused"], default="fused",
                     help="split-K workloads on N > 1: NCCL reduce-scatter after the GEMM, or fused into its epilogue")
     ap.add_argument("--check", action="store_true", help="split-K workloads: compare fused and NCCL results")
@@ -536,8 +655,9 @@ def main():
     ap.add_argument("--graph", type=int, default=-1, help="1: issue the timed steps as one CUDA graph, 0: one call per step; default: graph when a step is expected to take under 0.3 ms")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--wmma-baseline", action="store_true",
-                    help="also time the reference's WMMA kernel recompiled for sm_100a (oracle/_ref, if built)")
+    ap.add_argument("--wmma-baseline", type=int, default=-1,
+                    help="time the reference's own WMMA kernel recompiled for sm_100a (oracle/_ref/ref_wmma_async) beside "
+                         "the number: 1 = yes, 0 = no, default = yes on one GPU when the binary is there")
     ap.add_argument("--role-counters", action="store_true", help="add in-kernel per-role cycle counters of CTA 0")
     args = ap.parse_args()
     if args.impl == "reference":

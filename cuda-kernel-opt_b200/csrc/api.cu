@@ -42,6 +42,13 @@ int fail_cuda(cudaError_t e) {
     t_last_cuda_error = static_cast<int>(e);
     return B200_CUDA_ERROR;
 }
+}  // namespace
+
+// For the library's other translation units: remember the CUDA error behind a B200_CUDA_ERROR
+// return so that b200_last_cuda_error() reports it.
+int record_cuda_error(int cuda_error) { return fail_cuda(static_cast<cudaError_t>(cuda_error)); }
+
+namespace {
 
 // First call on a device: check the architecture, resolve the driver's tensor-map encoder and
 // opt the kernels into large dynamic shared memory.
@@ -627,6 +634,14 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
     cudaError_t e = cudaSuccess;
     int block_id = 0;
     const int steps = R > Cn ? R : Cn;
+    // An error return must not leave copies or kernels of this call in flight on the session's
+    // streams: the caller may free or reuse its host buffers as soon as the call is back.
+    auto drained = [s](int status) {
+        cudaStreamSynchronize(s->stream);
+        cudaStreamSynchronize(s->compute);
+        cudaStreamSynchronize(s->download);
+        return status;
+    };
     for (int t = 0; t < steps; ++t) {
         if (t < R) {
             const int64_t r0 = t * brows, rows = (M - r0 < brows) ? (M - r0) : brows;
@@ -635,17 +650,17 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
             if (e == cudaSuccess && beta != 0.0f)
                 e = cudaMemcpyAsync(s->dC + static_cast<size_t>(r0) * N, hC + static_cast<size_t>(r0) * N,
                                     static_cast<size_t>(rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
-            if (e != cudaSuccess) return fail_cuda(e);
+            if (e != cudaSuccess) return drained(fail_cuda(e));
         }
         if (t < Cn) {
             const int64_t c0 = t * bcols, cols = (N - c0 < bcols) ? (N - c0) : bcols;
             e = cudaMemcpyAsync(dB8 + static_cast<size_t>(c0) * K * 2, hB8 + static_cast<size_t>(c0) * K * 2,
                                 static_cast<size_t>(cols) * K * 2, cudaMemcpyHostToDevice, s->stream);
-            if (e != cudaSuccess) return fail_cuda(e);
+            if (e != cudaSuccess) return drained(fail_cuda(e));
         }
         e = cudaEventRecord(s->up[t], s->stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(s->compute, s->up[t], 0);
-        if (e != cudaSuccess) return fail_cuda(e);
+        if (e != cudaSuccess) return drained(fail_cuda(e));
         // blocks that became computable with this step: row t with columns 0..min(t, Cn-1), column t with rows 0..t-1
         for (int pass = 0; pass < 2; ++pass) {
             const int count = pass == 0 ? ((t < R) ? ((t < Cn ? t : Cn - 1) + 1) : 0) : ((t < Cn) ? (t < R ? t : R) : 0);
@@ -657,24 +672,21 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
                 const int st = gemm_impl(dtype, dA8 + static_cast<size_t>(r0) * K * 2, dB8 + static_cast<size_t>(c0) * K * 2,
                                          beta != 0.0f ? s->dC + off : nullptr, s->dD + off, alpha, beta, rows, cols, K, p, nullptr,
                                          0, s->compute, nullptr, N);
-                if (st != B200_OK) {
-                    cudaDeviceSynchronize();
-                    return st;
-                }
+                if (st != B200_OK) return drained(st);
                 e = cudaEventRecord(s->done[block_id], s->compute);
                 if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[block_id], 0);
                 if (e == cudaSuccess)
                     e = cudaMemcpy2DAsync(hD + off, static_cast<size_t>(N) * 4, s->dD + off, static_cast<size_t>(N) * 4,
                                           static_cast<size_t>(cols) * 4, static_cast<size_t>(rows), cudaMemcpyDeviceToHost,
                                           s->download);
-                if (e != cudaSuccess) return fail_cuda(e);
+                if (e != cudaSuccess) return drained(fail_cuda(e));
                 ++block_id;
             }
         }
     }
     e = cudaStreamSynchronize(s->download);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
-    if (e != cudaSuccess) return fail_cuda(e);
+    if (e != cudaSuccess) return drained(fail_cuda(e));
     return B200_OK;
 }
 

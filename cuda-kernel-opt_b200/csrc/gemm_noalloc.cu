@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "../../include/b200_gemm.h"
+#include "gemm_sm100.cuh"
 
 namespace {
 
@@ -29,12 +30,13 @@ std::mutex g_setup_mutex;
 int scratch_address(float **out) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_CUDA_ERROR;
+    if (e != cudaSuccess) return b200::record_cuda_error(static_cast<int>(e));
+    if (dev < 0 || dev >= kMaxDevices) return B200_UNSUPPORTED_DEVICE;
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (!g_scratch_ptr[dev]) {
         float *ptr = nullptr;
         e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_splitk_scratch);
-        if (e != cudaSuccess || !ptr) return B200_CUDA_ERROR;
+        if (e != cudaSuccess || !ptr) return b200::record_cuda_error(static_cast<int>(e != cudaSuccess ? e : cudaErrorUnknown));
         g_scratch_ptr[dev] = ptr;
     }
     *out = g_scratch_ptr[dev];
@@ -47,7 +49,8 @@ extern "C" int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt
                                         float beta, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
                                         void *stream) {
     if (!p || p->split_k < 2) return B200_INVALID_CONFIG;  // without a K split no scratch is needed: use b200_gemm_*
-    if (M <= 0 || N <= 0) return B200_INVALID_SHAPE;
+    if (M <= 0 || N <= 0 || M > (int64_t(1) << 30) || N > (int64_t(1) << 30)) return B200_INVALID_SHAPE;
+    if (p->split_k > 64) return B200_INVALID_CONFIG;   // the product below cannot wrap: 2^6 * 2^30 * 2^30
     const size_t need = static_cast<size_t>(p->split_k) * static_cast<size_t>(M) * static_cast<size_t>(N);
     if (need > kScratchFloats) return B200_WORKSPACE_TOO_SMALL;  // beyond the built-in 32 MiB: pass your own workspace
     float *scratch = nullptr;

@@ -34,6 +34,9 @@
 // its tensor memory and returns normally.
 #include <cuda_fp16.h>
 
+#include <mutex>
+#include <vector>
+
 #include "gemm_sm100.cuh"
 #include "ptx_sm100.cuh"
 
@@ -214,7 +217,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int ld_cd = g.ld_cd;
     const bool swap_ab = g.swap_ab != 0;
     const bool out_half = g.out_half != 0;   // C and D are fp16 (never with a workspace, tail or push path)
-    const int dbg = g.debug_flags;  // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage)
+    // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage); bits 2 and 3: the
+    // epilogue withholds its "slice staged" / "slice read" arrivals of the cluster reduce, so that those
+    // bounded waits run out and the launch ends with a DEVICE_TIMEOUT record (tests of the failure path)
+    const int dbg = g.debug_flags;
     const float g_alpha = g.alpha, g_beta = g.beta;
     const float *const gC = g.C;
     float *const gD = g.D;
@@ -791,7 +797,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     else mbar_arrive(tmem_empty0 + 8u * acc);
                 }
                 // the peers of this CTA: the CTA with the same rank in its pair, in every slice of the cluster
-                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane * CG) + rank));
+                if (lane < c.cl_split && !(dbg & 4)) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane * CG) + rank));
                 if (e == 0 && lane == 0) B200_TL(29);
                 // B: when all slices are staged, this CTA sums its share of the tile's columns over the
                 // cluster in slice order (the order of the workspace form) and writes D.
@@ -908,7 +914,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 }
                 __syncwarp();
                 if (e == 0 && lane == 0) B200_TL(31);
-                if (lane < c.cl_split) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane * CG) + rank));
+                if (lane < c.cl_split && !(dbg & 8)) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane * CG) + rank));
                 continue;
             }
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
@@ -1088,13 +1094,17 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         cluster_arrive();
         cluster_wait();
     }
-    if (push_world > 0 && tid == 0 && !*abort_flag) {
+    if (push_world > 0 && tid == 0) {
         // Count finished CTAs; the last one tells every owner that this rank's slots are complete.
+        // Every CTA counts, aborted or not, and the last one always zeroes the counter, so a launch
+        // that timed out leaves it ready for the next one; the flags are raised only when no wait of
+        // this launch expired (a CTA records its timeout in the status word before it counts).
         __threadfence();
         const unsigned int done = atomicAdd(g.push_done, 1u);
         if (done == gridDim.x - 1) {
             __threadfence_system();
-            for (int o = 0; o < push_world; ++o) *reinterpret_cast<volatile int *>(g.push_flag[o] + push_rank) = g.push_epoch;
+            if (*reinterpret_cast<volatile int *>(&g_device_status[0]) == 0)
+                for (int o = 0; o < push_world; ++o) *reinterpret_cast<volatile int *>(g.push_flag[o] + push_rank) = g.push_epoch;
             __threadfence_system();
             *g.push_done = 0u;
         }
@@ -1152,7 +1162,9 @@ __global__ void push_reduce_kernel(const float4 *slots, const int *flags, int wo
         const long long t0 = clock64();
         int ok = 1;
         for (int s = 0; s < world && ok; ++s) {
-            while (*reinterpret_cast<const volatile int *>(flags + s) != epoch) {
+            // Epochs only grow, so a flag past `epoch` also means "epoch `epoch` has arrived": the source
+            // may already have pushed its next step (into the other slot area) before this owner looked.
+            while (static_cast<int>(*reinterpret_cast<const volatile int *>(flags + s) - epoch) < 0) {
                 __nanosleep(200);
                 if (clock64() - t0 > budget) {
                     ok = 0;
@@ -1356,6 +1368,32 @@ KernelFn pick_kernel(int cta_group, bool simple, bool prof) {
     if (simple) return prof ? gemm_sm100_kernel<1, true, true> : gemm_sm100_kernel<1, true, false>;
     return prof ? gemm_sm100_kernel<1, false, true> : gemm_sm100_kernel<1, false, false>;
 }
+
+// How many clusters of the launch's size the current device holds at once (it depends on how the
+// SMs are grouped), asked once per {device, kernel instance, cluster size, shared-memory size}
+// and remembered; -1 = the runtime could not say. Callers on different host threads share the
+// table, hence the lock.
+int max_active_clusters(KernelFn fn, const cudaLaunchConfig_t &cfg, int cluster) {
+    struct Entry {
+        int dev;
+        KernelFn fn;
+        int cluster;
+        size_t smem;
+        int value;
+    };
+    static std::mutex mu;
+    static std::vector<Entry> table;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry &e : table)
+        if (e.dev == dev && e.fn == fn && e.cluster == cluster && e.smem == cfg.dynamicSmemBytes) return e.value;
+    int n = 0;
+    const int value = (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess && n > 0) ? n : -1;
+    cudaGetLastError();
+    table.push_back({dev, fn, cluster, cfg.dynamicSmemBytes, value});
+    return value;
+}
 }  // namespace
 
 int profile_slots() { return kProfSlots; }
@@ -1408,15 +1446,7 @@ int launch_gemm(const Plan &p, const GemmArgs &args, cudaStream_t stream) {
     if (p.cluster_reduce) {
         // A persistent grid wants every cluster resident at once: ask how many clusters of this
         // size the device holds (it depends on how the SMs are grouped) and cap the grid there.
-        static int max_clusters[16][9];  // per device and cluster size; 0 = not asked yet, -1 = unknown
-        int dev = 0;
-        cudaGetDevice(&dev);
-        int &mc = max_clusters[dev & 15][cluster];
-        if (mc == 0) {
-            int n = 0;
-            mc = (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess && n > 0) ? n : -1;
-            cudaGetLastError();
-        }
+        const int mc = max_active_clusters(fn, cfg, cluster);
         if (mc > 0 && grid > mc * cluster) cfg.gridDim = dim3(static_cast<unsigned>(mc * cluster), 1, 1);
     }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, args);

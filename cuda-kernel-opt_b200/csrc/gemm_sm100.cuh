@@ -70,6 +70,8 @@ int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int sp
                               unsigned int *done, int world, int rank, int epoch, cudaStream_t stream);
 // Second step of the tail split: D tile = alpha * sum of its K slices + beta * C for the r tail tiles.
 int launch_tail_reduce(const GemmArgs &args, cudaStream_t stream);
+// Remembers the cudaError_t behind a B200_CUDA_ERROR return for b200_last_cuda_error(); returns B200_CUDA_ERROR.
+int record_cuda_error(int cuda_error);
 int prepare_kernels();  // opt-in shared memory size; once per device
 int profile_slots();    // int64 slots per CTA of the profile buffer (16; 32 in a -DB200_TIMELINE build)
 

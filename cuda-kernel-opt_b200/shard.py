@@ -83,11 +83,13 @@ class PushExchange:
     (b200_gemm_push / b200_push_reduce): peers' fp32 tiles arrive in this GPU's slot area by plain
     NVLink stores while the GEMM is still running; what is left after the GEMM is a flag wait
     and one ordered sum of `world` local slabs. torch.distributed only carries the 64-byte IPC
-    handles at set-up and a barrier per step (slot reuse).
+    handles at set-up.
 
     Two slot areas alternate by step. No per-step barrier is needed: a rank starts the push of step
     e+2 (same area as step e) only after its own reduce of step e+1, which waited for every peer's
-    flag of step e+1, which each peer raised (in stream order) after its reduce of step e.
+    flag of step e+1, which each peer raised (in stream order) after its reduce of step e. A rank whose host
+    falls behind may therefore find a peer's flag already one epoch ahead when its own reduce looks: the
+    reduce accepts any flag that has reached its epoch (the data of its epoch sits in the other area, intact).
     """
 
     def __init__(self, pkg, M: int, N: int, group=None):
@@ -139,9 +141,9 @@ class PushExchange:
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
-    def gemm_reduce_scatter(self, A, Bt, D_rows, params, Cm_rows=None, alpha=1.0, beta=0.0, stream=None, workspace=None):
-        """A: M x K_local, Bt: N x K_local (this rank's K slice); D_rows: (M/world) x N fp32, this
-        rank's rows of the full product. Asynchronous on the current stream."""
+    def push(self, A, Bt, params, stream=None, workspace=None):
+        """First half of a step: this rank's K slice is multiplied and every finished tile is stored into
+        its owner's slot area (b200_gemm_push). Starts a new epoch. Asynchronous on the current stream."""
         import torch
         pkg, lib = self.pkg, self.pkg.lib()
         dtype = pkg.BF16 if A.dtype == torch.bfloat16 else pkg.F16
@@ -156,12 +158,26 @@ class PushExchange:
                                 self.done, self.epoch, workspace.data_ptr() if need else None, need, sptr)
         if st != pkg.OK:
             raise pkg.B200Error(st, "b200_gemm_push")
+
+    def reduce(self, D_rows, Cm_rows=None, alpha=1.0, beta=0.0, stream=None):
+        """Second half: waits (on the device, bounded) until every source's flag has reached the current epoch,
+        then sums the slots of this rank's rows into D_rows (b200_push_reduce)."""
+        import torch
+        pkg, lib = self.pkg, self.pkg.lib()
+        sptr = stream if stream is not None else torch.cuda.current_stream(D_rows.device).cuda_stream
+        odd = self.epoch & 1
         st = lib.b200_push_reduce(self.slots.value + (self.area_bytes if odd else 0), self.flags, self.world, self.epoch,
                                   Cm_rows.data_ptr() if Cm_rows is not None else None, D_rows.data_ptr(), alpha, beta,
                                   self.rows, self.N, sptr)
         if st != pkg.OK:
             raise pkg.B200Error(st, "b200_push_reduce")
         return D_rows
+
+    def gemm_reduce_scatter(self, A, Bt, D_rows, params, Cm_rows=None, alpha=1.0, beta=0.0, stream=None, workspace=None):
+        """A: M x K_local, Bt: N x K_local (this rank's K slice); D_rows: (M/world) x N fp32, this
+        rank's rows of the full product. Asynchronous on the current stream."""
+        self.push(A, Bt, params, stream=stream, workspace=workspace)
+        return self.reduce(D_rows, Cm_rows, alpha, beta, stream=stream)
 
     def close(self):
         import torch
@@ -176,3 +192,57 @@ class PushExchange:
             if p:
                 lib.b200_peer_free(p)
         self.slots = self.flags = self.done = None
+
+
+class PeerLeft(RuntimeError):
+    """Raised by Membership.check() when another rank has announced that it left, or has stopped beating."""
+
+    def __init__(self, rank: int, reason: str):
+        self.rank, self.reason = rank, reason
+        super().__init__(f"rank {rank} left the job: {reason}")
+
+
+class Membership:
+    """Host-side failure detection for the multi-GPU paths, between steps.
+
+    The exchange kernels wait for peers on the device (bounded, with a status record), and a collective
+    waits inside NCCL; neither should be entered when a peer is already known to be gone. Every rank
+    therefore keeps two notes in the job's key-value store (the TCP store torch.distributed rendezvoused
+    on): a heartbeat it refreshes once per step, and a leave note it writes when it goes between steps -
+    with none of its kernels or collectives in flight. check(), called before the next launch, raises
+    PeerLeft when a peer has left a note or its heartbeat is older than `stale_after` seconds, so the
+    survivors stop before they would wait. A peer that dies without a note and inside `stale_after` is
+    caught one level down: by the process group's timeout on the next collective, or by the bounded
+    wait of the exchange kernel (B200_DEVICE_TIMEOUT). The reference is single-GPU and has nothing of
+    the kind (matmul_shmem_tc_async_opt_port_2.cu:1503-1510).
+    """
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "b200/members", stale_after: float = 30.0, clock=None):
+        import time
+        self.store, self.rank, self.world, self.prefix, self.stale_after = store, rank, world, prefix, stale_after
+        self.clock = clock or time.time
+        self.beat(0)
+
+    def _key(self, kind: str, rank: int) -> str:
+        return f"{self.prefix}/{kind}/{rank}"
+
+    def beat(self, step: int) -> None:
+        """Refresh this rank's heartbeat (once per step is enough)."""
+        self.store.set(self._key("beat", self.rank), f"{step}:{self.clock():.3f}")
+
+    def leave(self, reason: str = "done") -> None:
+        """Announce that this rank is going. Call it between steps, after synchronising the device."""
+        self.store.set(self._key("left", self.rank), reason)
+
+    def check(self) -> None:
+        """Raises PeerLeft if a peer has announced its leave or has not beaten for stale_after seconds."""
+        now = self.clock()
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            if self.store.check([self._key("left", r)]):
+                raise PeerLeft(r, self.store.get(self._key("left", r)).decode())
+            if self.store.check([self._key("beat", r)]):
+                _, stamp = self.store.get(self._key("beat", r)).decode().split(":")
+                if now - float(stamp) > self.stale_after:
+                    raise PeerLeft(r, f"no heartbeat for {now - float(stamp):.1f} s")

@@ -45,6 +45,28 @@ MILESTONES = [
 ]
 
 
+def summarise(stamps):
+    """stamps: one row of %globaltimer values per CTA (nanoseconds, 0 = never stamped), at least 32 columns.
+    Returns (CTAs entered, CTAs with work, rows) where rows = [(milestone, mean, min, max)] in nanoseconds
+    from the first CTA's entry, over the CTAs that had work (an accumulator became ready); milestones no
+    working CTA stamped are left out. Pure numpy: the part of the tool that needs no GPU."""
+    import numpy as np
+    r = np.asarray(stamps, dtype=np.int64)
+    entered = r[:, 13] > 0
+    if not entered.any():
+        return 0, 0, []
+    working = entered & (r[:, 22] > 0)
+    t0 = int(r[entered, 13].min())
+    rows = []
+    for slot, name in MILESTONES:
+        v = r[working, slot]
+        v = v[v > 0] - t0
+        if v.size == 0:
+            continue
+        rows.append((name, float(v.mean()), int(v.min()), int(v.max())))
+    return int(entered.sum()), int(working.sum()), rows
+
+
 def timeline(M: int, N: int, K: int, dtype: str = "bf16", overrides: dict | None = None, out=print):
     import torch
     sys.path.insert(0, ROOT)
@@ -71,20 +93,11 @@ def timeline(M: int, N: int, K: int, dtype: str = "bf16", overrides: dict | None
     torch.cuda.synchronize()
     pkg.lib().b200_set_profile_buffer(None, 0)
     st, info = pkg.device_status()
-    r = prof.cpu()
-    entered = r[:, 13] > 0
-    working = entered & (r[:, 22] > 0)
-    t0 = int(r[entered, 13].min())
+    entered, working, rows = summarise(prof.cpu().numpy())
     out(f"{M} x {N} x {K} {dtype}, params {p.as_dict()}")
-    out(f"CTAs entered {int(entered.sum())}, with work {int(working.sum())}, device status {st}")
-    rows = []
-    for slot, name in MILESTONES:
-        v = r[working, slot]
-        v = v[v > 0] - t0
-        if v.numel() == 0:
-            continue
-        rows.append((name, float(v.float().mean()), int(v.min()), int(v.max())))
-        out(f"  {name:52s} mean {rows[-1][1]:9.0f} ns   min {rows[-1][2]:8d}   max {rows[-1][3]:8d}")
+    out(f"CTAs entered {entered}, with work {working}, device status {st}")
+    for name, mean, lo, hi in rows:
+        out(f"  {name:52s} mean {mean:9.0f} ns   min {lo:8d}   max {hi:8d}")
     return rows
 
 

@@ -27,7 +27,10 @@ extern "C" {
 enum {
     B200_OK = 0,
     B200_INVALID_CONFIG = 1,   /* tunables outside the supported domain, or over the smem/TMEM budget */
-    B200_INVALID_SHAPE = 2,    /* M, N, K not multiples of the tile / K segment, or not positive */
+    B200_INVALID_SHAPE = 2,    /* M, N, K not positive, N not a multiple of 4 or K not a multiple of 8 (rows must be
+                                  16-byte multiples); the split-K and multi-GPU forms add their own rules. Ragged
+                                  tile edges are accepted here; the reference-shaped launchers of b200_matmul.h
+                                  keep the reference's tile-multiple rule */
     B200_INVALID_POINTER = 3,  /* null or misaligned operand (A, Bt, D need 16-byte alignment) */
     B200_CUDA_ERROR = 4,       /* a CUDA runtime/driver call failed; see b200_last_cuda_error() */
     B200_DEVICE_TIMEOUT = 5,   /* a bounded wait inside the kernel expired; see b200_device_status() */
@@ -77,7 +80,10 @@ typedef struct b200_gemm_params {
                       B^T evict_first (A row panels are the reused operand of the grouped tile order),
                       2 = A evict_last, 3 = both evict_last */
     int diagnostic; /* must be 0. Bit 0 issues no MMA, bit 1 no operand load: pipeline ceilings for
-                       profiling; the output is garbage */
+                       profiling; the output is garbage. Bits 2 and 3 (with cluster_reduce) withhold the
+                       "slice staged" / "slice read" arrivals between the CTAs of a cluster, so those
+                       bounded waits expire: the launch returns normally with a B200_DEVICE_TIMEOUT
+                       record (barrier ids 701 / 700) and an unfinished D; for tests of that path */
     int k_order;    /* 0 = every tile sums K ascending; 1 = serpentine: every other tile of a CTA walks K downwards,
                        so consecutive waves meet their shared operand panels while they are still in L2.
                        Changes the fp32 summation order of those tiles (not the tolerance) */
@@ -87,13 +93,15 @@ typedef struct b200_gemm_params {
     int swap_ab;    /* 1 = operand roles swapped inside the kernel for skinny M (decode shapes): the rows of B^T feed
                        the 64/128-row side of the MMA and the few rows of A its N side, so a stage holds
                        tile_n rows of weights and only tile_m rows of activations, and the accumulator is
-                       written to D transposed (coalesced along N). Then tile_n is 64 or 128 and tile_m a
-                       multiple of 16 in [16, 256]; the bar_step fields follow their operands; needs
-                       cta_group = 1 and tail_split = 0, and drains with plain stores. Same results as 0 */
-    int cluster_reduce; /* 1 (with swap_ab = 1, split_k 2, 4 or 8, tile_m <= 128) = the split_k slices of a tile run
-                       as the CTAs of one thread-block cluster and are summed through distributed shared
-                       memory, in slice order: no workspace, no second kernel, same bits as the workspace
-                       form. 0 = slices meet in the workspace */
+                       written to D transposed (coalesced along N). Then tile_n is 64 or 128 with cta_group = 1,
+                       or 256 with the two-CTA pair (cta_group = 2: each CTA stages 128 weight rows and half of
+                       the activation rows); tile_m is a multiple of 16 (32 with the pair) in [16, 256]; the
+                       bar_step fields follow their operands; needs tail_split = 0 and drains with plain
+                       stores. Same results as 0 */
+    int cluster_reduce; /* 1 (with swap_ab = 1, split_k 2, 4 or 8, tile_m <= 128, cta_group * split_k <= 8) = the
+                       split_k slices of a tile run as the CTAs (or CTA pairs) of one thread-block cluster and
+                       are summed through distributed shared memory, in slice order: no workspace, no second
+                       kernel, same bits as the workspace form. 0 = slices meet in the workspace */
     int overlap_launch; /* 1 = programmatic dependent launch: the kernel is launched with programmatic stream
                        serialisation, runs its set-up (barriers, tensor memory, descriptor prefetch) while the
                        previous kernel of the stream finishes, waits for that kernel (griddepcontrol.wait)
@@ -151,9 +159,12 @@ int b200_gemm_f16_out_f16(const void *A, const void *Bt, const void *C, void *D,
  * exceed 8 Mi values; larger problems return B200_WORKSPACE_TOO_SMALL and belong to
  * b200_gemm_f16 / b200_gemm_bf16 with a caller workspace. p->split_k must be >= 2.
  *
- * The first call on a device looks up the array's device address (once per device); make that
- * first call outside any stream capture. No cudaMalloc, cudaFree or allocating library routine is
- * called, on the first call or later. All calls on a device share the one array: it keeps the
+ * The first call on a device looks up the array's device address (once per device). With lazy
+ * module loading that look-up is also the moment the driver loads this part of the library and
+ * places the 32 MiB array in device memory, which can stall the device: make the first call at
+ * start-up, outside any stream capture and outside the latency-critical region. No cudaMalloc,
+ * cudaFree or allocating library routine is called, on the first call or later, and from the second
+ * call on the device's free memory does not change. All calls on a device share the one array: it keeps the
  * previous call's partials, every element a call reads it has written first (nothing needs
  * clearing), and two calls whose kernels overlap on the GPU (different streams, no ordering)
  * race on it - order them. dtype is B200_F16 or B200_BF16; other arguments as b200_gemm_f16. */
@@ -175,11 +186,14 @@ int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt, const flo
  * (b200_gemm_workspace_bytes) and the sum is what travels, as coalesced 128-bit peer stores.
  *
  * b200_push_reduce, enqueued on the owner after its own b200_gemm_push, waits (bounded; a
- * DEVICE_TIMEOUT record if a peer never arrives) until all `world` flags show `epoch`, then
+ * DEVICE_TIMEOUT record if a peer never arrives) until all `world` flags have reached `epoch`
+ * (a flag already past it also counts: with two slot areas a fast peer may have pushed its next
+ * step before this owner looks), then
  * writes D_rows = alpha * sum over sources of slot[src] + beta * C_rows, sources in ascending
  * order. Use a new epoch (> 0, increasing) for every GEMM; slots of epoch e may be overwritten
  * only after every rank has finished b200_push_reduce of epoch e (a barrier per step, or two
- * alternating slot areas). */
+ * alternating slot areas). After a DEVICE_TIMEOUT read the record with b200_device_status before
+ * the next push: while a record is pending a push raises no flags. */
 int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
                    int world, int rank, void *const *slot_ptrs, void *const *flag_ptrs, void *done_counter, int epoch,
                    void *workspace, size_t workspace_bytes, void *stream);

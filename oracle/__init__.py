@@ -32,7 +32,8 @@ def build(force: bool = False) -> None:
     if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(
             os.path.join(_HERE, "gemm_oracle.c")):
         subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
-    ref_tree = os.environ.get("REFERENCE_TREE", "/root/reference")
+    # the reference checkout: named by REFERENCE_TREE, else looked for beside this repository
+    ref_tree = os.environ.get("REFERENCE_TREE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     if os.path.exists(os.path.join(ref_tree, "matmul_test.h")) and (force or not os.path.exists(_REF)):
         subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE={ref_tree}"], check=True, capture_output=True)
 

@@ -31,3 +31,37 @@ def tolerance_ok(got, want, k, scale=1.0):
 def to_device(torch, bits, dtype_code):
     t = torch.from_numpy(bits.view(np.int16)).cuda()
     return t.view(torch.bfloat16 if dtype_code == 1 else torch.float16)
+
+
+class Guarded:
+    """A device tensor carved out of the middle of a larger allocation whose two margins ("guard bands")
+    hold the byte 0xA5. A store that lands outside the tensor - a clipped edge that is off by a row, a
+    transposed or swapped drain with the wrong pitch - changes a band instead of a neighbouring
+    allocation nobody looks at; check() asserts both bands are untouched. Stands in for a memory
+    checker on machines where none can be run. The tensor starts 512-byte aligned."""
+
+    BYTE = 0xA5
+
+    def __init__(self, torch, shape, dtype, fill=float("nan"), band_bytes=None):
+        self.torch = torch
+        elem = torch.empty((), dtype=dtype).element_size()
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        if band_bytes is None:          # at least 130 rows of the tensor (more than one tile row off) + 4 KiB
+            row = int(shape[-1]) * elem if len(shape) > 1 else 0
+            band_bytes = min(16 << 20, 130 * row + 4096)
+        self.band = -(-band_bytes // 512) * 512
+        self.nbytes = numel * elem
+        self.buf = torch.full((2 * self.band + -(-self.nbytes // 512) * 512,), self.BYTE, dtype=torch.uint8, device="cuda")
+        self.t = self.buf[self.band:self.band + self.nbytes].view(dtype).view(*shape)
+        if fill is not None:
+            self.t.fill_(fill)
+
+    def check(self, what=""):
+        lo = self.buf[:self.band]
+        hi = self.buf[self.band + self.nbytes:]
+        bad_lo = int((lo != self.BYTE).sum())
+        bad_hi = int((hi != self.BYTE).sum())
+        assert bad_lo == 0 and bad_hi == 0, (f"{what}: {bad_lo} bytes changed before the tensor, {bad_hi} after it "
+                                             f"(first after: {int((hi != self.BYTE).nonzero()[0]) if bad_hi else None})")

@@ -10,24 +10,31 @@ import subprocess
 import numpy as np
 import pytest
 
-from helpers import GOLDEN, inputs, to_device, tolerance_ok
+from helpers import GOLDEN, Guarded, inputs, to_device, tolerance_ok
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def run_gemm(pkg, torch, dtype, A, Bt, Cm, alpha, beta, **ov):
+    """One GEMM through the C ABI. D and the workspace (when the configuration needs one) sit between
+    guard bands that must come back untouched; D starts as NaN, so every element must be written."""
     m, k = A.shape
     n = Bt.shape[0]
     p = pkg.default_params(m, n, k, dtype, **ov)
     assert pkg.validate(m, n, k, dtype, p) == pkg.OK, p.as_dict()
     dA, dB = to_device(torch, A, dtype), to_device(torch, Bt, dtype)
     dC = torch.from_numpy(Cm).cuda() if (Cm is not None and beta != 0.0) else None
-    D = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")   # canary: every element must be written
-    pkg.gemm(dA, dB, dC, D, alpha, beta, p)
+    gD = Guarded(torch, (m, n), torch.float32)
+    need = pkg.workspace_bytes(m, n, k, p)
+    gW = Guarded(torch, (need,), torch.uint8, fill=None, band_bytes=1 << 20) if need else None
+    pkg.gemm(dA, dB, dC, gD.t, alpha, beta, p, workspace=gW.t if gW else None)
     st, info = pkg.device_status()
     assert st == pkg.OK, f"device status {st} {info}"
-    return D.cpu().numpy()
+    gD.check(f"D of {m}x{n}x{k} {p.as_dict()}")
+    if gW:
+        gW.check(f"workspace of {m}x{n}x{k} {p.as_dict()}")
+    return gD.t.cpu().numpy()
 
 
 GOLD = sorted(p for p in glob.glob(os.path.join(GOLDEN, "*.npz"))
@@ -289,10 +296,12 @@ def test_fp16_output(pkg, cuda, oracle):
             assert pkg.validate(m, n, k, pkg.F16, p) == pkg.OK, p.as_dict()
             dA, dB = to_device(torch, A, pkg.F16), to_device(torch, Bt, pkg.F16)
             dC = torch.from_numpy(C16).cuda()
-            D = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+            gD = Guarded(torch, (m, n), torch.float16)
+            D = gD.t
             pkg.gemm(dA, dB, dC if beta else None, D, alpha, beta, p)
             st, info = pkg.device_status()
             assert st == pkg.OK, (st, info)
+            gD.check(f"fp16 D of {m}x{n}x{k} {ov}")
             want32 = oracle.gemm(A, Bt, C16.astype(np.float32) if beta else None, alpha, beta, oracle.FP16)
             got = D.cpu().numpy().astype(np.float32)
             assert np.isfinite(got).all()
@@ -420,27 +429,90 @@ def test_error_statuses_on_device_calls(pkg, cuda):
     assert pkg.device_status()[0] == pkg.OK
 
 
+WAIT_IDS = "100+s producer waits for a free stage, 200+ sub-tile producer, 300+acc MMA waits for a drained accumulator, " \
+           "400+/500+ MMA waits for data, 600+acc epilogue waits for a finished tile, 700/701 cluster reduce"
+
+
 def test_bounded_wait_reports_instead_of_hanging(pkg, cuda, oracle):
-    """Failure detection without a GPU fault: with a wait budget of about a nanosecond some wait
-    inside the kernel runs out; the kernel must return, record DEVICE_TIMEOUT, and leave the
-    context usable for the next (normal) launch."""
-    A, Bt, _ = inputs(pkg, pkg.F16, 512, 512, 2048, 90)
-    dA, dB = to_device(cuda, A, pkg.F16), to_device(cuda, Bt, pkg.F16)
-    D = cuda.empty((512, 512), dtype=cuda.float32, device="cuda")
-    p = pkg.default_params(512, 512, 2048, pkg.F16, num_stages=2)
+    """Failure detection without a GPU fault: with a wait budget of about a nanosecond and a K long
+    enough that the epilogue waits hundreds of microseconds for its first tile, a wait inside the
+    kernel MUST run out: the kernel returns, the record holds {DEVICE_TIMEOUT, block, barrier id,
+    phase}, and the context stays usable for the next (normal) launch."""
+    m, n, k = 512, 512, 131072
+    A = cuda.empty((m, k), dtype=cuda.float16, device="cuda"); Bt = cuda.empty((n, k), dtype=cuda.float16, device="cuda")
+    pkg.fill_device(A, 90, 1); pkg.fill_device(Bt, 90, 2)
+    D = cuda.empty((m, n), dtype=cuda.float32, device="cuda")
+    p = pkg.default_params(m, n, k, pkg.F16, tile_m=128, tile_n=128, num_stages=2)
+    seen = []
     pkg.set_wait_budget_ns(1)
     try:
-        pkg.gemm(dA, dB, None, D, 1.0, 0.0, p)
+        for _ in range(3):
+            pkg.gemm(A, Bt, None, D, 1.0, 0.0, p)
+            st, info = pkg.device_status()
+            seen.append((st, info))
+            assert pkg.device_status()[0] == pkg.OK                 # reading the record cleared it
+    finally:
+        pkg.set_wait_budget_ns(2_000_000_000)
+    assert all(st == pkg.DEVICE_TIMEOUT for st, _ in seen), seen    # every launch had a wait that ran out
+    for st, (code, block, bar, phase) in seen:
+        assert code == pkg.DEVICE_TIMEOUT
+        assert 0 <= block < pkg.num_sms()
+        assert 100 <= bar < 700, (bar, WAIT_IDS)                    # a barrier id of one of the roles
+        assert phase in (0, 1)
+    pkg.gemm(A, Bt, None, D, 1.0, 0.0, p)                           # the context is still usable
+    assert pkg.device_status()[0] == pkg.OK
+    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D, rows=8, elements=256)
+
+
+def test_push_reduce_times_out_on_a_flag_nobody_writes(pkg, cuda):
+    """Owner side of the fused split-K exchange on one GPU: the flags of an epoch no source ever
+    announces make the bounded wait of b200_push_reduce run out (record: barrier id 700 + source
+    rank, phase = the epoch); once the flags are there, the next call sums the slots."""
+    torch = cuda
+    world, rows, n = 2, 128, 256
+    slots = torch.arange(world * rows * n, dtype=torch.float32, device="cuda").reshape(world, rows, n) / 1024.0
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    gD = Guarded(torch, (rows, n), torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    pkg.set_wait_budget_ns(1000)
+    try:
+        st = pkg.lib().b200_push_reduce(slots.data_ptr(), flags.data_ptr(), world, 5, None, gD.t.data_ptr(), 1.0, 0.0, rows, n, stream)
+        assert st == pkg.OK                                          # the call enqueues; the wait runs on the device
         st, info = pkg.device_status()
     finally:
         pkg.set_wait_budget_ns(2_000_000_000)
-    assert st in (pkg.OK, pkg.DEVICE_TIMEOUT)
-    if st == pkg.DEVICE_TIMEOUT:
-        assert info[0] == pkg.DEVICE_TIMEOUT and info[2] >= 100     # a barrier id of one of the roles
-    assert pkg.device_status()[0] == pkg.OK                         # the record was cleared
-    pkg.gemm(dA, dB, None, D, 1.0, 0.0, p)
-    assert pkg.device_status()[0] == pkg.OK
-    ok, msg = tolerance_ok(D.cpu().numpy(), oracle.gemm(A, Bt), 2048)
+    assert st == pkg.DEVICE_TIMEOUT and info[0] == pkg.DEVICE_TIMEOUT and info[2] == 700 and info[3] == 5, (st, info)
+    assert bool(torch.isnan(gD.t).all()), "a timed-out reduce must not write D"
+    flags[:world] = torch.tensor([5, 6], dtype=torch.int32)          # source 1 is already one step ahead: still "arrived"
+    st = pkg.lib().b200_push_reduce(slots.data_ptr(), flags.data_ptr(), world, 5, None, gD.t.data_ptr(), 2.0, 0.0, rows, n, stream)
+    assert st == pkg.OK and pkg.device_status()[0] == pkg.OK
+    assert torch.equal(gD.t, 2.0 * (slots[0] + slots[1]))
+    gD.check("D of b200_push_reduce")
+
+
+def test_cluster_reduce_waits_time_out_when_arrivals_are_withheld(pkg, cuda, oracle):
+    """The two waits between the CTAs of a cluster-reduce launch (701: every K slice of the tile is staged;
+    700: every peer has read this CTA's slice) are bounded too: with the arrivals withheld (diagnostic
+    bits 2 / 3: a flag that nothing sets) and a 50 us budget each launch ends by itself with a
+    DEVICE_TIMEOUT record naming that barrier, and the next normal launch is correct."""
+    m, n, k = 16, 1024, 4096
+    A, Bt, _ = inputs(pkg, pkg.BF16, m, n, k, 91)
+    dA, dB = to_device(cuda, A, pkg.BF16), to_device(cuda, Bt, pkg.BF16)
+    D = cuda.empty((m, n), dtype=cuda.float32, device="cuda")
+    base = dict(swap_ab=1, tile_m=16, tile_n=128, split_k=4, cluster_reduce=1, num_sms=8)    # 8 tiles on 2 clusters of 4
+    for bit, want_bar in ((4, 701), (8, 700)):
+        p = pkg.default_params(m, n, k, pkg.BF16, diagnostic=bit, **base)
+        assert pkg.validate(m, n, k, pkg.BF16, p) == pkg.OK
+        pkg.set_wait_budget_ns(50_000)
+        try:
+            pkg.gemm(dA, dB, None, D, 1.0, 0.0, p)
+            st, info = pkg.device_status()
+        finally:
+            pkg.set_wait_budget_ns(2_000_000_000)
+        assert st == pkg.DEVICE_TIMEOUT and info[2] == want_bar, (bit, st, info, WAIT_IDS)
+        assert pkg.device_status()[0] == pkg.OK
+    got = run_gemm(pkg, cuda, pkg.BF16, A, Bt, None, 1.0, 0.0, **base)
+    ok, msg = tolerance_ok(got, oracle.gemm(A, Bt, None, 1.0, 0.0, oracle.BF16), k)
     assert ok, msg
 
 
@@ -470,20 +542,33 @@ def test_device_generator_equals_host_generator(pkg, cuda):
     assert np.array_equal(f.cpu().numpy(), pkg.fill_f32_host((50001,), 12, 3, 1, 0.5))
 
 
-def _sample_check(pkg, torch, oracle, dtype, A_t, B_t, D_t, alpha=1.0, rows=32, scale=1.0):
-    """Full-size check without a full CPU product: whole rows recomputed by the oracle plus
-    scattered elements in fp32 and fp64."""
+def _sample_check(pkg, torch, oracle, dtype, A_t, B_t, D_t, alpha=1.0, rows=64, elements=4096, scale=1.0):
+    """Full-size check without a full CPU product: `rows` whole rows of D recomputed by the oracle in the
+    reference's fp32 order, plus `elements` scattered elements recomputed in fp32 and in fp64. The fp64
+    values bound the kernel's error against the exact product with the same tolerance, and the oracle's own
+    fp32-vs-fp64 deviation is returned so the reference's rounding is not charged to the kernel."""
     m, k = A_t.shape
     n = B_t.shape[0]
+    A = A_t.view(torch.int16).cpu().numpy().view(np.uint16)
     Bt = B_t.view(torch.int16).cpu().numpy().view(np.uint16)
     rng = np.random.default_rng(7)
     ridx = np.sort(rng.choice(m, size=min(rows, m), replace=False))
-    A_rows = A_t[torch.from_numpy(ridx).cuda()].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    want = oracle.gemm(A_rows, Bt, None, alpha, 0.0, dtype)
+    want = oracle.gemm(np.ascontiguousarray(A[ridx]), Bt, None, alpha, 0.0, dtype)
     got = D_t[torch.from_numpy(ridx).cuda()].cpu().numpy()
     ok, msg = tolerance_ok(got, want, k, scale)
     assert ok, msg
-    return got, want
+    eidx = np.sort(rng.choice(m * n, size=min(elements, m * n), replace=False)).astype(np.int64)
+    w32, w64 = oracle.gemm_elements(A, Bt, None, alpha, 0.0, eidx, dtype)
+    g = D_t.reshape(-1)[torch.from_numpy(eidx).cuda()].cpu().numpy().astype(np.float64)
+    bound = 2.0 ** -10 * np.sqrt(k) * scale
+    err32 = float(np.abs(g - w32.astype(np.float64)).max())
+    err64 = float(np.abs(g - w64).max())
+    oracle_dev = float(np.abs(w32.astype(np.float64) - w64).max())
+    assert err32 <= bound and err64 <= bound, (err32, err64, bound)
+    rel64 = float(np.linalg.norm(g - w64) / max(np.linalg.norm(w64), 1e-30))
+    assert rel64 <= 1e-3, rel64
+    return {"rows": int(ridx.size), "elements": int(eidx.size), "max_err_vs_fp32": err32, "max_err_vs_fp64": err64,
+            "oracle_fp32_vs_fp64": oracle_dev, "bound": bound}
 
 
 def test_config2_4096_cubed_tile_and_stage_sweep(pkg, cuda, oracle):
@@ -508,10 +593,13 @@ def test_config2_4096_cubed_tile_and_stage_sweep(pkg, cuda, oracle):
                 pkg.gemm(A, Bt, None, D, 1.0, 0.0, p)
                 assert pkg.device_status()[0] == pkg.OK
                 if first is None:
-                    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D, rows=16)
+                    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D, rows=64)
                     first = D.clone()
                 else:
-                    # every configuration sums K in the same 16-wide steps: differences, if any, are rounding only
+                    # Only the first configuration meets the oracle directly; the others are compared with its
+                    # full 4096 x 4096 result, which is the stronger check (every element, not a sample) and is
+                    # transitively a check against the oracle. Every configuration sums K in the same 16-wide
+                    # steps: differences, if any, are rounding only.
                     assert float((D - first).abs().max()) <= 2.0 ** -10 * 64.0 / 64.0, ov
 
 
@@ -524,7 +612,7 @@ def test_config3_8192_cubed_fp16_and_bf16(pkg, cuda, oracle):
         pkg.fill_device(A, 2, 1); pkg.fill_device(Bt, 2, 2)
         D = pkg.gemm(A, Bt)
         assert pkg.device_status()[0] == pkg.OK
-        _sample_check(pkg, cuda, oracle, code, A, Bt, D, rows=16)
+        _sample_check(pkg, cuda, oracle, code, A, Bt, D, rows=64)
         D2 = pkg.gemm(A, Bt, alpha=2.0, params=pkg.default_params(n, n, n, code, tile_m=128, tile_n=256, cta_group=1, num_stages=4))
         assert float((D2 - 2.0 * D).norm() / D.norm()) < 1e-6    # linear in alpha; another tiling agrees
         del A, Bt, D, D2
@@ -560,10 +648,10 @@ def test_config5_tall_k_split(pkg, cuda, oracle):
     pkg.fill_device(A, 4, 1); pkg.fill_device(Bt, 4, 2)
     D1 = pkg.gemm(A, Bt, params=pkg.default_params(m, n, k, pkg.F16, split_k=1))
     assert pkg.device_status()[0] == pkg.OK
-    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D1, rows=8)
+    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D1, rows=64)
     D8 = pkg.gemm(A, Bt, params=pkg.default_params(m, n, k, pkg.F16, split_k=8))
     assert pkg.device_status()[0] == pkg.OK
-    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D8, rows=8)
+    _sample_check(pkg, cuda, oracle, oracle.FP16, A, Bt, D8, rows=64)
     rel = float((D8 - D1).norm() / D1.norm())
     assert rel < 1e-3, rel                                      # only the fp32 summation order differs
 

@@ -3,6 +3,7 @@ fused into the GEMM epilogue (peer stores over NVLink), against the CPU oracle. 
 GPU. Skipped on a single-GPU machine (tests/test_sharding.py covers the split logic on CPU)."""
 import os
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -20,7 +21,7 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
     import oracle
     from __graft_entry__ import load_package
-    from helpers import to_device, tolerance_ok
+    from helpers import Guarded, to_device, tolerance_ok
     pkg = load_package()
     shard = importlib.import_module("cuda_kernel_opt_b200.shard")
     torch.cuda.set_device(rank)
@@ -41,13 +42,34 @@ def _worker(rank, world, port, q):
         results["nccl"] = shard.reduce_scatter_rows(part).cpu().numpy()
         # (2) exchange fused into the epilogue, three steps in a row (alternating slot areas)
         ex = shard.PushExchange(pkg, m, n)
-        out = torch.empty((m // world, n), dtype=torch.float32, device="cuda")
+        gout = Guarded(torch, (m // world, n), torch.float32)
+        out = gout.t
         for tile in (dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=128, tile_n=128), dict(tile_m=256, tile_n=128, cta_group=2),
                      dict(tile_m=256, tile_n=256, cta_group=2, split_k=4), dict(tile_m=128, tile_n=256, split_k=3)):
             out.fill_(float("nan"))
             ex.gemm_reduce_scatter(dA, dB, out, pkg.default_params(m, n, ks.size, pkg.F16, **tile))
             torch.cuda.synchronize()
+            gout.check("rows of D, fused exchange " + str(tile))
             results["fused " + str(tile)] = out.cpu().numpy().copy()
+        # (2b) one rank's host stalls between its push and its reduce while the others run on: they finish that
+        # step and push the next one, so the late rank finds their flags one epoch ahead. Its reduce must take
+        # that as "arrived" (the step's slots sit in the other area, untouched), not wait for an exact match.
+        p_pair = pkg.default_params(m, n, ks.size, pkg.F16, tile_m=256, tile_n=256, cta_group=2)
+        late = []
+        for step in range(2):
+            gout = Guarded(torch, (m // world, n), torch.float32)
+            if rank == 0 and step == 0:
+                ex.push(dA, dB, p_pair)
+                torch.cuda.synchronize()
+                time.sleep(0.6)
+                ex.reduce(gout.t)
+            else:
+                ex.gemm_reduce_scatter(dA, dB, gout.t, p_pair)
+            late.append(gout)
+        torch.cuda.synchronize()
+        for step, gout in enumerate(late):
+            gout.check(f"rows of D, late-rank step {step}")
+            results[f"fused, rank 0 late, step {step}"] = gout.t.cpu().numpy().copy()
         # (3) the shards that need no exchange, with default tunables: rows of B^T (columns of D) of a decode
         # shape per rank (swapped roles, K over a cluster), rows of A of a square per rank
         m2, n2, k2 = 16, 1024 * world, 4096

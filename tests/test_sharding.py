@@ -80,3 +80,74 @@ def test_split_k_reduce_scatter_gloo_world2():
         assert shape == (32, 96)
         assert err_k < 2.0 ** -10 * np.sqrt(512), (rank, err_k)   # split-K changes the summation order only
         assert exact, "M-/N-shards must reproduce the unsharded product bit for bit"
+
+
+def _leaver(rank, world, port, q):
+    """Rank 1 goes away between steps: once with a leave note, once silently. Rank 0 must learn of it on the
+    host before its next launch (note), or have its next collective end with an error (short timeout)."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    sh = shard_mod()
+    store = dist.distributed_c10d._get_default_store()
+    out = {}
+    try:
+        mem = sh.Membership(store, rank, world, stale_after=1.0)
+        x = torch.ones(4)
+        dist.all_reduce(x)                                   # step 1: everybody is there
+        out["step1"] = float(x[0])
+        mem.beat(1)
+        if rank == 1:
+            mem.leave("planned exit after step 1")          # between steps, nothing in flight
+            q.put((rank, out))
+            return
+        # rank 0: wait for the note (bounded), then check before "launching" step 2
+        import time
+        t0 = time.time()
+        while time.time() - t0 < 20:
+            try:
+                mem.check()
+            except sh.PeerLeft as e:
+                out["left"] = (e.rank, e.reason)
+                break
+            time.sleep(0.05)
+        # a heartbeat that stops: the same check with a clock that has moved on
+        mem2 = sh.Membership(store, rank, world, prefix="b200/members2", stale_after=1.0)
+        store.set("b200/members2/beat/1", f"1:{time.time() - 5.0:.3f}")
+        try:
+            mem2.check()
+            out["stale"] = None
+        except sh.PeerLeft as e:
+            out["stale"] = (e.rank, "no heartbeat" in e.reason)
+        # a peer gone without a note: the next collective ends with an error after the group's short timeout
+        t0 = time.time()
+        try:
+            dist.all_reduce(x)
+            out["collective"] = "returned"
+        except Exception as e:       # gloo raises RuntimeError (timeout / connection closed by peer)
+            out["collective"] = "error"
+        out["collective_s"] = time.time() - t0
+        q.put((rank, out))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_leaving_between_steps_is_seen_on_the_host_gloo_world2():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_leaver, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    assert results[1]["step1"] == 2.0 and results[0]["step1"] == 2.0
+    assert results[0]["left"] == (1, "planned exit after step 1")
+    assert results[0]["stale"] == (1, True)
+    assert results[0]["collective"] == "error" and results[0]["collective_s"] < 30

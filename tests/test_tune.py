@@ -1,4 +1,5 @@
-"""CPU: the sweep harness's candidate generation, JSONL record and resume logic (no timing here)."""
+"""CPU: the sweep harness's candidate generation, JSONL record and resume logic (no timing here), and the
+stamp arithmetic of the launch-timeline tool."""
 import importlib
 import json
 import os
@@ -43,3 +44,28 @@ def test_record_resume_and_best(tmp_path):
     assert t.best(path, 64, 64, 64) == {"tile_n": 16}            # fastest with a clean device status
     assert t.best(path, 64, 64, 64, "bf16") is None
     assert t.best(str(tmp_path / "missing.jsonl"), 64, 64, 64) is None
+
+
+def test_timeline_summary_of_stamps():
+    """cuda-kernel-opt_b200/timeline.py: per-milestone mean / min / max over the CTAs that had work, measured
+    from the first CTA's entry; CTAs that never entered or never saw an accumulator are left out, and so are
+    milestones nobody stamped."""
+    import numpy as np
+    from __graft_entry__ import load_package
+    load_package()
+    tl = importlib.import_module("cuda_kernel_opt_b200.timeline")
+    stamps = np.zeros((4, 32), np.int64)
+    base = 1_000_000
+    stamps[0, 13], stamps[0, 14], stamps[0, 22], stamps[0, 15] = base, base + 500, base + 4000, base + 9000
+    stamps[1, 13], stamps[1, 14], stamps[1, 22], stamps[1, 15] = base + 100, base + 700, base + 5000, base + 9500
+    stamps[2, 13], stamps[2, 14], stamps[2, 15] = base + 50, base + 600, base + 800          # entered, no work
+    entered, working, rows = tl.summarise(stamps)                                               # CTA 3 never entered
+    assert (entered, working) == (3, 2)
+    got = {name: (mean, lo, hi) for name, mean, lo, hi in rows}
+    assert got["kernel entry"] == (50.0, 0, 100)
+    assert got["set-up barrier passed"] == (600.0, 500, 700)
+    assert got["epilogue: first accumulator ready"] == (4500.0, 4000, 5000)
+    assert got["exit"] == (9250.0, 9000, 9500)
+    assert "mma: first stage full" not in got
+    assert [name for name, *_ in rows] == [n for _, n in tl.MILESTONES if n in got]             # milestone order kept
+    assert tl.summarise(np.zeros((2, 32), np.int64)) == (0, 0, [])
