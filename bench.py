@@ -263,7 +263,8 @@ def run_ours(args):
     nshard = args.workload.startswith("c4")
 
     # --shard-of G on one GPU: time rank 0's shard of a G-GPU run of an N-sharded workload alone
-    shard_world = args.shard_of if (args.shard_of > 1 and world == 1 and nshard) else world
+    mshard_alone = args.shard_of > 1 and world == 1 and not nshard and not args.workload.startswith("c5")
+    shard_world = args.shard_of if (args.shard_of > 1 and world == 1 and (nshard or mshard_alone)) else world
     library = args.impl == "library"       # torch.matmul (cuBLAS) in the same harness, for scale only
 
     # ---- placement (see cuda-kernel-opt_b200/shard.py)
@@ -277,9 +278,9 @@ def run_ours(args):
         m_loc, n_loc, k_loc = M, ns.size, K
         scaling, parallelism = "strong", f"N-shard x{shard_world}, no collective" + (" (rank 0's shard alone on one GPU)" if shard_world != world else "")
     elif args.scaling == "strong":           # rows of A split over ranks, B^T replicated
-        ms = shard.m_shard(M, world, rank, 256)
+        ms = shard.m_shard(M, shard_world, rank, 256)
         m_loc, n_loc, k_loc = ms.size, N, K
-        scaling, parallelism = "strong", f"M-shard x{world}, no collective"
+        scaling, parallelism = "strong", f"M-shard x{shard_world}, no collective" + (" (rank 0's shard alone on one GPU)" if shard_world != world else "")
     else:                                    # every rank owns a full M-row block of a (M*world)-row A
         m_loc, n_loc, k_loc = M, N, K
         scaling, parallelism = "weak", f"M-shard x{world} ({M} rows per GPU), no collective"
@@ -298,7 +299,7 @@ def run_ours(args):
             Bt[r0:r0 + rows].copy_(tmp[:, ks.begin:ks.end])
         del tmp
     else:
-        a_row0 = (rank * M if (scaling == "weak") else (shard.m_shard(M, world, rank, 256).begin if not nshard else 0))
+        a_row0 = (rank * M if (scaling == "weak") else (shard.m_shard(M, shard_world, rank, 256).begin if not nshard else 0))
         b_row0 = shard.n_shard(N, shard_world, rank, 256).begin if nshard else 0
         pkg.fill_device(A, seed, 1, int(da[0]), float(da[1]), begin=a_row0 * K)
         pkg.fill_device(Bt, seed, 2, int(db[0]), float(db[1]), begin=b_row0 * K)
@@ -320,7 +321,8 @@ def run_ours(args):
     assert st == pkg.OK, f"invalid configuration {p.as_dict()}: {pkg.status_string(st)}"
     ws_bytes = pkg.workspace_bytes(m_loc, n_loc, k_loc, p)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-    launches_per_step = 1 + (1 if (p.split_k > 1 or ws_bytes > 0) else 0) + (1 if fused else 0)
+    # the split-K reduce is a second kernel (not with the cluster reduce; the stream-K schedule finishes inside the GEMM)
+    launches_per_step = 1 + (1 if (p.split_k > 1 and not p.cluster_reduce) else 0) + (1 if fused else 0)
     push = shard.PushExchange(pkg, M, N) if fused else None
     D_rows = torch.empty((M // world, N), dtype=torch.float32, device=dev) if fused else None
     if fused:
@@ -639,7 +641,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference", "library"], default="ours",
                     help="library: torch.matmul in this harness, a number for scale (single-process workloads only)")
-    ap.add_argument("--shard-of", type=int, default=0, help="one GPU: time rank 0's shard of a G-GPU run of an N-sharded workload")
+    ap.add_argument("--shard-of", type=int, default=0, help="one GPU: time rank 0's shard of a G-GPU run (N-shard of the decode workloads, M-shard of the squares)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c3_8192_f16")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
                     help="N > 1, square workloads: strong = the workload's M rows split over the GPUs (the baseline's "

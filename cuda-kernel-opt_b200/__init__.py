@@ -24,7 +24,7 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 
 # every symbol include/b200_gemm.h declares
 EXPORTS = [
-    "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes",
+    "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes", "b200_gemm_schedule",
     "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_f16_out_f16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
     "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_profile_slots", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
@@ -68,6 +68,8 @@ def lib():
         L.b200_gemm_smem_bytes.restype = i64
         L.b200_gemm_workspace_bytes.argtypes = [i64, i64, i64, PP]
         L.b200_gemm_workspace_bytes.restype = i64
+        L.b200_gemm_schedule.argtypes = [i64, i64, i64, PP, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int)]
+        L.b200_gemm_schedule.restype = C.c_int
         for fn in (L.b200_gemm_f16, L.b200_gemm_bf16):
             fn.argtypes = [vp, vp, vp, vp, f32, f32, i64, i64, i64, PP, vp, sz, vp]
             fn.restype = C.c_int
@@ -165,6 +167,18 @@ def smem_bytes(dtype, p: Params) -> int:
 
 def workspace_bytes(M, N, K, p: Params) -> int:
     return lib().b200_gemm_workspace_bytes(M, N, K, C.byref(p))
+
+
+def schedule(M, N, K, p: Params, num_sms: int = 148, group: int = 0):
+    """b200_gemm_schedule: (number of CTA groups, [(m0, n0, seg_begin, seg_end, kind, slice), ...]) for one group.
+    Host arithmetic only. Raises ValueError for an invalid configuration or group."""
+    groups = C.c_int(0)
+    n = lib().b200_gemm_schedule(M, N, K, C.byref(p), num_sms, group, None, 0, C.byref(groups))
+    if n < 0:
+        raise ValueError("invalid configuration or group")
+    buf = (C.c_int * (6 * max(n, 1)))()
+    lib().b200_gemm_schedule(M, N, K, C.byref(p), num_sms, group, buf, n, None)
+    return groups.value, [tuple(buf[6 * i:6 * i + 6]) for i in range(n)]
 
 
 def gemm_raw(dtype, A_ptr, Bt_ptr, C_ptr, D_ptr, alpha, beta, M, N, K, p, ws_ptr=None, ws_bytes=0, stream=None) -> int:

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200gemm.so")
 SOURCES = ["gemm_sm100.cu", "api.cu", "gemm_noalloc.cu"]
-HEADERS = ["gemm_sm100.cuh", "ptx_sm100.cuh", "plan.h", "synth.h", os.path.join("..", "..", "include", "b200_gemm.h")]
+HEADERS = ["gemm_sm100.cuh", "ptx_sm100.cuh", "plan.h", "schedule.h", "synth.h", os.path.join("..", "..", "include", "b200_gemm.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -13,6 +13,7 @@
 #include "../../include/b200_gemm.h"
 #include "gemm_sm100.cuh"
 #include "ptx_sm100.cuh"
+#include "schedule.h"
 #include "synth.h"
 
 namespace b200 {
@@ -20,6 +21,7 @@ namespace {
 
 thread_local int t_last_cuda_error = 0;
 std::atomic<uint64_t> g_wait_budget_ns{2000000000ull};
+std::atomic<unsigned int> g_sk_epoch{0u};
 std::atomic<long long *> g_prof_ptr{nullptr};
 std::atomic<int> g_prof_blocks{0};
 
@@ -227,6 +229,8 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
     // drain through swizzled shared memory and TMA stores: 3x shorter per tile than scattered 128-bit
     // stores (6.2 k vs 19 k cycles for 128 x 256 fp32), +2 % on 8192^3
     p->epilogue = 1;
+    // tiles that do not fill a wave are scheduled by K iterations (takes effect when the call gets a workspace)
+    p->tail_split = 1;
     // a grid that leaves SMs idle is a short kernel: overlap its set-up with the previous kernel's tail
     const int64_t ctas = ((M + p->tile_m - 1) / p->tile_m) * ((N + p->tile_n - 1) / p->tile_n) * p->cta_group;
     p->overlap_launch = ctas < 148 ? 1 : 0;
@@ -277,18 +281,20 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
          reinterpret_cast<uintptr_t>(C)) & 15u)
         return B200_INVALID_POINTER;
     const int64_t n_tiles = ((kM + p.tile_m - 1) / p.tile_m) * ((kN + p.tile_n - 1) / p.tile_n);
-    const TailSplit tail = make_tail_split(user->tail_split && !(push && push->world > 0), n_tiles, p.grid / p.cta_group,
-                                           (K + p.seg_k - 1) / p.seg_k, p.split_k);
-    if (tail.s > 1) {
-        const size_t need = static_cast<size_t>(tail.s) * tail.r * p.tile_m * p.tile_n * sizeof(float);
-        if (!workspace || workspace_bytes < need) return B200_WORKSPACE_TOO_SMALL;
-        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return B200_INVALID_POINTER;
-    }
+    // Stream-K (tail_split) is an optimisation of the schedule, taken when the caller's workspace can hold
+    // one partial tile per CTA; without it the plain schedule runs and the result is the same to rounding.
+    // (its CTAs wait for one another, so all of them must be resident at once: one per SM)
+    StreamK sk = make_stream_k(user->tail_split && !p.swap && p.grid <= stream_k_max_ctas() && p.grid <= dev->num_sms, n_tiles,
+                               p.grid / p.cta_group,
+                               (K + p.seg_k - 1) / p.seg_k, p.split_k, p.tile_n);
+    if (sk.sk_tiles > 0 && (!workspace || workspace_bytes < static_cast<size_t>(sk.slot_bytes) * p.grid ||
+                            (reinterpret_cast<uintptr_t>(workspace) & 15u)))
+        sk = StreamK();
     const int ws_split = p.cluster_reduce ? 1 : p.split_k;  // K slices that meet in the workspace
-    // fp16 output leaves through the plain, transposed and cluster drains only: the workspace forms
-    // (split-K, tail split, push) keep fp32 partials and their second kernels write fp32
-    if (out_half && (ws_split > 1 || tail.s > 1 || pushing)) return B200_INVALID_CONFIG;
-    if (ld_cd && ld_cd != N && (ws_split > 1 || tail.s > 1 || (push && push->world > 0) || ld_cd < N || ld_cd % 4))
+    // fp16 output leaves through the plain, transposed and cluster drains only: the split-K workspace and
+    // push forms keep fp32 partials and their second kernels write fp32
+    if (out_half && (ws_split > 1 || pushing)) return B200_INVALID_CONFIG;
+    if (ld_cd && ld_cd != N && (ws_split > 1 || (push && push->world > 0) || ld_cd < N || ld_cd % 4))
         return B200_INVALID_CONFIG;  // the second-step kernels assume a dense D
     if (ws_split > 1) {
         const size_t need = static_cast<size_t>(p.split_k) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
@@ -329,10 +335,14 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.split_k = ws_split;
     a.cl_split = p.cluster_reduce ? p.split_k : 0;
     a.num_units = a.num_tiles * ws_split;
-    a.tail_full = tail.full;
-    a.tail_r = tail.r;
-    a.tail_s = tail.s;
-    if (tail.s > 1) a.num_units = tail.full + tail.r * tail.s;
+    a.sk_tiles = sk.sk_tiles;
+    if (sk.sk_tiles > 0) {
+        // every launch that uses the fix-up flags gets its own epoch (never 0) and the next flag set in turn
+        unsigned int epoch = g_sk_epoch.fetch_add(1u) + 1u;
+        if (epoch == 0u) epoch = g_sk_epoch.fetch_add(1u) + 1u;
+        a.sk_epoch = epoch;
+        a.sk_set = static_cast<int>(epoch & 0x7fffffffu);
+    }
     a.num_segs = static_cast<int>((K + p.seg_k - 1) / p.seg_k);
     a.tile_m = p.tile_m;
     a.tile_n = p.tile_n;
@@ -396,9 +406,6 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     } else if (ws_split > 1) {
         const int re = launch_splitk_reduce(a.partial, C, D, alpha, beta, M * N, p.split_k, stream);
         if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
-    } else if (tail.s > 1) {
-        const int re = launch_tail_reduce(a, stream);
-        if (re != 0) return fail_cuda(static_cast<cudaError_t>(re));
     }
     return B200_OK;
 }
@@ -429,6 +436,8 @@ struct b200_session {
     cudaStream_t compute;     // launches
     cudaStream_t download;    // results
     cudaEvent_t up[16], done[16], b_ready;
+    void *dW;                 // workspace for the stream-K schedule of the block products
+    size_t w_bytes;
 };
 
 extern "C" {
@@ -462,15 +471,74 @@ int64_t b200_gemm_smem_bytes(int dtype, const b200_gemm_params *p) {
     return plan.status == B200_OK ? plan.smem_bytes : -1;
 }
 
+int b200_gemm_schedule(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p, int num_sms, int group, int *units,
+                       int max_units, int *num_groups_out) {
+    if (!p || num_sms <= 0) return -1;
+    b200_gemm_params q = *p;
+    q.num_sms = num_sms;
+    const Plan plan = make_plan(q, num_sms);
+    if (plan.status != B200_OK || check_shape(plan, M, N, K) != B200_OK) return -1;
+    const int64_t kM = plan.swap ? N : M, kN = plan.swap ? M : N;
+    Cfg c;
+    std::memset(&c, 0, sizeof(c));
+    c.tile_m = plan.tile_m;
+    c.tile_n = plan.tile_n;
+    c.tiles_m = static_cast<int>((kM + plan.tile_m - 1) / plan.tile_m);
+    c.tiles_n = static_cast<int>((kN + plan.tile_n - 1) / plan.tile_n);
+    c.num_tiles = c.tiles_m * c.tiles_n;
+    c.tile_group_m = plan.tile_group_m;
+    c.num_segs = static_cast<int>((K + plan.seg_k - 1) / plan.seg_k);
+    c.split_k = plan.cluster_reduce ? 1 : plan.split_k;
+    c.cl_split = plan.cluster_reduce ? plan.split_k : 1;
+    c.num_units = c.num_tiles * c.split_k;
+    int grid = plan.grid;
+    if (plan.cluster_reduce) {                      // as launch_gemm: whole clusters, no more than there are tiles
+        const int per_tile = plan.split_k * plan.cta_group;
+        grid -= grid % per_tile;
+        if (grid > c.num_tiles * per_tile) grid = c.num_tiles * per_tile;
+        if (grid < per_tile) grid = per_tile;
+    }
+    const int num_groups = grid / (plan.cta_group * c.cl_split);
+    if (num_groups_out) *num_groups_out = num_groups;
+    if (group < 0 || group >= num_groups) return -1;
+    const StreamK sk = make_stream_k(q.tail_split && !plan.swap && grid <= stream_k_max_ctas(), c.num_tiles, num_groups, c.num_segs,
+                                     plan.split_k, plan.tile_n);
+    c.sk_tiles = sk.sk_tiles;
+    if (c.sk_tiles > 0) {
+        c.sk_lo = sk_range_begin(group, c.sk_tiles, c.num_segs, num_groups);
+        c.sk_hi = sk_range_begin(group + 1, c.sk_tiles, c.num_segs, num_groups);
+    }
+    c.cl_seg_end = c.num_segs;   // a cluster's slices: listed for slice 0 .. as the whole K range of the tile
+    Walk walk;
+    walk_init(c, walk, group);
+    Unit w;
+    int n = 0;
+    while (walk_next(c, walk, num_groups, w)) {
+        if (units && n < max_units) {
+            int *u = units + 6 * n;
+            u[0] = w.m0; u[1] = w.n0; u[2] = w.seg_begin; u[3] = w.seg_end; u[4] = w.kind; u[5] = w.slice;
+        }
+        ++n;
+    }
+    return n;
+}
+
 int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p) {
     if (!p) return 0;
     if (p->split_k > 1 && !p->cluster_reduce) return static_cast<int64_t>(p->split_k) * M * N * static_cast<int64_t>(sizeof(float));
     if (p->tail_split) {
-        const Plan plan = make_plan(*p, p->num_sms > 0 ? p->num_sms : 148);
-        if (plan.status != B200_OK) return 0;
+        int sms = p->num_sms;
+        if (sms <= 0) {                        // the grid follows the device: ask it; 148 (a B200) without one
+            int dev = 0, n = 0;
+            sms = (cudaGetDevice(&dev) == cudaSuccess &&
+                   cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+            cudaGetLastError();
+        }
+        const Plan plan = make_plan(*p, sms);
+        if (plan.status != B200_OK || plan.swap || plan.grid > stream_k_max_ctas()) return 0;
         const int64_t n_tiles = ((M + plan.tile_m - 1) / plan.tile_m) * ((N + plan.tile_n - 1) / plan.tile_n);
-        const TailSplit t = make_tail_split(1, n_tiles, plan.grid / plan.cta_group, (K + plan.seg_k - 1) / plan.seg_k, plan.split_k);
-        if (t.s > 1) return static_cast<int64_t>(t.s) * t.r * plan.tile_m * plan.tile_n * static_cast<int64_t>(sizeof(float));
+        const StreamK k = make_stream_k(1, n_tiles, plan.grid / plan.cta_group, (K + plan.seg_k - 1) / plan.seg_k, plan.split_k, plan.tile_n);
+        if (k.sk_tiles > 0) return k.slot_bytes * plan.grid;
     }
     return 0;
 }
@@ -573,6 +641,8 @@ int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_sessio
     if (e == cudaSuccess) e = cudaMalloc(&s->dB, static_cast<size_t>(max_n) * max_k * 2);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dC), static_cast<size_t>(max_m) * max_n * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dD), static_cast<size_t>(max_m) * max_n * 4);
+    s->w_bytes = static_cast<size_t>(stream_k_max_ctas()) * 128 * 256 * sizeof(float);   // one 128 x 256 fp32 partial per CTA
+    if (e == cudaSuccess) e = cudaMalloc(&s->dW, s->w_bytes);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->compute, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->download, cudaStreamNonBlocking);
@@ -603,6 +673,7 @@ void b200_session_destroy(b200_session *s) {
     cudaFree(s->dB);
     cudaFree(s->dC);
     cudaFree(s->dD);
+    cudaFree(s->dW);
     delete s;
 }
 
@@ -670,8 +741,8 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
                 const int64_t c0 = bj * bcols, cols = (N - c0 < bcols) ? (N - c0) : bcols;
                 const size_t off = static_cast<size_t>(r0) * N + c0;
                 const int st = gemm_impl(dtype, dA8 + static_cast<size_t>(r0) * K * 2, dB8 + static_cast<size_t>(c0) * K * 2,
-                                         beta != 0.0f ? s->dC + off : nullptr, s->dD + off, alpha, beta, rows, cols, K, p, nullptr,
-                                         0, s->compute, nullptr, N);
+                                         beta != 0.0f ? s->dC + off : nullptr, s->dD + off, alpha, beta, rows, cols, K, p, s->dW,
+                                         s->w_bytes, s->compute, nullptr, N);
                 if (st != B200_OK) return drained(st);
                 e = cudaEventRecord(s->done[block_id], s->compute);
                 if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[block_id], 0);

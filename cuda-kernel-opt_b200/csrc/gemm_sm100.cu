@@ -39,6 +39,7 @@
 
 #include "gemm_sm100.cuh"
 #include "ptx_sm100.cuh"
+#include "schedule.h"
 
 namespace b200 {
 
@@ -54,78 +55,25 @@ constexpr int kProfSlots = 32;
 constexpr int kProfSlots = 16;
 #define B200_TL(slot) do { } while (0)
 #endif
-constexpr int kMaxThreads = 512;  // (7 producer + 1 MMA + 8 epilogue warps) * 32
+constexpr int kMaxThreads = 384;  // (3 producer + 1 MMA + 8 epilogue warps) * 32: up to 168 registers per thread
 
-struct Unit {
-    int m0, n0, slice, seg_begin, seg_end;
-    int tail_idx;  // >= 0: a K slice of tail tile tail_idx, written to the workspace; -1: not a tail unit
-};
+// Flags of the stream-K fix-up: [set][CTA][epilogue warp] holds the epoch of the launch whose partial
+// that warp has stored. A set belongs to one launch at a time (the host deals them out in turn); the
+// finishing warp puts the flag back to zero. Zero at load.
+constexpr int kSkSets = 32;
+constexpr int kSkMaxCtas = 192;
+__device__ unsigned int g_sk_flags[kSkSets][kSkMaxCtas][8];
 
-// Launch constants the role loops need, copied once from the kernel parameter into registers.
-// The parameter is __grid_constant__ and its address escapes (tensor maps), so reading a field
-// after an asm statement with a memory clobber is a fresh load through the parameter window;
-// those loads sat on the critical path of the single-thread producer and MMA loops.
-struct Cfg {
-    int num_units, num_tiles, tiles_m, tiles_n, tile_group_m, tile_m, tile_n, num_segs, split_k;
-    int tail_full, tail_r, tail_s;
-    int kblocks, stages, stage_bytes, a_stage_bytes, cta_rows_a;
-    int a_box_rows, a_boxes, a_priv, a_bars, chunk_n, b_priv, b_res_chunks, b_bars;
-    int acc_cols, mma_m, epi_mode, epi_warps, M, N;
-    int cl_split, cl_rank;  // cluster reduce: K slices per tile (= cluster size) and this CTA's slice
-    int cl_seg_begin, cl_seg_end;
-    uint32_t idesc_chunk, idesc_res;
-    long long budget;
-};
-
-// Work unit -> tile and K slice. Tiles follow the reference's grouped order
-// (get_tile_offset_cd, port_0.cu:201-210): tile_group_m tile rows are walked column-major inside
-// a group so concurrently running CTAs share B^T column panels in L2; the last group may be short.
-__device__ __forceinline__ Unit decode_unit(const Cfg &c, int u) {
-    // The roles that call this are single dependent instruction chains, where an integer
-    // division costs on the order of a hundred cycles: the common cases avoid them.
-    Unit w;
-    int t;
-    if (c.tail_s > 1 && u >= c.tail_full) {
-        // last wave: tail tile (u - full) mod r, K slice (u - full) / r
-        const int tl = u - c.tail_full;
-        w.tail_idx = tl % c.tail_r;
-        t = c.tail_full + w.tail_idx;
-        w.slice = tl / c.tail_r;
-        w.seg_begin = static_cast<int>(static_cast<unsigned>(w.slice) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.tail_s));
-        w.seg_end = static_cast<int>(static_cast<unsigned>(w.slice + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.tail_s));
-    } else if (c.cl_split > 1) {
-        w.tail_idx = -1;
-        t = u;
-        w.slice = c.cl_rank;
-        w.seg_begin = c.cl_seg_begin;   // the same K slice for every tile of this CTA
-        w.seg_end = c.cl_seg_end;
-    } else if (c.split_k == 1) {
-        w.tail_idx = -1;
-        t = u;
-        w.slice = 0;
-        w.seg_begin = 0;
-        w.seg_end = c.num_segs;
-    } else {
-        w.tail_idx = -1;
-        t = u % c.num_tiles;
-        w.slice = u / c.num_tiles;
-        // slice <= 64 and num_segs < 2^24: the products fit 32 bits
-        w.seg_begin = static_cast<int>(static_cast<unsigned>(w.slice) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.split_k));
-        w.seg_end = static_cast<int>(static_cast<unsigned>(w.slice + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.split_k));
+// A bounded wait ran out: raise the block-wide abort flag and leave {code, block, wait id, detail} in
+// the device status record (the first timeout of a launch wins).
+__device__ __noinline__ void record_timeout(volatile int *abort_flag, int wait_id, int detail) {
+    *abort_flag = 1;
+    if (atomicCAS(&g_device_status[0], 0, B200_DEVICE_TIMEOUT) == 0) {
+        g_device_status[1] = static_cast<int>(blockIdx.x);
+        g_device_status[2] = wait_id;
+        g_device_status[3] = detail;
     }
-    if (c.tiles_m == 1) {
-        // one row of tiles (the skinny shapes): the grouped order is the plain column order
-        w.m0 = 0;
-        w.n0 = t * c.tile_n;
-        return w;
-    }
-    const int group_tile_count = c.tile_group_m * c.tiles_n;
-    const int group_first_row = (t / group_tile_count) * c.tile_group_m;
-    const int group_rows = min(c.tiles_m - group_first_row, c.tile_group_m);
-    const int in_group = t % group_tile_count;
-    w.m0 = (group_first_row + in_group % group_rows) * c.tile_m;
-    w.n0 = (in_group / group_rows) * c.tile_n;
-    return w;
+    __threadfence();
 }
 
 // Bounded mbarrier wait. Returns false when the budget ran out here or elsewhere in the block.
@@ -142,40 +90,73 @@ __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, long long 
         if ((++spins & 31u) == 0) {
             if (*abort_flag) return false;
             if (clock64() - t0 > budget) {
-                *abort_flag = 1;
-                if (atomicCAS(&g_device_status[0], 0, B200_DEVICE_TIMEOUT) == 0) {
-                    g_device_status[1] = static_cast<int>(blockIdx.x);
-                    g_device_status[2] = bar_id;
-                    g_device_status[3] = static_cast<int>(parity);
-                }
-                __threadfence();
+                record_timeout(abort_flag, bar_id, static_cast<int>(parity));
                 return false;
             }
         }
     }
 }
 
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
+// One lane of a converged warp waits (`leader` is true in exactly one lane), the others park at the vote,
+// where the result reaches every lane: a waiting warp then costs one polling thread, not thirty-two. What the
+// leader observed (TMA bytes landed, MMAs committed, a peer's release) is ordered before what any lane does
+// after the vote; lanes that go on to read tensor memory still issue their own tcgen05 fence.
+// -DB200_WAIT_ALL_LANES restores polling by every lane (for A/B measurements of the difference).
+#ifdef B200_WAIT_ALL_LANES
+constexpr bool kAllLanesPoll = true;
+#else
+constexpr bool kAllLanesPoll = false;
+#endif
+
+template <bool CLUSTER_ACQUIRE = false>
+__device__ __forceinline__ bool wait_one(bool leader, uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
                                          int bar_id) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return wait_slow(bar, parity, budget, abort_flag, bar_id);
+    int ok = 1;
+    if (leader || kAllLanesPoll) {
+        const bool first = CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity);
+        if (!first) ok = wait_slow<CLUSTER_ACQUIRE>(bar, parity, budget, abort_flag, bar_id) ? 1 : 0;
+    }
+    return __all_sync(0xffffffffu, ok) != 0;
 }
 
-// Bounded wait whose success is an acquire at cluster scope (data written by other CTAs of the
-// cluster before their release-arrive may be read afterwards).
-__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
-                                                 int bar_id) {
-    if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
-    return wait_slow<true>(bar, parity, budget, abort_flag, bar_id);
-}
-
-// All lanes of a converged warp wait; the result is the same in every lane.
-__device__ __forceinline__ bool wait_all(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
-                                         int bar_id) {
-    bool ok = mbar_try_wait(bar, parity);
-    if (__all_sync(0xffffffffu, ok)) return true;
-    if (!ok) ok = wait_slow(bar, parity, budget, abort_flag, bar_id);
-    return __all_sync(0xffffffffu, ok);
+// Stream-K, the CTA that finishes a cut tile: how many CTA groups after this one hold later K parts of the
+// tile (those whose ranges begin before the tile ends), and a bounded wait until warp e of each of them has
+// stored its partial (flag == this launch's epoch; lane 0 polls and puts the flag back to zero). All lanes
+// call it; returns the number of peers, or -1 when the wait ran out or the block is aborting.
+__device__ __forceinline__ int sk_wait_peers(volatile unsigned int *sk_flags, unsigned int epoch, int group, int num_groups,
+                                          int sk_hi, int sk_tiles, int num_segs, int tile_end, int cg, int rank, int e,
+                                          long long budget, volatile int *abort_flag) {
+    int h = group + 1;
+    int lo = sk_hi;                                   // where group + 1 begins
+    while (h < num_groups && lo < tile_end) {
+        ++h;
+        lo = sk_range_begin(h, sk_tiles, num_segs, num_groups);
+    }
+    const int peers = h - group - 1;
+    int got = 1;
+    if (lane_id() == 0) {
+        const long long t0 = clock64();
+        for (int i = 1; i <= peers && got; ++i) {
+            const int peer_cta = (group + i) * cg + rank;
+            volatile unsigned int *flag = sk_flags + peer_cta * 8 + e;
+            while (*flag != epoch) {
+                __nanosleep(100);
+                if (*abort_flag) {
+                    got = 0;
+                    break;
+                }
+                if (clock64() - t0 > budget) {
+                    record_timeout(abort_flag, 800 + e, peer_cta);
+                    got = 0;
+                    break;
+                }
+            }
+            if (got) *flag = 0u;                      // ready for the next launch that is dealt this flag set
+        }
+        __threadfence();
+    }
+    got = __shfl_sync(0xffffffffu, got, 0);
+    return got ? peers : -1;
 }
 
 template <int CG>
@@ -202,7 +183,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     Cfg c;
     c.num_units = g.num_units; c.num_tiles = g.num_tiles; c.tiles_m = g.tiles_m; c.tiles_n = g.tiles_n;
     c.tile_group_m = g.tile_group_m; c.tile_m = g.tile_m; c.tile_n = g.tile_n; c.num_segs = g.num_segs;
-    c.split_k = g.split_k; c.tail_full = g.tail_full; c.tail_r = g.tail_r; c.tail_s = g.tail_s; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
+    c.split_k = g.split_k; c.sk_tiles = g.sk_tiles; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
     c.a_stage_bytes = g.a_stage_bytes; c.cta_rows_a = g.cta_rows_a; c.a_box_rows = g.a_box_rows;
     c.a_boxes = g.a_boxes; c.a_priv = g.a_priv; c.a_bars = g.a_bars; c.chunk_n = g.chunk_n; c.b_priv = g.b_priv;
     c.b_res_chunks = g.b_res_chunks; c.b_bars = g.b_bars; c.acc_cols = g.acc_cols; c.mma_m = g.mma_m;
@@ -219,9 +200,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const bool out_half = g.out_half != 0;   // C and D are fp16 (never with a workspace, tail or push path)
     // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage); bits 2 and 3: the
     // epilogue withholds its "slice staged" / "slice read" arrivals of the cluster reduce, so that those
-    // bounded waits run out and the launch ends with a DEVICE_TIMEOUT record (tests of the failure path)
+    // bounded waits run out and the launch ends with a DEVICE_TIMEOUT record (tests of the failure path); bit 4:
+    // the same for the "partial stored" flags of the stream-K schedule
     const int dbg = g.debug_flags;
     const float g_alpha = g.alpha, g_beta = g.beta;
+    volatile unsigned int *const sk_flags = &g_sk_flags[g.sk_set % kSkSets][0][0];
+    const unsigned int sk_epoch = g.sk_epoch;
     const float *const gC = g.C;
     float *const gD = g.D;
     float *const g_partial = g.partial;
@@ -259,6 +243,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     }
     const int group = static_cast<int>(blockIdx.x) / (CG * c.cl_split);   // CTAs that share a tile share a group
     const int num_groups = static_cast<int>(gridDim.x) / (CG * c.cl_split);
+    c.sk_lo = c.sk_hi = 0;
+    if (c.sk_tiles > 0) {
+        c.sk_lo = sk_range_begin(group, c.sk_tiles, c.num_segs, num_groups);
+        c.sk_hi = sk_range_begin(group + 1, c.sk_tiles, c.num_segs, num_groups);
+    }
 
     // Barrier map, per stage: [full A x a_bars][full B x b_bars][empty A][pad x (a_bars-1)][empty B x b_bars];
     // after the stages: tmem_full[2], tmem_empty[2].
@@ -361,8 +350,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const bool k_serpentine = g.k_order == 1;
             long long t_wait = 0;
             const long long t_begin = PROF ? clock64() : 0;
-            for (int u = group; ok && u < c.num_units; u += num_groups) {
-                const Unit w = decode_unit(c, u);
+            Walk walk;
+            walk_init(c, walk, group);
+            Unit w;
+            while (ok && walk_next(c, walk, num_groups, w)) {
                 const int a_row = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
                 const int b_row = w.n0 + static_cast<int>(rank) * (c.tile_n / CG);
                 // Serpentine K: every other tile of this CTA walks its K segments downwards, so the
@@ -376,7 +367,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 ++tile_no;
                 for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
                     const long long tw = PROF ? clock64() : 0;
-                    ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
+                    ok = wait_one(issuer, sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
                     if (PROF) t_wait += clock64() - tw;
                     if (!ok) break;
                     if (arm) mbar_arrive_expect_tx(sb, (dbg & 2) ? 0u : my_bytes);
@@ -432,12 +423,14 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             bool ok = true;
             long long t_full = 0, t_acc = 0;
             const long long t_begin = PROF ? clock64() : 0;
-            for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
-                const Unit w = decode_unit(c, u);
+            Walk walk;
+            walk_init(c, walk, group);
+            Unit w;
+            for (; ok && walk_next(c, walk, num_groups, w); ++tl) {
                 const uint32_t acc = tl & 1u;
                 const uint32_t aph = (tl >> 1) & 1u;
                 const long long ta = PROF ? clock64() : 0;
-                ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                ok = wait_one(issuer, tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
                 if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -445,7 +438,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 uint32_t accumulate = 0;
                 for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
                     const long long tf = PROF ? clock64() : 0;
-                    ok = wait_all(sb, ph, c.budget, abort_flag, 400 + s);
+                    ok = wait_one(issuer, sb, ph, c.budget, abort_flag, 400 + s);
                     if (PROF) t_full += clock64() - tf;
                     if (!ok) break;
                     if (it == 0 && lane == 0) B200_TL(20);
@@ -514,14 +507,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             bool ok = true;
             long long t_wait = 0;
             const long long t_begin = PROF ? clock64() : 0;
-            for (int u = group; ok && u < c.num_units; u += num_groups) {
-                const Unit w = decode_unit(c, u);
+            Walk walk;
+            walk_init(c, walk, group);
+            Unit w;
+            while (ok && walk_next(c, walk, num_groups, w)) {
                 const int a_row = w.m0 + static_cast<int>(rank) * c.cta_rows_a;
                 int k = w.seg_begin * c.kblocks * kBoxK;
                 for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
                     if (do_a) {
                         const long long tw = PROF ? clock64() : 0;
-                        ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
+                        ok = wait_one(issuer, sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
                         if (PROF) t_wait += clock64() - tw;
                         if (!ok) break;
                         uint32_t box_dst = stage;
@@ -559,7 +554,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         for (int t = 0; t < c.b_bars; ++t) {
                             if (!(merged && do_a)) {  // merged + same warp: the stage was acquired above
                                 const long long tw = PROF ? clock64() : 0;
-                                ok = wait_all(sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u, c.budget, abort_flag,
+                                ok = wait_one(issuer, sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u, c.budget, abort_flag,
                                               200 + s * 32 + t);
                                 if (PROF) t_wait += clock64() - tw;
                                 if (!ok) break;
@@ -629,12 +624,14 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             bool ok = true;
             long long t_full = 0, t_acc = 0;
             const long long t_begin = PROF ? clock64() : 0;
-            for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
-                const Unit w = decode_unit(c, u);
+            Walk walk;
+            walk_init(c, walk, group);
+            Unit w;
+            for (; ok && walk_next(c, walk, num_groups, w); ++tl) {
                 const uint32_t acc = tl & 1u;
                 const uint32_t aph = (tl >> 1) & 1u;
                 const long long ta = PROF ? clock64() : 0;
-                ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                ok = wait_one(issuer, tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
                 if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -642,7 +639,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 uint32_t later_seg = 0;
                 for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
                     const long long tf = PROF ? clock64() : 0;
-                    for (int j = 0; ok && j < c.a_bars; ++j) ok = wait_all(sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j);
+                    for (int j = 0; ok && j < c.a_bars; ++j) ok = wait_one(issuer, sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j);
                     if (PROF) t_full += clock64() - tf;
                     if (!ok) break;
                     uint64_t sub_desc = b_desc;
@@ -650,7 +647,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     for (int t = 0; t < c.b_bars; ++t) {
                         if (!merged) {
                             const long long tb = PROF ? clock64() : 0;
-                            ok = wait_all(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
+                            ok = wait_one(issuer, sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
                             if (PROF) t_full += clock64() - tb;
                             if (!ok) break;
                         }
@@ -726,13 +723,14 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         bool ok = true;
         long long t_tfull = 0;
         const long long t_begin = clock64();
-        for (int u = group; ok && u < c.num_units; u += num_groups, ++tl) {
-            const Unit w = decode_unit(c, u);
+        Walk walk;
+        walk_init(c, walk, group);
+        Unit w;
+        for (; ok && walk_next(c, walk, num_groups, w); ++tl) {
             const uint32_t acc = tl & 1u;
             const uint32_t aph = (tl >> 1) & 1u;
             const long long te = prof ? clock64() : 0;
-            ok = wait_bar(tmem_full0 + 8u * acc, aph, c.budget, abort_flag, 600 + static_cast<int>(acc));
-            ok = __all_sync(0xffffffffu, ok);
+            ok = wait_one(lane == 0, tmem_full0 + 8u * acc, aph, c.budget, abort_flag, 600 + static_cast<int>(acc));
             if (prof) t_tfull += clock64() - te;
             if (!ok) break;
             if (tl == 0 && e == 0 && lane == 0) B200_TL(22);
@@ -749,21 +747,32 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 out = g.push_slot[owner];
                 row_off = (static_cast<size_t>(push_rank) * push_rows + static_cast<size_t>(row - owner * push_rows)) * c.N + w.n0;
             }
-            const bool tail = w.tail_idx >= 0;
-            if (tail) {
-                // a K slice of a tail tile: raw accumulator into the workspace, tile-local layout
-                out = g_partial;
-                row_off = (static_cast<size_t>(w.slice * c.tail_r + w.tail_idx) * c.tile_m + static_cast<size_t>(row - w.m0)) * c.tile_n;
-            }
-            const float a_u = tail ? 1.0f : alpha;
-            const float b_u = tail ? 0.0f : beta;
+            const float a_u = alpha;
+            const float b_u = beta;
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
+            // Stream-K pieces. The workspace holds one partial per CTA: per 32-lane quarter and 32-column chunk
+            // eight groups of [32 lanes] float4 (lane l keeps its columns 4j .. 4j+3 in group j), so a warp
+            // stores and re-loads 512 consecutive bytes per instruction, and warp e of the finishing CTA reads
+            // exactly what warp e of a peer wrote. A piece of kind 1 first waits (bounded) until the CTAs that
+            // hold the tile's later K parts have stored theirs: those are the groups after this one whose
+            // ranges begin inside this tile.
+            int sk_peers = 0;
+            if (w.kind == 1) {
+                sk_peers = sk_wait_peers(sk_flags, sk_epoch, group, num_groups, c.sk_hi, c.sk_tiles, c.num_segs, w.tile_end, CG,
+                                         static_cast<int>(rank), e, c.budget, abort_flag);
+                if (sk_peers < 0) {
+                    ok = false;
+                    break;
+                }
+            }
+            const uint32_t sk_chunks = static_cast<uint32_t>(c.tile_n + 31) >> 5;
+            const uint32_t sk_slot = sk_chunks * 1024u;                                    // float4 per CTA (offsets fit 32 bits)
+            const uint32_t sk_lane = static_cast<uint32_t>(q) * sk_chunks * 256u + static_cast<uint32_t>(lane);
             if (c.cl_split > 1) {
                 // ---- K slices of this tile live in the CTAs of the cluster (transposed drain only).
                 // A: raw accumulator -> this CTA's shared memory as [column][row]; tell every CTA.
                 const uint32_t pbuf = base + static_cast<uint32_t>(off_epi);
-                ok = wait_bar_cluster(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
-                ok = __all_sync(0xffffffffu, ok);
+                ok = wait_one<true>(lane == 0, part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
                 if (!ok) break;
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                     uint32_t r[32];
@@ -801,8 +810,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (e == 0 && lane == 0) B200_TL(29);
                 // B: when all slices are staged, this CTA sums its share of the tile's columns over the
                 // cluster in slice order (the order of the workspace form) and writes D.
-                ok = wait_bar_cluster(part_full, tl & 1u, c.budget, abort_flag, 701);
-                ok = __all_sync(0xffffffffu, ok);
+                ok = wait_one<true>(lane == 0, part_full, tl & 1u, c.budget, abort_flag, 701);
                 if (!ok) break;
                 if (e == 0 && lane == 0) B200_TL(30);
                 const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
@@ -934,6 +942,29 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 tmem_ld_wait();
                 if (e == 0 && lane == 0) B200_TL(18);
                 const int nvec = wide ? 8 : 4;
+                if (w.kind == 2) {
+                    // raw partial of this chunk into this CTA's slot (a 16-column last chunk stores its zero padding too)
+                    float4 *dst = reinterpret_cast<float4 *>(g_partial) + (blockIdx.x * sk_slot + sk_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        dst[j * 32] = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
+                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    continue;
+                }
+                for (int i = 1; i <= sk_peers; ++i) {
+                    // the peers' partials of this chunk, added in ascending K order; .cg: written by other SMs
+                    const float4 *src = reinterpret_cast<const float4 *>(g_partial) +
+                                        (static_cast<uint32_t>((group + i) * CG + static_cast<int>(rank)) * sk_slot + sk_lane +
+                                         static_cast<uint32_t>(c0 >> 5) * 256u);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 v = __ldcg(src + j * 32);
+                        r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + v.x);
+                        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+                        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                    }
+                }
                 if (swap_ab) {
                     // Transposed drain: this thread's row is a column of D and register j its row
                     // w.n0 + c0 + j, so for every j the 32 lanes store 32 consecutive floats. The
@@ -1009,7 +1040,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                             }
                         }
                     }
-                } else if (c.epi_mode == 0 || !wide || tail) {
+                } else if (c.epi_mode == 0 || !wide) {
                     if (row_ok) {
                         float4 *dst = reinterpret_cast<float4 *>(out + row_off + c0);
                         const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
@@ -1064,6 +1095,15 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         tma_store_commit();
                     }
                     ++store_idx;
+                }
+            }
+            if (w.kind == 2) {
+                // this warp's part of the partial is complete: make it visible, then say so
+                __threadfence();
+                __syncwarp();
+                if (lane == 0 && !(dbg & 16)) {
+                    __threadfence();
+                    *(sk_flags + static_cast<int>(blockIdx.x) * 8 + e) = sk_epoch;
                 }
             }
             // accumulator slot drained: hand it back to the MMA thread
@@ -1270,81 +1310,6 @@ int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int sp
     return static_cast<int>(cudaGetLastError());
 }
 
-// Second step of the tail split. One block column per tail tile; the tile's position comes from
-// the same grouped order as decode_unit. Slices are summed in ascending order.
-struct TailReduceArgs {
-    const float *partial;
-    const float *C;
-    float *D;
-    float alpha, beta;
-    int M, N, tile_m, tile_n, tiles_m, tiles_n, tile_group_m, full, r, s;
-};
-
-__global__ void tail_reduce_kernel(const __grid_constant__ TailReduceArgs a) {
-    const int idx = blockIdx.y;  // tail tile
-    const int t = a.full + idx;
-    const int group_tile_count = a.tile_group_m * a.tiles_n;
-    const int group_first_row = (t / group_tile_count) * a.tile_group_m;
-    const int group_rows = min(a.tiles_m - group_first_row, a.tile_group_m);
-    const int in_group = t % group_tile_count;
-    const int m0 = (group_first_row + in_group % group_rows) * a.tile_m;
-    const int n0 = (in_group / group_rows) * a.tile_n;
-    const int n4 = a.tile_n / 4;
-    const long long tile_elems4 = static_cast<long long>(a.tile_m) * n4;
-    const float4 *p4 = reinterpret_cast<const float4 *>(a.partial);
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < tile_elems4;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int row = m0 + static_cast<int>(i / n4);
-        const int col = n0 + static_cast<int>(i % n4) * 4;
-        if (row >= a.M || col >= a.N) continue;
-        float4 sum = p4[static_cast<long long>(idx) * tile_elems4 + i];
-        for (int k = 1; k < a.s; ++k) {
-            const float4 v = p4[(static_cast<long long>(k) * a.r + idx) * tile_elems4 + i];
-            sum.x += v.x;
-            sum.y += v.y;
-            sum.z += v.z;
-            sum.w += v.w;
-        }
-        const size_t o = static_cast<size_t>(row) * a.N + col;
-        float4 out;
-        out.x = a.alpha * sum.x;
-        out.y = a.alpha * sum.y;
-        out.z = a.alpha * sum.z;
-        out.w = a.alpha * sum.w;
-        if (a.beta != 0.0f) {
-            const float4 c = *reinterpret_cast<const float4 *>(a.C + o);
-            out.x += a.beta * c.x;
-            out.y += a.beta * c.y;
-            out.z += a.beta * c.z;
-            out.w += a.beta * c.w;
-        }
-        *reinterpret_cast<float4 *>(a.D + o) = out;
-    }
-}
-
-int launch_tail_reduce(const GemmArgs &g, cudaStream_t stream) {
-    TailReduceArgs a;
-    a.partial = g.partial;
-    a.C = g.C;
-    a.D = g.D;
-    a.alpha = g.alpha;
-    a.beta = g.beta;
-    a.M = g.M;
-    a.N = g.N;
-    a.tile_m = g.tile_m;
-    a.tile_n = g.tile_n;
-    a.tiles_m = g.tiles_m;
-    a.tiles_n = g.tiles_n;
-    a.tile_group_m = g.tile_group_m;
-    a.full = g.tail_full;
-    a.r = g.tail_r;
-    a.s = g.tail_s;
-    const int per_tile = (g.tile_m * g.tile_n / 4 + 255) / 256;
-    dim3 grid(static_cast<unsigned>(per_tile < 16 ? per_tile : 16), static_cast<unsigned>(g.tail_r), 1);
-    tail_reduce_kernel<<<grid, 256, 0, stream>>>(a);
-    return static_cast<int>(cudaGetLastError());
-}
-
 int launch_push_reduce(const float *slots, const int *flags, int world, int epoch, const float *C, float *D, float alpha,
                        float beta, int64_t rows, int64_t n, long long budget_cycles, cudaStream_t stream) {
     const long long n4 = rows * n / 4;
@@ -1397,6 +1362,7 @@ int max_active_clusters(KernelFn fn, const cudaLaunchConfig_t &cfg, int cluster)
 }  // namespace
 
 int profile_slots() { return kProfSlots; }
+int stream_k_max_ctas() { return kSkMaxCtas; }
 
 int prepare_kernels() {
     for (int cg = 1; cg <= 2; ++cg)
@@ -1474,6 +1440,11 @@ int read_device_status(int out[4], cudaStream_t stream) {
     if (host[0] != 0) {
         const int zero[4] = {0, 0, 0, 0};
         e = cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        // a launch that timed out may have left stream-K flags raised that nobody consumed
+        void *flags = nullptr;
+        e = cudaGetSymbolAddress(&flags, g_sk_flags);
+        if (e == cudaSuccess) e = cudaMemset(flags, 0, sizeof(unsigned int) * kSkSets * kSkMaxCtas * 8);
         if (e != cudaSuccess) return static_cast<int>(e);
     }
     for (int i = 0; i < 4; ++i) out[i] = host[i];

@@ -53,29 +53,37 @@ struct Plan {
                                           //    in distributed shared memory (no workspace, no second kernel)
 };
 
-// Tail split: with T tiles on S slots (CTAs or CTA pairs) the last wave holds r = T mod S tiles.
-// If r <= S / 2 each of them is cut into s = floor(S / r) K slices so the wave takes 1/s of a tile
-// time; the slices meet in the workspace. s == 1 means "not worth it / off".
-struct TailSplit {
-    int full = 0;    // tiles processed whole (a multiple of S)
-    int r = 0;       // tiles of the last wave
-    int s = 1;       // K slices per tail tile
+// Stream-K schedule of the tiles that do not fill a wave of the persistent grid (tail_split = 1).
+// T tiles on S slots (CTAs, or CTA pairs) leave r = T mod S tiles for a last, partly idle wave. Instead,
+// a "stream-K region" of sk_tiles tiles is processed first and cut by K iterations, not by tiles: its
+// sk_tiles * num_segs iterations (one iteration = one K segment of one tile) are dealt out in S equal
+// contiguous ranges, one per slot, so a slot's range covers the end of one tile, possibly whole tiles,
+// and the beginning of another. The remaining T - sk_tiles tiles (a multiple of S) follow as whole
+// tiles. A tile cut between slots is finished by the slot that holds its first K iterations (it comes
+// last in that slot's range, when the others are done): the other slots store their raw partial
+// accumulators in the workspace and raise a flag, the finishing slot adds them in ascending K order.
+// sk_tiles == 0 means "off / nothing to gain".
+struct StreamK {
+    int sk_tiles = 0;        // tiles of the stream-K region (the first sk_tiles tiles in tile order)
+    int64_t slot_bytes = 0;  // one partial per CTA: 128 lanes x ceil(tile_n / 32) chunks of 32 columns, fp32
 };
 
-inline TailSplit make_tail_split(int enabled, int64_t tiles, int slots, int64_t num_segs, int split_k) {
-    TailSplit t;
-    t.full = static_cast<int>(tiles);
-    if (!enabled || split_k > 1 || slots < 1 || tiles <= 0) return t;
-    const int r = static_cast<int>(tiles % slots);
-    if (r == 0) return t;
-    int s = slots / r;
-    if (s > 8) s = 8;
-    if (s > num_segs) s = static_cast<int>(num_segs);
-    if (s < 2) return t;
-    t.full = static_cast<int>(tiles - r);
-    t.r = r;
-    t.s = s;
-    return t;
+inline StreamK make_stream_k(int enabled, int64_t tiles, int slots, int64_t num_segs, int split_k, int tile_n) {
+    StreamK k;
+    if (!enabled || split_k > 1 || slots < 2 || tiles <= 0) return k;
+    const int64_t r = tiles % slots;
+    if (r == 0) return k;
+    // The region: the r left-over tiles when they are at least half a wave; otherwise one more whole wave
+    // is folded in, so that a tile is cut between two or three slots rather than among many (every peer of a
+    // finishing slot costs it one more partial tile to read back).
+    int64_t sk = r;
+    if (2 * r < slots) sk = (tiles >= r + slots) ? r + slots : r;
+    if (4 * sk < slots) return k;                          // a tile would be cut among more than five slots
+    const int64_t iters = sk * num_segs;
+    if (iters >= (int64_t(1) << 31) || iters / slots < 4) return k;   // 32-bit iteration counters; ranges of >= 4 segments
+    k.sk_tiles = static_cast<int>(sk);
+    k.slot_bytes = int64_t((tile_n + 31) / 32) * 4 * 32 * 32 * 4;
+    return k;
 }
 
 inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
@@ -131,9 +139,9 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     if (q.num_producer_warps != 1 && q.num_producer_warps != 2 && q.num_producer_warps != 4 &&
         q.num_producer_warps != 8)
         return p;                                                      // async.cu:516
-    // Only the first two producer warps issue copies; of eight requested, seven are launched, which keeps
-    // the block at 16 warps (512 threads: 128 registers per thread instead of 96).
-    p.producer_warps = q.num_producer_warps > 7 ? 7 : q.num_producer_warps;
+    // Only the first two producer warps issue copies, the others would idle: at most three are launched, which
+    // keeps the block at 12 warps (384 threads) and the kernel's register budget at 168 per thread.
+    p.producer_warps = q.num_producer_warps > 3 ? 3 : q.num_producer_warps;
     if (q.num_consumer_warps != 4 && q.num_consumer_warps != 8) return p;  // async.cu:517
     p.epi_warps = q.num_consumer_warps;
     p.threads = (p.producer_warps + 1 + p.epi_warps) * 32;

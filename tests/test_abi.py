@@ -173,17 +173,89 @@ def test_swapped_roles_and_cluster_reduce_domain(pkg):
     assert d.swap_ab == 0 and pkg.validate(16, 28672, 8192, pkg.BF16, d) == pkg.OK
 
 
-def test_tail_split_planning(pkg):
-    """Tiles mod slots decides: 4096^3 in 256x256 pair tiles is 256 tiles on 74 pairs = 3 waves + 34,
-    so each of the 34 is cut in 2; 8192^3 leaves 62 of 74 (no gain); a full wave leaves nothing."""
+def _coverage(pkg, M, N, K, p, num_sms):
+    """Walks every CTA group's schedule; returns ({(m0, n0): [(seg_begin, seg_end, kind, group), ...]}, groups)."""
+    groups, _ = pkg.schedule(M, N, K, p, num_sms, 0)
+    tiles = {}
+    for g in range(groups):
+        _, units = pkg.schedule(M, N, K, p, num_sms, g)
+        for (m0, n0, sb, se, kind, sl) in units:
+            tiles.setdefault((m0, n0), []).append((sb, se, kind, g))
+    return tiles, groups
+
+
+def test_stream_k_schedule_covers_every_k_segment_once(pkg):
+    """tail_split = 1 (stream-K): whatever the shape, every K segment of every tile is computed by exactly one
+    CTA group; a tile cut between groups has one finishing piece (kind 1, from segment 0) in the lowest group and
+    its later parts (kind 2) in the groups right after it, each the first unit of its group; whole tiles are kind 0;
+    every group does the same number of K segments to within one tile's worth of rounding."""
     pair = dict(tile_m=256, tile_n=256, cta_group=2, bar_step_rows_a=256, bar_step_rows_b=256, num_stages=6, tail_split=1)
-    assert pkg.workspace_bytes(4096, 4096, 4096, P(pkg, **pair)) == 2 * 34 * 256 * 256 * 4
-    assert pkg.workspace_bytes(8192, 8192, 8192, P(pkg, **pair)) == 0
-    assert pkg.workspace_bytes(256 * 74, 256, 4096, P(pkg, **pair)) == 0
-    assert pkg.workspace_bytes(4096, 4096, 4096, P(pkg, **dict(pair, tail_split=0))) == 0
     one = dict(tile_m=128, tile_n=128, tail_split=1)
-    assert pkg.workspace_bytes(128 * 3, 128 * 50, 64, P(pkg, **one)) == 0        # one K segment cannot be split
-    assert pkg.workspace_bytes(128 * 3, 128 * 50, 1024, P(pkg, **one)) == 8 * 2 * 128 * 128 * 4   # 150 tiles on 148: 2 left, 8 slices each (the cap)
+    cases = [(4096, 4096, 4096, pair, 148), (8192, 8192, 8192, pair, 148), (1024, 8192, 8192, pair, 148), (2048, 2048, 262144, pair, 148),
+             (128 * 3, 128 * 50, 1024, one, 148), (1000, 1000, 520, one, 148), (2048, 2048, 2048, pair, 148), (640, 896, 4096, one, 20),
+             (4096, 4096, 4096, dict(pair, num_sms=132), 132), (256 * 74, 256, 4096, pair, 148), (300, 520, 2048, dict(one, tile_n=64), 40)]
+    engaged = 0
+    for M, N, K, ov, sms in cases:
+        p = P(pkg, **dict(ov, num_sms=sms))
+        assert pkg.validate(M, N, K, pkg.F16, p) == pkg.OK
+        tiles, groups = _coverage(pkg, M, N, K, p, sms)
+        tm, tn, segs = p.tile_m, p.tile_n, -(-K // p.segment_dim_k)
+        assert len(tiles) == -(-M // tm) * -(-N // tn), (M, N, K)
+        work = [0] * groups
+        cut = 0
+        for (m0, n0), parts in tiles.items():
+            assert m0 % tm == 0 and n0 % tn == 0 and m0 < M and n0 < N
+            parts.sort()
+            assert parts[0][0] == 0 and parts[-1][1] == segs, ((m0, n0), parts)
+            for (sb, se, kind, g), nxt in zip(parts, parts[1:] + [None]):
+                assert sb < se
+                work[g] += se - sb
+                if nxt is not None:
+                    assert se == nxt[0], ((m0, n0), parts)                 # no gap, no overlap
+                    assert nxt[3] == g + 1                                 # the later part belongs to the next group
+            if len(parts) == 1:
+                assert parts[0][2] == 0
+            else:
+                cut += 1
+                assert parts[0][2] == 1 and all(k == 2 for _, _, k, _ in parts[1:]), parts
+                assert len(parts) <= 6
+        for g in range(groups):                                            # a later part is always a group's first unit
+            _, units = pkg.schedule(M, N, K, p, sms, g)
+            assert all(u[4] != 2 for u in units[1:]), (g, units)
+        if cut:
+            engaged += 1
+            assert max(work) - min(work) <= 1, (M, N, K, min(work), max(work))   # equal shares of the K segments
+            assert pkg.workspace_bytes(M, N, K, p) == (p.num_sms or sms) * -(-tn // 32) * 16384
+        else:
+            assert pkg.workspace_bytes(M, N, K, p) == 0
+        off, _ = _coverage(pkg, M, N, K, P(pkg, **dict(ov, num_sms=sms, tail_split=0)), sms)
+        assert all(len(v) == 1 and v[0][2] == 0 for v in off.values()) and set(off) == set(tiles)
+    assert engaged >= 7
+    # 256 tiles on 74 pairs: 34 left over, fewer than half a wave, so one whole wave joins the region (108 tiles, 2 waves of whole tiles follow)
+    tiles, groups = _coverage(pkg, 4096, 4096, 4096, P(pkg, **pair), 148)
+    assert groups == 74 and sum(1 for v in tiles.values() if len(v) > 1) == 72   # 73 inner range boundaries, one falls on a tile edge
+    # a full last wave leaves nothing to cut; one K segment cannot be cut
+    assert pkg.workspace_bytes(256 * 74, 256, 4096, P(pkg, **pair)) == 0
+    assert pkg.workspace_bytes(128 * 3, 128 * 50, 64, P(pkg, **one)) == 0
+    with pytest.raises(ValueError):
+        pkg.schedule(4096, 4096, 4096, P(pkg, **pair), 148, 74)
+
+
+def test_plain_and_split_k_schedules(pkg):
+    """Without stream-K: group g takes units g, g + groups, ...; split_k slices are separate units of the same tile;
+    the tiles follow the reference's grouped order (tile_group_m tile rows column-major inside a group,
+    matmul_shmem_tc_async_opt_port_0.cu:201-210)."""
+    p = P(pkg, tile_group_m=2, num_sms=4)
+    groups, u0 = pkg.schedule(512, 384, 256, p, 4, 0)
+    assert groups == 4
+    order = []
+    for i in range(12):
+        _, u = pkg.schedule(512, 384, 256, p, 4, i % 4)
+        order.append(u[i // 4][:2])
+    assert order == [(0, 0), (128, 0), (0, 128), (128, 128), (0, 256), (128, 256), (256, 0), (384, 0), (256, 128), (384, 128), (256, 256), (384, 256)]
+    p = P(pkg, split_k=2, num_sms=8)
+    tiles, groups = _coverage(pkg, 256, 256, 1024, p, 8)
+    assert groups == 8 and all(sorted((sb, se) for sb, se, _, _ in v) == [(0, 8), (8, 16)] for v in tiles.values())
 
 
 def test_default_params_are_valid(pkg):
@@ -201,7 +273,9 @@ def test_status_strings(pkg):
 
 def test_defaults_are_valid_everywhere_and_need_no_workspace(pkg):
     """b200_gemm_default_params (and its plain twin) over a grid of shapes: always a valid configuration for the
-    shape, never one that needs a caller workspace, swapped forms only where the activations are few."""
+    shape, never one that needs a caller workspace (the stream-K schedule of tail_split only uses one when it is
+    given; K slices that must meet in a workspace are never a default), swapped forms only where the activations
+    are few."""
     import itertools
     Ms = (1, 7, 16, 17, 32, 33, 64, 65, 100, 128, 129, 256, 300, 1000, 1024, 4096, 8192)
     Ns = (4, 16, 64, 100, 128, 256, 1000, 1024, 3584, 4096, 7168, 14336, 28672, 28676)
@@ -213,7 +287,11 @@ def test_defaults_are_valid_everywhere_and_need_no_workspace(pkg):
                 fn = pkg.lib().b200_gemm_default_params_plain if plain else pkg.lib().b200_gemm_default_params
                 assert fn(M, N, K, dtype, ctypes.byref(p)) == pkg.OK
                 assert pkg.validate(M, N, K, dtype, p) == pkg.OK, (M, N, K, plain, p.as_dict())
-                assert pkg.workspace_bytes(M, N, K, p) == 0, (M, N, K, plain, p.as_dict())
+                assert p.split_k == 1 or p.cluster_reduce == 1, (M, N, K, plain, p.as_dict())
+                if pkg.workspace_bytes(M, N, K, p):
+                    assert p.tail_split == 1 and p.swap_ab == 0
+                    p.tail_split = 0
+                    assert pkg.workspace_bytes(M, N, K, p) == 0, (M, N, K, plain, p.as_dict())
                 assert pkg.smem_bytes(dtype, p) > 0
                 if plain or M > 128:
                     assert p.swap_ab == 0
