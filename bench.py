@@ -321,7 +321,7 @@ def run_ours(args):
     assert st == pkg.OK, f"invalid configuration {p.as_dict()}: {pkg.status_string(st)}"
     ws_bytes = pkg.workspace_bytes(m_loc, n_loc, k_loc, p)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-    # the split-K reduce is a second kernel (not with the cluster reduce; the stream-K schedule finishes inside the GEMM)
+    # the split-K reduce is a second kernel (not with the cluster reduce; the tail split finishes inside the GEMM)
     launches_per_step = 1 + (1 if (p.split_k > 1 and not p.cluster_reduce) else 0) + (1 if fused else 0)
     push = shard.PushExchange(pkg, M, N) if fused else None
     D_rows = torch.empty((M // world, N), dtype=torch.float32, device=dev) if fused else None

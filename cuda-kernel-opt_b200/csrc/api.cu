@@ -21,7 +21,7 @@ namespace {
 
 thread_local int t_last_cuda_error = 0;
 std::atomic<uint64_t> g_wait_budget_ns{2000000000ull};
-std::atomic<unsigned int> g_sk_epoch{0u};
+std::atomic<unsigned int> g_tail_epoch{0u};
 std::atomic<long long *> g_prof_ptr{nullptr};
 std::atomic<int> g_prof_blocks{0};
 
@@ -281,15 +281,14 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
          reinterpret_cast<uintptr_t>(C)) & 15u)
         return B200_INVALID_POINTER;
     const int64_t n_tiles = ((kM + p.tile_m - 1) / p.tile_m) * ((kN + p.tile_n - 1) / p.tile_n);
-    // Stream-K (tail_split) is an optimisation of the schedule, taken when the caller's workspace can hold
-    // one partial tile per CTA; without it the plain schedule runs and the result is the same to rounding.
-    // (its CTAs wait for one another, so all of them must be resident at once: one per SM)
-    StreamK sk = make_stream_k(user->tail_split && !p.swap && p.grid <= stream_k_max_ctas() && p.grid <= dev->num_sms, n_tiles,
-                               p.grid / p.cta_group,
-                               (K + p.seg_k - 1) / p.seg_k, p.split_k, p.tile_n);
-    if (sk.sk_tiles > 0 && (!workspace || workspace_bytes < static_cast<size_t>(sk.slot_bytes) * p.grid ||
-                            (reinterpret_cast<uintptr_t>(workspace) & 15u)))
-        sk = StreamK();
+    // The tail split is an optimisation of the schedule, taken when the caller's workspace can hold the partials;
+    // without it the plain schedule runs and the result is the same to rounding. Its CTAs wait for one another,
+    // so all of them must be resident at once: one per SM.
+    TailPlan tail = make_tail_plan(user->tail_split && !p.swap && p.grid <= dev->num_sms, n_tiles, p.grid / p.cta_group,
+                                   (K + p.seg_k - 1) / p.seg_k, p.split_k, p.tile_n, p.cta_group);
+    if (tail.tiles > 0 && (!workspace || workspace_bytes < static_cast<size_t>(tail.slot_bytes * tail.slots) ||
+                           (reinterpret_cast<uintptr_t>(workspace) & 15u)))
+        tail = TailPlan();
     const int ws_split = p.cluster_reduce ? 1 : p.split_k;  // K slices that meet in the workspace
     // fp16 output leaves through the plain, transposed and cluster drains only: the split-K workspace and
     // push forms keep fp32 partials and their second kernels write fp32
@@ -335,13 +334,14 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.split_k = ws_split;
     a.cl_split = p.cluster_reduce ? p.split_k : 0;
     a.num_units = a.num_tiles * ws_split;
-    a.sk_tiles = sk.sk_tiles;
-    if (sk.sk_tiles > 0) {
+    a.tail_tiles = tail.tiles;
+    a.tail_slices = tail.slices;
+    if (tail.tiles > 0) {
         // every launch that uses the fix-up flags gets its own epoch (never 0) and the next flag set in turn
-        unsigned int epoch = g_sk_epoch.fetch_add(1u) + 1u;
-        if (epoch == 0u) epoch = g_sk_epoch.fetch_add(1u) + 1u;
-        a.sk_epoch = epoch;
-        a.sk_set = static_cast<int>(epoch & 0x7fffffffu);
+        unsigned int epoch = g_tail_epoch.fetch_add(1u) + 1u;
+        if (epoch == 0u) epoch = g_tail_epoch.fetch_add(1u) + 1u;
+        a.tail_epoch = epoch;
+        a.tail_set = static_cast<int>(epoch & 0x7fffffffu);
     }
     a.num_segs = static_cast<int>((K + p.seg_k - 1) / p.seg_k);
     a.tile_m = p.tile_m;
@@ -436,7 +436,7 @@ struct b200_session {
     cudaStream_t compute;     // launches
     cudaStream_t download;    // results
     cudaEvent_t up[16], done[16], b_ready;
-    void *dW;                 // workspace for the stream-K schedule of the block products
+    void *dW;                 // workspace for the tail split of the block products
     size_t w_bytes;
 };
 
@@ -501,13 +501,10 @@ int b200_gemm_schedule(int64_t M, int64_t N, int64_t K, const b200_gemm_params *
     const int num_groups = grid / (plan.cta_group * c.cl_split);
     if (num_groups_out) *num_groups_out = num_groups;
     if (group < 0 || group >= num_groups) return -1;
-    const StreamK sk = make_stream_k(q.tail_split && !plan.swap && grid <= stream_k_max_ctas(), c.num_tiles, num_groups, c.num_segs,
-                                     plan.split_k, plan.tile_n);
-    c.sk_tiles = sk.sk_tiles;
-    if (c.sk_tiles > 0) {
-        c.sk_lo = sk_range_begin(group, c.sk_tiles, c.num_segs, num_groups);
-        c.sk_hi = sk_range_begin(group + 1, c.sk_tiles, c.num_segs, num_groups);
-    }
+    const TailPlan tail = make_tail_plan(q.tail_split && !plan.swap, c.num_tiles, num_groups, c.num_segs, plan.split_k, plan.tile_n,
+                                         plan.cta_group);
+    c.tail_tiles = tail.tiles;
+    c.tail_slices = tail.slices;
     c.cl_seg_end = c.num_segs;   // a cluster's slices: listed for slice 0 .. as the whole K range of the tile
     Walk walk;
     walk_init(c, walk, group);
@@ -535,10 +532,11 @@ int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_ge
             cudaGetLastError();
         }
         const Plan plan = make_plan(*p, sms);
-        if (plan.status != B200_OK || plan.swap || plan.grid > stream_k_max_ctas()) return 0;
+        if (plan.status != B200_OK || plan.swap) return 0;
         const int64_t n_tiles = ((M + plan.tile_m - 1) / plan.tile_m) * ((N + plan.tile_n - 1) / plan.tile_n);
-        const StreamK k = make_stream_k(1, n_tiles, plan.grid / plan.cta_group, (K + plan.seg_k - 1) / plan.seg_k, plan.split_k, plan.tile_n);
-        if (k.sk_tiles > 0) return k.slot_bytes * plan.grid;
+        const TailPlan t = make_tail_plan(1, n_tiles, plan.grid / plan.cta_group, (K + plan.seg_k - 1) / plan.seg_k, plan.split_k,
+                                          plan.tile_n, plan.cta_group);
+        if (t.tiles > 0) return t.slot_bytes * t.slots;
     }
     return 0;
 }
@@ -641,7 +639,7 @@ int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_sessio
     if (e == cudaSuccess) e = cudaMalloc(&s->dB, static_cast<size_t>(max_n) * max_k * 2);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dC), static_cast<size_t>(max_m) * max_n * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&s->dD), static_cast<size_t>(max_m) * max_n * 4);
-    s->w_bytes = static_cast<size_t>(stream_k_max_ctas()) * 128 * 256 * sizeof(float);   // one 128 x 256 fp32 partial per CTA
+    s->w_bytes = static_cast<size_t>(192) * 128 * 256 * sizeof(float);   // tail-split partials of the block products (a smaller need is the common case; a larger one falls back to the plain schedule)
     if (e == cudaSuccess) e = cudaMalloc(&s->dW, s->w_bytes);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->compute, cudaStreamNonBlocking);

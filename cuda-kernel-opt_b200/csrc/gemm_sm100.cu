@@ -57,12 +57,11 @@ constexpr int kProfSlots = 16;
 #endif
 constexpr int kMaxThreads = 384;  // (3 producer + 1 MMA + 8 epilogue warps) * 32: up to 168 registers per thread
 
-// Flags of the stream-K fix-up: [set][CTA][epilogue warp] holds the epoch of the launch whose partial
-// that warp has stored. A set belongs to one launch at a time (the host deals them out in turn); the
-// finishing warp puts the flag back to zero. Zero at load.
-constexpr int kSkSets = 32;
-constexpr int kSkMaxCtas = 192;
-__device__ unsigned int g_sk_flags[kSkSets][kSkMaxCtas][8];
+// Flags of the tail split's fix-up: [set][partial slot][epilogue warp] holds the epoch of the launch whose
+// partial that warp has stored. A set belongs to one launch at a time (the host deals them out in turn);
+// the finishing warp puts the flag back to zero. Zero at load.
+constexpr int kTailSets = 16;
+__device__ unsigned int g_tail_flags[kTailSets][kTailMaxSlots][8];
 
 // A bounded wait ran out: raise the block-wide abort flag and leave {code, block, wait id, detail} in
 // the device status record (the first timeout of a launch wins).
@@ -97,66 +96,48 @@ __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, long long 
     }
 }
 
-// One lane of a converged warp waits (`leader` is true in exactly one lane), the others park at the vote,
-// where the result reaches every lane: a waiting warp then costs one polling thread, not thirty-two. What the
-// leader observed (TMA bytes landed, MMAs committed, a peer's release) is ordered before what any lane does
-// after the vote; lanes that go on to read tensor memory still issue their own tcgen05 fence.
-// -DB200_WAIT_ALL_LANES restores polling by every lane (for A/B measurements of the difference).
-#ifdef B200_WAIT_ALL_LANES
-constexpr bool kAllLanesPoll = true;
-#else
-constexpr bool kAllLanesPoll = false;
-#endif
-
+// Every lane of a converged warp waits; the result is the same in every lane. All lanes execute the same
+// try_wait on the same barrier, so the warp never diverges here and the .sync.aligned tensor-memory
+// instructions that follow a wait find it converged. (Letting one elected lane poll while the others park at
+// the vote was tried to save issue slots: it measured 1.3 % slower on 8192^3, the extra branch and vote sit on
+// the MMA thread's critical path, with no difference in joules per TFLOP, so it was dropped.)
 template <bool CLUSTER_ACQUIRE = false>
-__device__ __forceinline__ bool wait_one(bool leader, uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
+__device__ __forceinline__ bool wait_all(uint32_t bar, uint32_t parity, long long budget, volatile int *abort_flag,
                                          int bar_id) {
-    int ok = 1;
-    if (leader || kAllLanesPoll) {
-        const bool first = CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity);
-        if (!first) ok = wait_slow<CLUSTER_ACQUIRE>(bar, parity, budget, abort_flag, bar_id) ? 1 : 0;
-    }
-    return __all_sync(0xffffffffu, ok) != 0;
+    bool ok = CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity);
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if (!ok) ok = wait_slow<CLUSTER_ACQUIRE>(bar, parity, budget, abort_flag, bar_id);
+    return __all_sync(0xffffffffu, ok);
 }
 
-// Stream-K, the CTA that finishes a cut tile: how many CTA groups after this one hold later K parts of the
-// tile (those whose ranges begin before the tile ends), and a bounded wait until warp e of each of them has
-// stored its partial (flag == this launch's epoch; lane 0 polls and puts the flag back to zero). All lanes
-// call it; returns the number of peers, or -1 when the wait ran out or the block is aborting.
-__device__ __forceinline__ int sk_wait_peers(volatile unsigned int *sk_flags, unsigned int epoch, int group, int num_groups,
-                                          int sk_hi, int sk_tiles, int num_segs, int tile_end, int cg, int rank, int e,
-                                          long long budget, volatile int *abort_flag) {
-    int h = group + 1;
-    int lo = sk_hi;                                   // where group + 1 begins
-    while (h < num_groups && lo < tile_end) {
-        ++h;
-        lo = sk_range_begin(h, sk_tiles, num_segs, num_groups);
-    }
-    const int peers = h - group - 1;
-    int got = 1;
-    if (lane_id() == 0) {
-        const long long t0 = clock64();
-        for (int i = 1; i <= peers && got; ++i) {
-            const int peer_cta = (group + i) * cg + rank;
-            volatile unsigned int *flag = sk_flags + peer_cta * 8 + e;
-            while (*flag != epoch) {
-                __nanosleep(100);
-                if (*abort_flag) {
-                    got = 0;
-                    break;
-                }
-                if (clock64() - t0 > budget) {
-                    record_timeout(abort_flag, 800 + e, peer_cta);
-                    got = 0;
-                    break;
-                }
+// Tail split, the CTA that runs a cut tile's last K slice: a bounded wait until warp e of every CTA that ran
+// one of the tile's earlier slices has stored its partial (flag == this launch's epoch; lane 0 puts the flag
+// back to zero). slot0 is the CTA-unit slot of slice 0, the slots of the following slices are
+// slot_step apart. All lanes call it; false when the wait ran out or the block is aborting.
+__device__ __forceinline__ bool tail_wait_peers(volatile unsigned int *flags, unsigned int epoch, int slot0, int slot_step,
+                                                int peers, int e, long long budget, volatile int *abort_flag) {
+    // Every lane reads the same flag word and the loop exits on votes, so the warp stays converged for the
+    // .sync.aligned tensor-memory loads that follow.
+    const long long t0 = clock64();
+    for (int i = 0; i < peers; ++i) {
+        volatile unsigned int *flag = flags + (slot0 + i * slot_step) * 8 + e;
+        for (;;) {
+            const bool there = (*flag == epoch);
+            if (__all_sync(0xffffffffu, there)) break;
+            __nanosleep(100);
+            const bool aborting = (*abort_flag != 0);
+            const bool late = clock64() - t0 > budget;
+            if (__any_sync(0xffffffffu, aborting || late)) {
+                if (lane_id() == 0 && !aborting) record_timeout(abort_flag, 800 + e, slot0 + i * slot_step);
+                __syncwarp();
+                return false;
             }
-            if (got) *flag = 0u;                      // ready for the next launch that is dealt this flag set
         }
-        __threadfence();
+        __syncwarp();
+        if (lane_id() == 0) *flag = 0u;               // ready for the next launch that is dealt this flag set
     }
-    got = __shfl_sync(0xffffffffu, got, 0);
-    return got ? peers : -1;
+    __threadfence();
+    return true;
 }
 
 template <int CG>
@@ -183,7 +164,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     Cfg c;
     c.num_units = g.num_units; c.num_tiles = g.num_tiles; c.tiles_m = g.tiles_m; c.tiles_n = g.tiles_n;
     c.tile_group_m = g.tile_group_m; c.tile_m = g.tile_m; c.tile_n = g.tile_n; c.num_segs = g.num_segs;
-    c.split_k = g.split_k; c.sk_tiles = g.sk_tiles; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
+    c.split_k = g.split_k; c.tail_tiles = g.tail_tiles; c.tail_slices = g.tail_slices; c.kblocks = g.kblocks; c.stages = g.stages; c.stage_bytes = g.stage_bytes;
     c.a_stage_bytes = g.a_stage_bytes; c.cta_rows_a = g.cta_rows_a; c.a_box_rows = g.a_box_rows;
     c.a_boxes = g.a_boxes; c.a_priv = g.a_priv; c.a_bars = g.a_bars; c.chunk_n = g.chunk_n; c.b_priv = g.b_priv;
     c.b_res_chunks = g.b_res_chunks; c.b_bars = g.b_bars; c.acc_cols = g.acc_cols; c.mma_m = g.mma_m;
@@ -201,11 +182,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage); bits 2 and 3: the
     // epilogue withholds its "slice staged" / "slice read" arrivals of the cluster reduce, so that those
     // bounded waits run out and the launch ends with a DEVICE_TIMEOUT record (tests of the failure path); bit 4:
-    // the same for the "partial stored" flags of the stream-K schedule
+    // the same for the "partial stored" flags of the tail split
     const int dbg = g.debug_flags;
     const float g_alpha = g.alpha, g_beta = g.beta;
-    volatile unsigned int *const sk_flags = &g_sk_flags[g.sk_set % kSkSets][0][0];
-    const unsigned int sk_epoch = g.sk_epoch;
+    volatile unsigned int *const tail_flags = &g_tail_flags[g.tail_set % kTailSets][0][0];
+    const unsigned int tail_epoch = g.tail_epoch;
     const float *const gC = g.C;
     float *const gD = g.D;
     float *const g_partial = g.partial;
@@ -243,11 +224,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     }
     const int group = static_cast<int>(blockIdx.x) / (CG * c.cl_split);   // CTAs that share a tile share a group
     const int num_groups = static_cast<int>(gridDim.x) / (CG * c.cl_split);
-    c.sk_lo = c.sk_hi = 0;
-    if (c.sk_tiles > 0) {
-        c.sk_lo = sk_range_begin(group, c.sk_tiles, c.num_segs, num_groups);
-        c.sk_hi = sk_range_begin(group + 1, c.sk_tiles, c.num_segs, num_groups);
-    }
 
     // Barrier map, per stage: [full A x a_bars][full B x b_bars][empty A][pad x (a_bars-1)][empty B x b_bars];
     // after the stages: tmem_full[2], tmem_empty[2].
@@ -367,7 +343,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 ++tile_no;
                 for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
                     const long long tw = PROF ? clock64() : 0;
-                    ok = wait_one(issuer, sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
+                    ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
                     if (PROF) t_wait += clock64() - tw;
                     if (!ok) break;
                     if (arm) mbar_arrive_expect_tx(sb, (dbg & 2) ? 0u : my_bytes);
@@ -430,7 +406,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const uint32_t acc = tl & 1u;
                 const uint32_t aph = (tl >> 1) & 1u;
                 const long long ta = PROF ? clock64() : 0;
-                ok = wait_one(issuer, tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
                 if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -438,7 +414,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 uint32_t accumulate = 0;
                 for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
                     const long long tf = PROF ? clock64() : 0;
-                    ok = wait_one(issuer, sb, ph, c.budget, abort_flag, 400 + s);
+                    ok = wait_all(sb, ph, c.budget, abort_flag, 400 + s);
                     if (PROF) t_full += clock64() - tf;
                     if (!ok) break;
                     if (it == 0 && lane == 0) B200_TL(20);
@@ -516,7 +492,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
                     if (do_a) {
                         const long long tw = PROF ? clock64() : 0;
-                        ok = wait_one(issuer, sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
+                        ok = wait_all(sb + empty_a_off, ph ^ 1u, c.budget, abort_flag, 100 + s);
                         if (PROF) t_wait += clock64() - tw;
                         if (!ok) break;
                         uint32_t box_dst = stage;
@@ -554,7 +530,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         for (int t = 0; t < c.b_bars; ++t) {
                             if (!(merged && do_a)) {  // merged + same warp: the stage was acquired above
                                 const long long tw = PROF ? clock64() : 0;
-                                ok = wait_one(issuer, sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u, c.budget, abort_flag,
+                                ok = wait_all(sb + (merged ? empty_a_off : empty_b_off + 8u * t), ph ^ 1u, c.budget, abort_flag,
                                               200 + s * 32 + t);
                                 if (PROF) t_wait += clock64() - tw;
                                 if (!ok) break;
@@ -631,7 +607,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const uint32_t acc = tl & 1u;
                 const uint32_t aph = (tl >> 1) & 1u;
                 const long long ta = PROF ? clock64() : 0;
-                ok = wait_one(issuer, tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
                 if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -639,7 +615,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 uint32_t later_seg = 0;
                 for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
                     const long long tf = PROF ? clock64() : 0;
-                    for (int j = 0; ok && j < c.a_bars; ++j) ok = wait_one(issuer, sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j);
+                    for (int j = 0; ok && j < c.a_bars; ++j) ok = wait_all(sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j);
                     if (PROF) t_full += clock64() - tf;
                     if (!ok) break;
                     uint64_t sub_desc = b_desc;
@@ -647,7 +623,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     for (int t = 0; t < c.b_bars; ++t) {
                         if (!merged) {
                             const long long tb = PROF ? clock64() : 0;
-                            ok = wait_one(issuer, sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
+                            ok = wait_all(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
                             if (PROF) t_full += clock64() - tb;
                             if (!ok) break;
                         }
@@ -730,7 +706,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint32_t acc = tl & 1u;
             const uint32_t aph = (tl >> 1) & 1u;
             const long long te = prof ? clock64() : 0;
-            ok = wait_one(lane == 0, tmem_full0 + 8u * acc, aph, c.budget, abort_flag, 600 + static_cast<int>(acc));
+            ok = wait_all(tmem_full0 + 8u * acc, aph, c.budget, abort_flag, 600 + static_cast<int>(acc));
             if (prof) t_tfull += clock64() - te;
             if (!ok) break;
             if (tl == 0 && e == 0 && lane == 0) B200_TL(22);
@@ -750,29 +726,26 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const float a_u = alpha;
             const float b_u = beta;
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
-            // Stream-K pieces. The workspace holds one partial per CTA: per 32-lane quarter and 32-column chunk
-            // eight groups of [32 lanes] float4 (lane l keeps its columns 4j .. 4j+3 in group j), so a warp
+            // Tail split. The workspace holds one partial per CTA and slice unit: per 32-lane quarter and 32-column
+            // chunk eight groups of [32 lanes] float4 (lane l keeps its columns 4j .. 4j+3 in group j), so a warp
             // stores and re-loads 512 consecutive bytes per instruction, and warp e of the finishing CTA reads
-            // exactly what warp e of a peer wrote. A piece of kind 1 first waits (bounded) until the CTAs that
-            // hold the tile's later K parts have stored theirs: those are the groups after this one whose
-            // ranges begin inside this tile.
-            int sk_peers = 0;
-            if (w.kind == 1) {
-                sk_peers = sk_wait_peers(sk_flags, sk_epoch, group, num_groups, c.sk_hi, c.sk_tiles, c.num_segs, w.tile_end, CG,
-                                         static_cast<int>(rank), e, c.budget, abort_flag);
-                if (sk_peers < 0) {
-                    ok = false;
-                    break;
-                }
+            // exactly what warp e of a peer wrote. The CTA that runs a tile's last slice (kind 1) first waits
+            // (bounded) until the CTAs of the earlier slices have stored theirs.
+            const int tail_peers = (w.kind == 1) ? c.tail_slices - 1 : 0;
+            const int tail_slot = w.slot * CG + static_cast<int>(rank);     // in CTA units
+            const int tail_step = c.tail_tiles * CG;                        // from one slice of a tile to the next
+            if (w.kind == 1 && !tail_wait_peers(tail_flags, tail_epoch, tail_slot, tail_step, tail_peers, e, c.budget, abort_flag)) {
+                ok = false;
+                break;
             }
-            const uint32_t sk_chunks = static_cast<uint32_t>(c.tile_n + 31) >> 5;
-            const uint32_t sk_slot = sk_chunks * 1024u;                                    // float4 per CTA (offsets fit 32 bits)
-            const uint32_t sk_lane = static_cast<uint32_t>(q) * sk_chunks * 256u + static_cast<uint32_t>(lane);
+            const uint32_t tail_chunks = static_cast<uint32_t>(c.tile_n + 31) >> 5;
+            const uint32_t tail_slot4 = tail_chunks * 1024u;                                // float4 per slot (offsets fit 32 bits)
+            const uint32_t tail_lane = static_cast<uint32_t>(q) * tail_chunks * 256u + static_cast<uint32_t>(lane);
             if (c.cl_split > 1) {
                 // ---- K slices of this tile live in the CTAs of the cluster (transposed drain only).
                 // A: raw accumulator -> this CTA's shared memory as [column][row]; tell every CTA.
                 const uint32_t pbuf = base + static_cast<uint32_t>(off_epi);
-                ok = wait_one<true>(lane == 0, part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
+                ok = wait_all<true>(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
                 if (!ok) break;
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                     uint32_t r[32];
@@ -810,7 +783,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (e == 0 && lane == 0) B200_TL(29);
                 // B: when all slices are staged, this CTA sums its share of the tile's columns over the
                 // cluster in slice order (the order of the workspace form) and writes D.
-                ok = wait_one<true>(lane == 0, part_full, tl & 1u, c.budget, abort_flag, 701);
+                ok = wait_all<true>(part_full, tl & 1u, c.budget, abort_flag, 701);
                 if (!ok) break;
                 if (e == 0 && lane == 0) B200_TL(30);
                 const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
@@ -943,26 +916,35 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (e == 0 && lane == 0) B200_TL(18);
                 const int nvec = wide ? 8 : 4;
                 if (w.kind == 2) {
-                    // raw partial of this chunk into this CTA's slot (a 16-column last chunk stores its zero padding too)
-                    float4 *dst = reinterpret_cast<float4 *>(g_partial) + (blockIdx.x * sk_slot + sk_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
+                    // raw partial of this chunk into this unit's slot (a 16-column last chunk stores its zero padding too)
+                    float4 *dst = reinterpret_cast<float4 *>(g_partial) +
+                                  (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         dst[j * 32] = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
                     continue;
                 }
-                for (int i = 1; i <= sk_peers; ++i) {
-                    // the peers' partials of this chunk, added in ascending K order; .cg: written by other SMs
+                if (tail_peers > 0) {
+                    // the earlier slices' partials of this chunk, summed in ascending K order, then this (last) slice;
+                    // .cg: they were written by other SMs
                     const float4 *src = reinterpret_cast<const float4 *>(g_partial) +
-                                        (static_cast<uint32_t>((group + i) * CG + static_cast<int>(rank)) * sk_slot + sk_lane +
-                                         static_cast<uint32_t>(c0 >> 5) * 256u);
+                                        (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
+                    const uint32_t step4 = static_cast<uint32_t>(tail_step) * tail_slot4;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const float4 v = __ldcg(src + j * 32);
-                        r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + v.x);
-                        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
-                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
-                        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                        float4 v = __ldcg(src + j * 32);
+                        for (int i = 1; i < tail_peers; ++i) {
+                            const float4 u = __ldcg(src + i * step4 + j * 32);
+                            v.x += u.x;
+                            v.y += u.y;
+                            v.z += u.z;
+                            v.w += u.w;
+                        }
+                        r[4 * j + 0] = __float_as_uint(v.x + __uint_as_float(r[4 * j + 0]));
+                        r[4 * j + 1] = __float_as_uint(v.y + __uint_as_float(r[4 * j + 1]));
+                        r[4 * j + 2] = __float_as_uint(v.z + __uint_as_float(r[4 * j + 2]));
+                        r[4 * j + 3] = __float_as_uint(v.w + __uint_as_float(r[4 * j + 3]));
                     }
                 }
                 if (swap_ab) {
@@ -1103,7 +1085,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 __syncwarp();
                 if (lane == 0 && !(dbg & 16)) {
                     __threadfence();
-                    *(sk_flags + static_cast<int>(blockIdx.x) * 8 + e) = sk_epoch;
+                    *(tail_flags + tail_slot * 8 + e) = tail_epoch;
                 }
             }
             // accumulator slot drained: hand it back to the MMA thread
@@ -1362,7 +1344,6 @@ int max_active_clusters(KernelFn fn, const cudaLaunchConfig_t &cfg, int cluster)
 }  // namespace
 
 int profile_slots() { return kProfSlots; }
-int stream_k_max_ctas() { return kSkMaxCtas; }
 
 int prepare_kernels() {
     for (int cg = 1; cg <= 2; ++cg)
@@ -1441,10 +1422,10 @@ int read_device_status(int out[4], cudaStream_t stream) {
         const int zero[4] = {0, 0, 0, 0};
         e = cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero));
         if (e != cudaSuccess) return static_cast<int>(e);
-        // a launch that timed out may have left stream-K flags raised that nobody consumed
+        // a launch that timed out may have left tail-split flags raised that nobody consumed
         void *flags = nullptr;
-        e = cudaGetSymbolAddress(&flags, g_sk_flags);
-        if (e == cudaSuccess) e = cudaMemset(flags, 0, sizeof(unsigned int) * kSkSets * kSkMaxCtas * 8);
+        e = cudaGetSymbolAddress(&flags, g_tail_flags);
+        if (e == cudaSuccess) e = cudaMemset(flags, 0, sizeof(unsigned int) * kTailSets * kTailMaxSlots * 8);
         if (e != cudaSuccess) return static_cast<int>(e);
     }
     for (int i = 0; i < 4; ++i) out[i] = host[i];

@@ -15,16 +15,16 @@ struct alignas(64) GemmArgs {
     CUtensorMap map_d;  // D   as {N, M}  fp32, box {32, 32}, 128-byte swizzle (TMA-store epilogue)
     const float *C;
     float *D;
-    float *partial;     // split-K workspace: split_k slabs of M x N fp32; stream-K: one partial tile per CTA
+    float *partial;     // split-K workspace: split_k slabs of M x N fp32; tail split: one partial per CTA and slice unit
     float alpha, beta;
     int M, N, K;
     int ld_cd;          // row pitch of C and D in elements (N unless D is a column block of a wider matrix)
     int tiles_m, tiles_n, num_tiles, num_units;
     int num_segs;       // K / seg_k
     int split_k;
-    int sk_tiles;       // > 0: stream-K schedule (plan.h); the first sk_tiles tiles are cut by K iterations over the CTAs
-    int sk_set;         // which set of the fix-up flags this launch uses
-    unsigned int sk_epoch;  // the value its flags carry (never 0)
+    int tail_tiles, tail_slices;  // tail split (plan.h): the first tail_tiles tiles are cut into tail_slices K slices; 0 = off
+    int tail_set;                 // which set of the fix-up flags this launch uses
+    unsigned int tail_epoch;      // the value its flags carry (never 0)
     // plan
     int tile_m, tile_n, cta_rows_a, mma_m;
     int kblocks, stages, tile_group_m;
@@ -70,7 +70,6 @@ int launch_push_reduce(const float *slots, const int *flags, int world, int epoc
 // Second step of split-K when the rows go to their owner GPUs instead of a local D.
 int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int split_k, float *const *slots, int *const *flags,
                               unsigned int *done, int world, int rank, int epoch, cudaStream_t stream);
-int stream_k_max_ctas();  // largest grid the stream-K flags cover
 // Remembers the cudaError_t behind a B200_CUDA_ERROR return for b200_last_cuda_error(); returns B200_CUDA_ERROR.
 int record_cuda_error(int cuda_error);
 int prepare_kernels();  // opt-in shared memory size; once per device

@@ -53,37 +53,53 @@ struct Plan {
                                           //    in distributed shared memory (no workspace, no second kernel)
 };
 
-// Stream-K schedule of the tiles that do not fill a wave of the persistent grid (tail_split = 1).
-// T tiles on S slots (CTAs, or CTA pairs) leave r = T mod S tiles for a last, partly idle wave. Instead,
-// a "stream-K region" of sk_tiles tiles is processed first and cut by K iterations, not by tiles: its
-// sk_tiles * num_segs iterations (one iteration = one K segment of one tile) are dealt out in S equal
-// contiguous ranges, one per slot, so a slot's range covers the end of one tile, possibly whole tiles,
-// and the beginning of another. The remaining T - sk_tiles tiles (a multiple of S) follow as whole
-// tiles. A tile cut between slots is finished by the slot that holds its first K iterations (it comes
-// last in that slot's range, when the others are done): the other slots store their raw partial
-// accumulators in the workspace and raise a flag, the finishing slot adds them in ascending K order.
-// sk_tiles == 0 means "off / nothing to gain".
-struct StreamK {
-    int sk_tiles = 0;        // tiles of the stream-K region (the first sk_tiles tiles in tile order)
-    int64_t slot_bytes = 0;  // one partial per CTA: 128 lanes x ceil(tile_n / 32) chunks of 32 columns, fp32
+// Tail split (tail_split = 1): the tiles that do not fill a wave of the persistent grid are cut along K.
+// T tiles on S slots (CTAs, or CTA pairs) leave r = T mod S tiles for a last, partly idle wave that still
+// costs a whole tile time. Instead those r tiles are cut into s equal K slices each; the r * s slice units
+// are dealt to the slots in rounds of S, slice-major (all first slices, then all second slices, ...), and
+// run FIRST, before the whole tiles. A round costs 1/s of a tile time, so the tail costs
+// ceil(r * s / S) / s tile times instead of 1. Slice-major rounds keep the slots in step along K: the CTAs
+// that run at the same time read the same K range of neighbouring tiles, so operand panels are shared in
+// L2 as in a wave of whole tiles. (A plain stream-K cut - one contiguous range of K iterations per slot -
+// balances better on paper but puts every slot at a different K offset: nothing is shared, the phase turns
+// DRAM-bound and the gain is lost; measured.) The slot that runs a tile's last slice finishes the tile: the
+// other slices store their raw fp32 accumulators in the workspace and raise a flag, the finisher adds them
+// in ascending K order before the usual alpha / beta / store. Running the tail first hides that fix-up
+// behind the whole tiles that follow. tiles == 0 means "off / nothing to gain".
+struct TailPlan {
+    int tiles = 0;           // r: the first r tiles in tile order are cut
+    int slices = 1;          // s: K slices per cut tile
+    int64_t slot_bytes = 0;  // one partial per CTA and slice unit: 128 lanes x ceil(tile_n / 32) chunks of 32 columns, fp32
+    int64_t slots = 0;       // partials in CTA units: r * (s - 1) * cta_group
 };
 
-inline StreamK make_stream_k(int enabled, int64_t tiles, int slots, int64_t num_segs, int split_k, int tile_n) {
-    StreamK k;
-    if (!enabled || split_k > 1 || slots < 2 || tiles <= 0) return k;
+constexpr int kTailMaxSlices = 8;
+constexpr int kTailMaxSlots = 1040;   // flags per set the library keeps: covers 148 one-CTA tiles x 7 slices
+
+inline TailPlan make_tail_plan(int enabled, int64_t tiles, int slots, int64_t num_segs, int split_k, int tile_n, int cta_group) {
+    TailPlan t;
+    if (!enabled || split_k > 1 || slots < 2 || tiles <= 0) return t;
     const int64_t r = tiles % slots;
-    if (r == 0) return k;
-    // The region: the r left-over tiles when they are at least half a wave; otherwise one more whole wave
-    // is folded in, so that a tile is cut between two or three slots rather than among many (every peer of a
-    // finishing slot costs it one more partial tile to read back).
-    int64_t sk = r;
-    if (2 * r < slots) sk = (tiles >= r + slots) ? r + slots : r;
-    if (4 * sk < slots) return k;                          // a tile would be cut among more than five slots
-    const int64_t iters = sk * num_segs;
-    if (iters >= (int64_t(1) << 31) || iters / slots < 4) return k;   // 32-bit iteration counters; ranges of >= 4 segments
-    k.sk_tiles = static_cast<int>(sk);
-    k.slot_bytes = int64_t((tile_n + 31) / 32) * 4 * 32 * 32 * 4;
-    return k;
+    if (r == 0) return t;
+    // cost of the tail in tile times for s slices, plus a small charge per extra slice (partials to write and read back)
+    double best = 1.0;
+    int best_s = 1;
+    for (int s = 2; s <= kTailMaxSlices; ++s) {
+        if (num_segs / s < 4) break;                                   // slices of at least four K segments
+        if (r * (s - 1) * cta_group > kTailMaxSlots) break;
+        const double cost = double((r * s + slots - 1) / slots) / double(s) + 0.01 * (s - 1);
+        if (cost < best - 1e-9) {
+            best = cost;
+            best_s = s;
+        }
+    }
+    const int64_t waves = (tiles + slots - 1) / slots;
+    if (best_s == 1 || (1.0 - best) / double(waves) < 0.02) return t;   // under 2 % of the launch: not worth the traffic
+    t.tiles = static_cast<int>(r);
+    t.slices = best_s;
+    t.slot_bytes = int64_t((tile_n + 31) / 32) * 4 * 32 * 32 * 4;
+    t.slots = r * (best_s - 1) * cta_group;
+    return t;
 }
 
 inline int round_up(int x, int m) { return (x + m - 1) / m * m; }

@@ -20,13 +20,11 @@ B200_HD int sched_min(int a, int b) { return a < b ? a : b; }
 
 struct Unit {
     int m0, n0, slice, seg_begin, seg_end;
-    // stream-K: 0 = a whole tile (or a tile that ends up whole in this CTA), 1 = the first K iterations of a
-    // tile that other CTAs continue (this CTA finishes it: adds their partials and writes D), 2 = a later
-    // part of a tile another CTA finishes (raw accumulator to this CTA's slot of the workspace)
+    // tail split: 0 = a whole tile, 1 = the last K slice of a cut tile (this CTA finishes the tile: adds the other
+    // slices' partials and writes D), 2 = an earlier K slice (raw accumulator to slot `slot` of the workspace)
     int kind;
-    int tile_end;  // kind 1: the stream-K iteration index at which this tile ends (finds the peers)
+    int slot;      // kind 2: this unit's partial slot; kind 1: the slot of the tile's slice 0 (slice i: slot + i * tiles)
 };
-
 
 // Launch constants the role loops need, copied once from the kernel parameter into registers.
 // The parameter is __grid_constant__ and its address escapes (tensor maps), so reading a field
@@ -34,7 +32,7 @@ struct Unit {
 // those loads sat on the critical path of the single-thread producer and MMA loops.
 struct Cfg {
     int num_units, num_tiles, tiles_m, tiles_n, tile_group_m, tile_m, tile_n, num_segs, split_k;
-    int sk_tiles, sk_lo, sk_hi;  // stream-K region (tiles) and this CTA group's range of its K iterations
+    int tail_tiles, tail_slices;  // tail split: the first tail_tiles tiles are cut into tail_slices K slices each
     int kblocks, stages, stage_bytes, a_stage_bytes, cta_rows_a;
     int a_box_rows, a_boxes, a_priv, a_bars, chunk_n, b_priv, b_res_chunks, b_bars;
     int acc_cols, mma_m, epi_mode, epi_warps, M, N;
@@ -62,14 +60,14 @@ B200_HD void tile_origin(const Cfg &c, int t, Unit &w) {
     w.n0 = (in_group / group_rows) * c.tile_n;
 }
 
-// Work unit -> tile and K slice (every schedule but stream-K).
+// Work unit -> tile and K slice (every schedule but the tail split).
 B200_HD Unit decode_unit(const Cfg &c, int u) {
     // The roles that call this are single dependent instruction chains, where an integer
     // division costs on the order of a hundred cycles: the common cases avoid them.
     Unit w;
     int t;
     w.kind = 0;
-    w.tile_end = 0;
+    w.slot = 0;
     if (c.cl_split > 1) {
         t = u;
         w.slice = c.cl_rank;
@@ -91,59 +89,48 @@ B200_HD Unit decode_unit(const Cfg &c, int u) {
     return w;
 }
 
-// First stream-K iteration of CTA group g: the region's iterations dealt out in num_groups equal ranges.
-B200_HD int sk_range_begin(int g, int sk_tiles, int num_segs, int num_groups) {
-    return static_cast<int>(static_cast<long long>(g) * sk_tiles * num_segs / num_groups);
-}
-
 // The sequence of work units of one CTA group; every role of the CTA walks the same sequence.
-// Plain schedules: units group, group + num_groups, ... Stream-K: first the pieces of this group's
-// range of the region's K iterations (the end of a tile, whole tiles, the beginning of a tile), then
+// Plain schedules: units group, group + num_groups, ... Tail split: first this group's K-slice units of the
+// cut tiles (unit p = slice * tail_tiles + tile, dealt out in rounds: p = group, group + num_groups, ...), then
 // whole tiles of the rest, one per wave.
 struct Walk {
-    int u;                           // plain schedules: next unit
-    int sk_pos, sk_tile, sk_first;   // stream-K: next iteration; the tile it belongs to; that tile's first iteration
-    int dp_tile;                     // next whole tile after the region
+    int u;         // plain schedules: next unit; tail split: next slice unit
+    int dp_tile;   // tail split: next whole tile
 };
 
 B200_HD void walk_init(const Cfg &c, Walk &k, int group) {
     k.u = group;
-    k.sk_pos = c.sk_lo;
-    k.sk_tile = c.sk_tiles > 0 ? c.sk_lo / c.num_segs : 0;
-    k.sk_first = k.sk_tile * c.num_segs;
-    k.dp_tile = c.sk_tiles + group;
+    k.dp_tile = c.tail_tiles + group;
 }
 
 B200_HD bool walk_next(const Cfg &c, Walk &k, int num_groups, Unit &w) {
-    if (c.sk_tiles == 0) {
+    if (c.tail_tiles == 0) {
         if (k.u >= c.num_units) return false;
         w = decode_unit(c, k.u);
         k.u += num_groups;
         return true;
     }
     int t;
-    if (k.sk_pos < c.sk_hi) {
-        t = k.sk_tile;
-        const int tile_end = k.sk_first + c.num_segs;
-        const int end = sched_min(c.sk_hi, tile_end);
-        w.seg_begin = k.sk_pos - k.sk_first;
-        w.seg_end = end - k.sk_first;
-        w.kind = w.seg_begin > 0 ? 2 : (end < tile_end ? 1 : 0);
-        w.tile_end = tile_end;
-        k.sk_pos = end;
-        k.sk_tile += 1;
-        k.sk_first = tile_end;
+    if (k.u < c.tail_tiles * c.tail_slices) {
+        const int sl = k.u / c.tail_tiles;
+        t = k.u - sl * c.tail_tiles;
+        w.slice = sl;
+        w.seg_begin = static_cast<int>(static_cast<unsigned>(sl) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.tail_slices));
+        w.seg_end = static_cast<int>(static_cast<unsigned>(sl + 1) * static_cast<unsigned>(c.num_segs) / static_cast<unsigned>(c.tail_slices));
+        w.kind = (sl == c.tail_slices - 1) ? 1 : 2;
+        w.slot = (w.kind == 2) ? k.u : t;
+        k.u += num_groups;
     } else if (k.dp_tile < c.num_tiles) {
         t = k.dp_tile;
         k.dp_tile += num_groups;
+        w.slice = 0;
         w.seg_begin = 0;
         w.seg_end = c.num_segs;
         w.kind = 0;
-        w.tile_end = 0;
+        w.slot = 0;
     } else {
         return false;
     }
-    w.slice = 0;
     tile_origin(c, t, w);
     return true;
 }

@@ -84,22 +84,24 @@ typedef struct b200_gemm_params {
                        "slice staged" / "slice read" arrivals between the CTAs of a cluster, so those
                        bounded waits expire: the launch returns normally with a B200_DEVICE_TIMEOUT
                        record (barrier ids 701 / 700) and an unfinished D; bit 4 (with tail_split) withholds the
-                       "partial stored" flags of the stream-K schedule in the same way (wait ids 800 + warp);
+                       "partial stored" flags of its fix-up in the same way (wait ids 800 + warp);
                        for tests of those paths */
     int k_order;    /* 0 = every tile sums K ascending; 1 = serpentine: every other tile of a CTA walks K downwards,
                        so consecutive waves meet their shared operand panels while they are still in L2.
                        Changes the fp32 summation order of those tiles (not the tolerance) */
-    int tail_split; /* 1 = stream-K schedule for the tiles that do not fill a wave of the persistent grid: a region
-                       of tiles (the left-over ones, plus one whole wave when they are few) is cut by K
-                       iterations into equal contiguous ranges, one per CTA (pair), and processed first; a
-                       tile cut between CTAs is finished inside the kernel by the CTA that holds its first K
-                       iterations, which adds the others' fp32 partials (ascending K, deterministic) from the
-                       workspace before the usual alpha / beta / store. Successor of the reference's
-                       persistent tile loop (matmul_shmem_tc_async.cu:251-252), which leaves SMs idle in
-                       the last wave. Takes effect only when the call is given b200_gemm_workspace_bytes
-                       of workspace (one partial tile per CTA); without it the plain schedule runs. At most
-                       32 such launches may be in flight on a device at once (they share flag sets inside
-                       the library); launches on one stream never are. 0 = off */
+    int tail_split; /* 1 = the tiles that do not fill a wave of the persistent grid (T tiles on S CTAs or CTA pairs
+                       leave r = T mod S for a last, partly idle wave) are cut into s equal K slices each; the
+                       r * s slice units run first, dealt to the CTAs in rounds, slice-major, so that CTAs
+                       running together stay in step along K and share operand panels in L2; the tail then
+                       costs ceil(r * s / S) / s tile times instead of one (s <= 8 is chosen by that cost; off
+                       when under 2 % of the launch would be gained). A cut tile is finished inside the kernel
+                       by the CTA that runs its last slice, which adds the other slices' fp32 partials
+                       (ascending K, deterministic) from the workspace before the usual alpha / beta / store:
+                       no second kernel. Successor of the reference's persistent tile loop
+                       (matmul_shmem_tc_async.cu:251-252), which leaves SMs idle in the last wave. Takes effect
+                       only when the call is given b200_gemm_workspace_bytes of workspace; without it the plain
+                       schedule runs. At most 16 such launches may be in flight on a device at once (they share
+                       flag sets inside the library); launches on one stream never are. 0 = off */
     int swap_ab;    /* 1 = operand roles swapped inside the kernel for skinny M (decode shapes): the rows of B^T feed
                        the 64/128-row side of the MMA and the few rows of A its N side, so a stage holds
                        tile_n rows of weights and only tile_m rows of activations, and the accumulator is
@@ -136,16 +138,16 @@ int b200_gemm_validate(int64_t M, int64_t N, int64_t K, int dtype, const b200_ge
 int64_t b200_gemm_smem_bytes(int dtype, const b200_gemm_params *p);
 
 /* Bytes of caller-provided device workspace for the configuration: what split_k > 1 (without
- * cluster_reduce) needs, or what tail_split = 1 can use on this shape (0 when the tiles fill their
- * waves); 0 otherwise. With num_sms = 0 the grid follows the current device (148 SMs assumed
+ * cluster_reduce) needs, or what tail_split = 1 can use on this shape (0 when nothing would be cut);
+ * 0 otherwise. With num_sms = 0 the grid follows the current device (148 SMs assumed
  * when there is none). */
 int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_gemm_params *p);
 
 /* Lists the work units CTA group `group` (a CTA, or a two-CTA pair) of a launch on num_sms SMs walks, in
  * order: units[6*i .. 6*i+5] = {first row, first column of the tile (of the transposed problem with
  * swap_ab), first K segment, end K segment, kind, K slice}; kind 0 = the CTA finishes the tile alone,
- * 1 = it holds the tile's first K segments and finishes it with other CTAs' partials (stream-K),
- * 2 = a later K part whose partial another CTA adds. Host arithmetic only, the same code the kernel runs:
+ * 1 = the last K slice of a cut tile: the CTA finishes the tile with the other slices' partials (tail_split),
+ * 2 = an earlier K slice, whose partial the finishing CTA adds. Host arithmetic only, the same code the kernel runs:
  * for tests and tuners (in the reference the schedule is the loop `for (tile = blockIdx.x; tile < tiles;
  * tile += gridDim.x)`, matmul_shmem_tc_async.cu:251-252). Returns the number of units (which may exceed
  * max_units; only that many are written), -1 for an invalid configuration or group; *num_groups_out
@@ -168,8 +170,8 @@ int b200_gemm_bf16(const void *A, const void *Bt, const float *C, float *D, floa
 /* The same product with fp16 C and D (m x n row-major halves): stands in for the reference's DT = DT_ACC = half
  * instances of the launchers above (matmul_shmem_tc_async.cu:411-478 instantiate both). Accumulation stays
  * fp32 in tensor memory and the result is rounded to fp16 once (the reference's half instances accumulate in
- * half), so it is at least as close to the exact product. Needs no workspace (the stream-K schedule of
- * tail_split does not engage without one): configurations whose K slices meet in a workspace (split_k > 1
+ * half), so it is at least as close to the exact product. Needs no workspace (tail_split does not engage
+ * without one): configurations whose K slices meet in a workspace (split_k > 1
  * without cluster_reduce) are B200_INVALID_CONFIG here. */
 int b200_gemm_f16_out_f16(const void *A, const void *Bt, const void *C, void *D, float alpha, float beta, int64_t M,
                           int64_t N, int64_t K, const b200_gemm_params *p, void *stream);

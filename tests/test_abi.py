@@ -184,65 +184,70 @@ def _coverage(pkg, M, N, K, p, num_sms):
     return tiles, groups
 
 
-def test_stream_k_schedule_covers_every_k_segment_once(pkg):
-    """tail_split = 1 (stream-K): whatever the shape, every K segment of every tile is computed by exactly one
-    CTA group; a tile cut between groups has one finishing piece (kind 1, from segment 0) in the lowest group and
-    its later parts (kind 2) in the groups right after it, each the first unit of its group; whole tiles are kind 0;
-    every group does the same number of K segments to within one tile's worth of rounding."""
+def test_tail_split_schedule_covers_every_k_segment_once(pkg):
+    """tail_split = 1: whatever the shape, every K segment of every tile is computed by exactly one CTA group; a cut
+    tile has s equal slices, the last one of kind 1 (its CTA finishes the tile), the others of kind 2; the slice
+    units come first in every group's walk, slice-major in rounds; whole tiles are kind 0; and the launch gets
+    shorter by what the plan promises."""
     pair = dict(tile_m=256, tile_n=256, cta_group=2, bar_step_rows_a=256, bar_step_rows_b=256, num_stages=6, tail_split=1)
     one = dict(tile_m=128, tile_n=128, tail_split=1)
-    cases = [(4096, 4096, 4096, pair, 148), (8192, 8192, 8192, pair, 148), (1024, 8192, 8192, pair, 148), (2048, 2048, 262144, pair, 148),
-             (128 * 3, 128 * 50, 1024, one, 148), (1000, 1000, 520, one, 148), (2048, 2048, 2048, pair, 148), (640, 896, 4096, one, 20),
-             (4096, 4096, 4096, dict(pair, num_sms=132), 132), (256 * 74, 256, 4096, pair, 148), (300, 520, 2048, dict(one, tile_n=64), 40)]
-    engaged = 0
-    for M, N, K, ov, sms in cases:
+    cases = [  # M, N, K, overrides, SMs, expected (cut tiles, slices) or None when nothing is gained
+        (4096, 4096, 4096, pair, 148, (34, 2)),            # 256 tiles on 74 pairs: 34 left, two halves each -> 3.5 instead of 4 tile times
+        (1024, 8192, 8192, pair, 148, (54, 4)),            # 128 tiles: 54 left, quarters in 3 rounds -> 1.75 instead of 2
+        (8192, 8192, 8192, pair, 148, None),               # 62 left of 74: 7 slices would save 1 % of 14 waves
+        (2048, 2048, 262144, pair, 148, (64, 8)),          # 64 tiles on 74 pairs: eighths in 7 rounds -> 0.875 of a tile time
+        (128 * 3, 128 * 50, 1024, one, 148, (2, 4)),       # 150 tiles on 148: 2 left, 16 K segments -> at most 4 slices of 4
+        (640, 896, 4096, one, 20, (15, 4)),                # 35 tiles on 20 CTAs: 15 left, quarters in 3 rounds
+        (256 * 74, 256, 4096, pair, 148, None),            # a full wave
+        (300, 520, 2048, dict(one, tile_n=64), 40, (27, 7)),  # 27 tiles on 40 CTAs: sevenths in 5 rounds -> 0.71
+    ]
+    for M, N, K, ov, sms, want in cases:
         p = P(pkg, **dict(ov, num_sms=sms))
         assert pkg.validate(M, N, K, pkg.F16, p) == pkg.OK
         tiles, groups = _coverage(pkg, M, N, K, p, sms)
         tm, tn, segs = p.tile_m, p.tile_n, -(-K // p.segment_dim_k)
-        assert len(tiles) == -(-M // tm) * -(-N // tn), (M, N, K)
-        work = [0] * groups
-        cut = 0
+        T = -(-M // tm) * -(-N // tn)
+        assert len(tiles) == T, (M, N, K)
+        cut = {k: v for k, v in tiles.items() if len(v) > 1}
+        slices = {len(v) for v in cut.values()}
+        assert len(slices) <= 1
+        s_ = slices.pop() if slices else 1
         for (m0, n0), parts in tiles.items():
             assert m0 % tm == 0 and n0 % tn == 0 and m0 < M and n0 < N
             parts.sort()
             assert parts[0][0] == 0 and parts[-1][1] == segs, ((m0, n0), parts)
-            for (sb, se, kind, g), nxt in zip(parts, parts[1:] + [None]):
-                assert sb < se
-                work[g] += se - sb
-                if nxt is not None:
-                    assert se == nxt[0], ((m0, n0), parts)                 # no gap, no overlap
-                    assert nxt[3] == g + 1                                 # the later part belongs to the next group
+            assert all(a[1] == b[0] for a, b in zip(parts, parts[1:])), parts          # no gap, no overlap
             if len(parts) == 1:
                 assert parts[0][2] == 0
             else:
-                cut += 1
-                assert parts[0][2] == 1 and all(k == 2 for _, _, k, _ in parts[1:]), parts
-                assert len(parts) <= 6
-        for g in range(groups):                                            # a later part is always a group's first unit
+                assert [k for _, _, k, _ in parts] == [2] * (s_ - 1) + [1], parts
+                assert max(se - sb for sb, se, _, _ in parts) - min(se - sb for sb, se, _, _ in parts) <= 1
+        longest = 0.0
+        for g in range(groups):
             _, units = pkg.schedule(M, N, K, p, sms, g)
-            assert all(u[4] != 2 for u in units[1:]), (g, units)
+            kinds = [u[4] for u in units]
+            first_whole = kinds.index(0) if 0 in kinds else len(kinds)
+            assert all(k == 0 for k in kinds[first_whole:]), (g, kinds)                # slice units first, then whole tiles
+            longest = max(longest, sum(u[3] - u[2] for u in units) / segs)
         if cut:
-            engaged += 1
-            assert max(work) - min(work) <= 1, (M, N, K, min(work), max(work))   # equal shares of the K segments
-            assert pkg.workspace_bytes(M, N, K, p) == (p.num_sms or sms) * -(-tn // 32) * 16384
+            r = len(cut)
+            assert r == T % groups
+            assert abs(longest - (T // groups + -(-r * s_ // groups) / s_)) < 0.06 and longest < -(-T // groups) - 0.02   # slices differ by one K segment
+            assert pkg.workspace_bytes(M, N, K, p) == r * (s_ - 1) * p.cta_group * -(-tn // 32) * 16384
         else:
+            assert longest == -(-T // groups)
             assert pkg.workspace_bytes(M, N, K, p) == 0
         off, _ = _coverage(pkg, M, N, K, P(pkg, **dict(ov, num_sms=sms, tail_split=0)), sms)
         assert all(len(v) == 1 and v[0][2] == 0 for v in off.values()) and set(off) == set(tiles)
-    assert engaged >= 7
-    # 256 tiles on 74 pairs: 34 left over, fewer than half a wave, so one whole wave joins the region (108 tiles, 2 waves of whole tiles follow)
-    tiles, groups = _coverage(pkg, 4096, 4096, 4096, P(pkg, **pair), 148)
-    assert groups == 74 and sum(1 for v in tiles.values() if len(v) > 1) == 72   # 73 inner range boundaries, one falls on a tile edge
-    # a full last wave leaves nothing to cut; one K segment cannot be cut
-    assert pkg.workspace_bytes(256 * 74, 256, 4096, P(pkg, **pair)) == 0
+        assert ((len(cut), s_) if cut else None) == want, (M, N, K, sms, len(cut), s_)
+    # one K segment cannot be cut
     assert pkg.workspace_bytes(128 * 3, 128 * 50, 64, P(pkg, **one)) == 0
     with pytest.raises(ValueError):
         pkg.schedule(4096, 4096, 4096, P(pkg, **pair), 148, 74)
 
 
 def test_plain_and_split_k_schedules(pkg):
-    """Without stream-K: group g takes units g, g + groups, ...; split_k slices are separate units of the same tile;
+    """Without the tail split: group g takes units g, g + groups, ...; split_k slices are separate units of the same tile;
     the tiles follow the reference's grouped order (tile_group_m tile rows column-major inside a group,
     matmul_shmem_tc_async_opt_port_0.cu:201-210)."""
     p = P(pkg, tile_group_m=2, num_sms=4)
@@ -273,7 +278,7 @@ def test_status_strings(pkg):
 
 def test_defaults_are_valid_everywhere_and_need_no_workspace(pkg):
     """b200_gemm_default_params (and its plain twin) over a grid of shapes: always a valid configuration for the
-    shape, never one that needs a caller workspace (the stream-K schedule of tail_split only uses one when it is
+    shape, never one that needs a caller workspace (tail_split only uses one when it is
     given; K slices that must meet in a workspace are never a default), swapped forms only where the activations
     are few."""
     import itertools

@@ -235,7 +235,7 @@ def test_cuda_graph_capture_and_overlapped_launch(pkg, cuda, oracle):
     torch = cuda
     cases = [(16, 1536, 2048, pkg.BF16, dict()), (300, 512, 1024, pkg.F16, dict()), (64, 768, 4096, pkg.BF16, dict(split_k=3)),
              (16, 1024, 8192, pkg.BF16, dict(swap_ab=1, tile_m=16, split_k=4, cluster_reduce=1)), (520, 1024, 512, pkg.F16, dict(tile_m=256, tile_n=256, cta_group=2)),
-             (640, 128 * 30, 1024, pkg.F16, dict(tile_m=128, tile_n=128, tail_split=1, num_sms=40))]     # stream-K: replays reuse the flags
+             (640, 128 * 30, 1024, pkg.F16, dict(tile_m=128, tile_n=128, tail_split=1, num_sms=40))]     # tail split: replays reuse the flags
     for overlap in (0, 1):
         prepared = []
         for i, (m, n, k, dtype, ov) in enumerate(cases):
@@ -396,21 +396,21 @@ def test_split_k(pkg, cuda, oracle):
 
 
 def test_tail_split(pkg, cuda, oracle):
-    """tail_split = 1, the stream-K schedule: the tiles that do not fill a wave are cut by K iterations over all
-    CTAs, and a cut tile is finished inside the kernel from the other CTAs' partials (workspace + flags).
-    Against the oracle on shapes where it engages, for both tile families, both drains, 4 and 8 draining warps,
-    64-row tiles, ragged edges, fewer tiles than CTAs, alpha / beta; twice in a row bit for bit (ascending-K
-    sums, no atomics); and it is what the defaults use."""
+    """tail_split = 1: the tiles that do not fill a wave are cut into K slices that run first, in rounds, and a cut
+    tile is finished inside the kernel from the other slices' partials (workspace + flags). Against the oracle
+    on shapes where it engages, for both tile families, both drains, 4 and 8 draining warps, 64-row tiles,
+    ragged edges, fewer tiles than CTAs, alpha / beta; twice in a row bit for bit (ascending-K sums, no
+    atomics); and it is what the defaults use."""
     sms = pkg.num_sms()
     cases = [  # m, n, k, overrides
         (128 * 10, 128 * (sms // 10 + 2), 1024, dict(tile_m=128, tile_n=128)),                         # 1-CTA tiles, a few left over
-        (256 * 5, 256 * (sms // 10 + 1), 2048, dict(tile_m=256, tile_n=256, cta_group=2)),             # pairs
-        (200, 128 * (sms + 3), 512, dict(tile_m=128, tile_n=128, segment_dim_k=128, num_stages=3)),    # ragged M, 3 tiles left over: one more wave joins
-        (1536, 2048, 4096, dict(tile_m=256, tile_n=256, cta_group=2)),                                 # 48 tiles on 74 pairs: every tile is cut
+        (256 * 5, 256 * (sms // 10 + 1), 2048, dict(tile_m=256, tile_n=256, cta_group=2)),             # pairs, one tile left over: eight slices
+        (200, 128 * (sms + 3), 2048, dict(tile_m=128, tile_n=128, segment_dim_k=128, num_stages=3)),   # ragged M, 3 tiles left over
+        (1536, 2048, 4096, dict(tile_m=256, tile_n=256, cta_group=2)),                                 # 48 tiles on 74 pairs: every tile is cut in three
         (640, 64 * 50, 1096, dict(tile_m=64, tile_n=64, num_sms=40)),                                  # 64-row atoms, ragged K
-        (700, 1000, 2048, dict(tile_m=128, tile_n=224, num_consumer_warps=8, num_sms=30)),             # 8 draining warps, ragged M and N, 16-column last chunk
-        (1024, 128 * 37, 1536, dict(tile_m=128, tile_n=128, epilogue=0, num_sms=100, num_producer_warps=2)),   # plain-store drain
-        (2048, 2048, 2048, dict(tile_m=256, tile_n=128, cta_group=2, num_stages=4)),                   # 128 tiles on 74 pairs
+        (700, 1000, 2048, dict(tile_m=128, tile_n=224, num_consumer_warps=8, num_sms=28)),             # 8 draining warps, ragged M and N, 16-column last chunk
+        (1024, 128 * 37, 1536, dict(tile_m=128, tile_n=128, epilogue=0, num_sms=110, num_producer_warps=2)),   # plain-store drain
+        (2048, 2048, 2048, dict(tile_m=256, tile_n=128, cta_group=2, num_stages=4)),                   # 128 tiles on 74 pairs: 54 left, quarters
     ]
     for m, n, k, ov in cases:
         p = pkg.default_params(m, n, k, pkg.F16, tail_split=1, **ov)
@@ -421,9 +421,9 @@ def test_tail_split(pkg, cuda, oracle):
         ok, msg = tolerance_ok(got, want, k, 3.0)
         assert ok, (m, n, k, ov, msg)
         again = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.5, 1.0, tail_split=1, **ov)
-        assert np.array_equal(got, again), ("stream-K result changed between two launches", m, n, k, ov)
+        assert np.array_equal(got, again), ("the result changed between two launches", m, n, k, ov)
         plain = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.5, 1.0, tail_split=0, **ov)
-        assert float(np.abs(got - plain).max()) <= 2.0 ** -10 * np.sqrt(k), (m, n, k, ov)   # cut tiles sum K in another order
+        assert float(np.abs(got - plain).max()) <= 2.0 ** -10 * np.sqrt(k) * 3.0, (m, n, k, ov)   # cut tiles sum K in another order
     # the defaults ask for it wherever it can gain, and a call without a workspace still works (plain schedule)
     m, n, k = 2048, 4096, 1024
     p = pkg.default_params(m, n, k, pkg.F16)
@@ -445,11 +445,11 @@ def test_tail_split(pkg, cuda, oracle):
     assert pkg.workspace_bytes(128 * sms, 128, 512, pkg.default_params(128 * sms, 128, 512, pkg.F16, tile_m=128, tile_n=128, tail_split=1)) == 0
 
 
-def test_stream_k_wait_for_a_partial_nobody_announces_times_out(pkg, cuda, oracle):
+def test_tail_split_wait_for_a_partial_nobody_announces_times_out(pkg, cuda, oracle):
     """The finishing CTA's wait for its peers' partials is bounded like every other wait: with the "partial stored"
     flags withheld (diagnostic bit 4: a flag that nothing sets) and a 100 us budget the launch ends by itself with
-    a DEVICE_TIMEOUT record naming that wait (800 + draining warp, detail = the peer CTA); reading the record
-    also clears the flag sets, and the next normal stream-K launch is correct."""
+    a DEVICE_TIMEOUT record naming that wait (800 + draining warp, detail = the partial slot); reading the record
+    also clears the flag sets, and the next normal launch with cut tiles is correct."""
     m, n, k = 1536, 2048, 1024
     ov = dict(tile_m=256, tile_n=256, cta_group=2, tail_split=1)
     A, Bt, _ = inputs(pkg, pkg.F16, m, n, k, 198)
@@ -464,7 +464,7 @@ def test_stream_k_wait_for_a_partial_nobody_announces_times_out(pkg, cuda, oracl
         st, info = pkg.device_status()
     finally:
         pkg.set_wait_budget_ns(2_000_000_000)
-    assert st == pkg.DEVICE_TIMEOUT and 800 <= info[2] < 808 and 0 <= info[3] < pkg.num_sms(), (st, info, WAIT_IDS)
+    assert st == pkg.DEVICE_TIMEOUT and 800 <= info[2] < 808 and info[3] >= 0, (st, info, WAIT_IDS)
     assert pkg.device_status()[0] == pkg.OK
     got = run_gemm(pkg, cuda, pkg.F16, A, Bt, None, 1.0, 0.0, **ov)
     ok, msg = tolerance_ok(got, oracle.gemm(A, Bt), k)
@@ -488,7 +488,7 @@ def test_error_statuses_on_device_calls(pkg, cuda):
 
 WAIT_IDS = "100+s producer waits for a free stage, 200+ sub-tile producer, 300+acc MMA waits for a drained accumulator, " \
            "400+/500+ MMA waits for data, 600+acc epilogue waits for a finished tile, 700/701 cluster reduce, " \
-           "800+warp stream-K wait for a peer's partial"
+           "800+warp tail split: wait for an earlier slice's partial"
 
 
 def test_bounded_wait_reports_instead_of_hanging(pkg, cuda, oracle):
