@@ -549,17 +549,20 @@ def run_ours(args):
     # ---- optional: per-role cycle counters of CTA 0 from one extra launch (tracing hook of the library)
     roles = None
     if args.role_counters and rank == 0:
-        prof = torch.zeros((2, pkg.profile_slots()), dtype=torch.int64, device=dev)
-        pkg.lib().b200_set_profile_buffer(prof.data_ptr(), 2)
+        nblk = args.role_block + 1
+        prof = torch.zeros((nblk, pkg.profile_slots()), dtype=torch.int64, device=dev)
+        pkg.lib().b200_set_profile_buffer(prof.data_ptr(), nblk)
         pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
         torch.cuda.synchronize()
         pkg.lib().b200_set_profile_buffer(None, 0)
-        r = prof.cpu().tolist()[0]
+        r = prof.cpu().tolist()[args.role_block]
         it, tiles = max(r[9], 1), max(r[12], 1)
-        roles = {"stages": r[9], "tiles": r[12], "producer_cycles_per_stage": r[1] / max(r[2], 1),
+        roles = {"block": args.role_block, "stages": r[9], "units": r[12], "producer_cycles_per_stage": r[1] / max(r[2], 1),
                  "producer_wait_per_stage": r[0] / max(r[2], 1), "mma_cycles_per_stage": r[8] / it,
-                 "mma_wait_data_per_stage": r[6] / it, "mma_wait_accumulator_per_tile": r[7] / tiles,
-                 "epilogue_cycles_per_tile": r[11] / tiles, "epilogue_wait_per_tile": r[10] / tiles}
+                 "mma_wait_data_per_stage": r[6] / it, "mma_wait_accumulator_per_unit": r[7] / tiles,
+                 "mma_wait_accumulator_total": r[7], "mma_cycles_total": r[8],
+                 "epilogue_cycles_per_unit": r[11] / tiles, "epilogue_wait_per_unit": r[10] / tiles,
+                 "epilogue_cycles_total": r[11], "epilogue_wait_total": r[10], "kernel_ns": r[15] - r[13]}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only, bounded sample)
     cpu = None
@@ -660,7 +663,8 @@ def main():
     ap.add_argument("--wmma-baseline", type=int, default=-1,
                     help="time the reference's own WMMA kernel recompiled for sm_100a (oracle/_ref/ref_wmma_async) beside "
                          "the number: 1 = yes, 0 = no, default = yes on one GPU when the binary is there")
-    ap.add_argument("--role-counters", action="store_true", help="add in-kernel per-role cycle counters of CTA 0")
+    ap.add_argument("--role-counters", action="store_true", help="add in-kernel per-role cycle counters of one CTA")
+    ap.add_argument("--role-block", type=int, default=0, help="which CTA the role counters come from")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

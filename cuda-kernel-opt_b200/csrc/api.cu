@@ -182,9 +182,34 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
     }
     if (pair) {
         p->tile_m = 256;
-        p->tile_n = 256;
         p->cta_group = 2;
-        p->num_stages = 6;
+        // Tile width against wave quantisation: 74 CTA pairs run a wave of tiles, and a last wave that is partly
+        // empty still costs a whole tile time. Narrower tiles (224 or 192 columns, the last tile column ragged
+        // where they do not divide N) can make the waves come out even - 1024 x 8192: 4 x 37 tiles of 224 columns
+        // are exactly two waves, where 4 x 32 tiles of 256 take two waves of which the second is 73 % full -
+        // at the price of more operand traffic per flop. Cost = waves x (columns + a per-tile charge), with the
+        // tail split's single-round saving counted where it applies (it needs the caller's workspace).
+        const int64_t rows = (M + 255) / 256;
+        int best_n = 256;
+        double best_cost = 0.0;
+        for (int tn = 256; tn >= 192; tn -= 32) {
+            const int64_t tiles = rows * ((N + tn - 1) / tn);
+            const int64_t full = tiles / 74, r = tiles % 74;
+            double waves = double(full);
+            if (r > 0) {
+                const int64_t s = 74 / r > 8 ? 8 : 74 / r;
+                waves += (s >= 2 && K / 64 / s >= 4) ? 1.0 / double(s) + 0.04 : 1.0;
+            }
+            const double cost = waves * double(tn + 12) * (tn == 256 ? 1.0 : 1.02);
+            if (tn == 256 || cost < best_cost * 0.97) {   // a narrower tile has to win by 3 %
+                if (tn == 256 || cost < best_cost) {
+                    best_cost = cost;
+                    best_n = tn;
+                }
+            }
+        }
+        p->tile_n = best_n;
+        p->num_stages = 6;   // 6 x (128 + tile_n / 2) rows x 128 B, and 32 KB of TMA-store staging: 224 KB with 256 columns
         p->num_producer_warps = 2;
         p->l2_hint = 3;  // keep operand panels in L2: fewer DRAM re-reads, measured +2.5 % under the power limit
     } else {

@@ -902,6 +902,30 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
                 uint32_t r[32];
                 const bool wide = (col_end - c0) >= 32;
+                float4 part[8];
+                if (tail_peers > 0) {
+                    // The earlier slices' partials of this chunk, summed in ascending K order (this, the last slice, is
+                    // added below). Eight independent 16-byte loads per lane and slice are in flight at once, and the
+                    // first batch is issued ahead of the tensor-memory load; .cg: other SMs wrote them.
+                    const float4 *src = reinterpret_cast<const float4 *>(g_partial) +
+                                        (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
+                    const uint32_t step4 = static_cast<uint32_t>(tail_step) * tail_slot4;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) part[j] = __ldcg(src + j * 32);
+#pragma unroll 1
+                    for (int i = 1; i < tail_peers; ++i) {
+                        float4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + i * step4 + j * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            part[j].x += v[j].x;
+                            part[j].y += v[j].y;
+                            part[j].z += v[j].z;
+                            part[j].w += v[j].w;
+                        }
+                    }
+                }
                 if (wide) {
                     tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
                 } else {
@@ -926,25 +950,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     continue;
                 }
                 if (tail_peers > 0) {
-                    // the earlier slices' partials of this chunk, summed in ascending K order, then this (last) slice;
-                    // .cg: they were written by other SMs
-                    const float4 *src = reinterpret_cast<const float4 *>(g_partial) +
-                                        (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
-                    const uint32_t step4 = static_cast<uint32_t>(tail_step) * tail_slot4;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        float4 v = __ldcg(src + j * 32);
-                        for (int i = 1; i < tail_peers; ++i) {
-                            const float4 u = __ldcg(src + i * step4 + j * 32);
-                            v.x += u.x;
-                            v.y += u.y;
-                            v.z += u.z;
-                            v.w += u.w;
-                        }
-                        r[4 * j + 0] = __float_as_uint(v.x + __uint_as_float(r[4 * j + 0]));
-                        r[4 * j + 1] = __float_as_uint(v.y + __uint_as_float(r[4 * j + 1]));
-                        r[4 * j + 2] = __float_as_uint(v.z + __uint_as_float(r[4 * j + 2]));
-                        r[4 * j + 3] = __float_as_uint(v.w + __uint_as_float(r[4 * j + 3]));
+                        r[4 * j + 0] = __float_as_uint(part[j].x + __uint_as_float(r[4 * j + 0]));
+                        r[4 * j + 1] = __float_as_uint(part[j].y + __uint_as_float(r[4 * j + 1]));
+                        r[4 * j + 2] = __float_as_uint(part[j].z + __uint_as_float(r[4 * j + 2]));
+                        r[4 * j + 3] = __float_as_uint(part[j].w + __uint_as_float(r[4 * j + 3]));
                     }
                 }
                 if (swap_ab) {

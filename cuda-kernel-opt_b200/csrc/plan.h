@@ -56,9 +56,9 @@ struct Plan {
 // Tail split (tail_split = 1): the tiles that do not fill a wave of the persistent grid are cut along K.
 // T tiles on S slots (CTAs, or CTA pairs) leave r = T mod S tiles for a last, partly idle wave that still
 // costs a whole tile time. Instead those r tiles are cut into s equal K slices each; the r * s slice units
-// are dealt to the slots in rounds of S, slice-major (all first slices, then all second slices, ...), and
-// run FIRST, before the whole tiles. A round costs 1/s of a tile time, so the tail costs
-// ceil(r * s / S) / s tile times instead of 1. Slice-major rounds keep the slots in step along K: the CTAs
+// are dealt to the slots slice-major (all first slices, then all second slices, ...) and run FIRST, before
+// the whole tiles; with s = floor(S / r) they fit one round, so the tail costs 1 / s of a tile time instead
+// of 1. The slice-major order keeps the slots in step along K: the CTAs
 // that run at the same time read the same K range of neighbouring tiles, so operand panels are shared in
 // L2 as in a wave of whole tiles. (A plain stream-K cut - one contiguous range of K iterations per slot -
 // balances better on paper but puts every slot at a different K offset: nothing is shared, the phase turns
@@ -81,20 +81,17 @@ inline TailPlan make_tail_plan(int enabled, int64_t tiles, int slots, int64_t nu
     if (!enabled || split_k > 1 || slots < 2 || tiles <= 0) return t;
     const int64_t r = tiles % slots;
     if (r == 0) return t;
-    // cost of the tail in tile times for s slices, plus a small charge per extra slice (partials to write and read back)
-    double best = 1.0;
-    int best_s = 1;
-    for (int s = 2; s <= kTailMaxSlices; ++s) {
-        if (num_segs / s < 4) break;                                   // slices of at least four K segments
-        if (r * (s - 1) * cta_group > kTailMaxSlots) break;
-        const double cost = double((r * s + slots - 1) / slots) / double(s) + 0.01 * (s - 1);
-        if (cost < best - 1e-9) {
-            best = cost;
-            best_s = s;
-        }
-    }
+    // One round only: s = floor(S / r) slices (at most 8, and slices of at least four K segments), so every slot runs
+    // at most one slice unit and the tail costs 1 / s of a tile time. Plans with several rounds balance better on
+    // paper (54 tiles left on 74 pairs: quarters in three rounds, 0.75) but measured slower than the plain schedule:
+    // every extra slice is a 128 x tile_n fp32 partial written and read back, and under the power limit the time of
+    // a launch follows the energy it spends more than the SM time it leaves idle.
+    int best_s = static_cast<int>(slots / r);
+    if (best_s > kTailMaxSlices) best_s = kTailMaxSlices;
+    while (best_s > 1 && num_segs / best_s < 4) --best_s;
+    while (best_s > 1 && r * (best_s - 1) * cta_group > kTailMaxSlots) --best_s;
     const int64_t waves = (tiles + slots - 1) / slots;
-    if (best_s == 1 || (1.0 - best) / double(waves) < 0.02) return t;   // under 2 % of the launch: not worth the traffic
+    if (best_s < 2 || (1.0 - 1.0 / best_s) / double(waves) < 0.02) return t;   // under 2 % of the launch: not worth the traffic
     t.tiles = static_cast<int>(r);
     t.slices = best_s;
     t.slot_bytes = int64_t((tile_n + 31) / 32) * 4 * 32 * 32 * 4;

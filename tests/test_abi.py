@@ -193,13 +193,16 @@ def test_tail_split_schedule_covers_every_k_segment_once(pkg):
     one = dict(tile_m=128, tile_n=128, tail_split=1)
     cases = [  # M, N, K, overrides, SMs, expected (cut tiles, slices) or None when nothing is gained
         (4096, 4096, 4096, pair, 148, (34, 2)),            # 256 tiles on 74 pairs: 34 left, two halves each -> 3.5 instead of 4 tile times
-        (1024, 8192, 8192, pair, 148, (54, 4)),            # 128 tiles: 54 left, quarters in 3 rounds -> 1.75 instead of 2
-        (8192, 8192, 8192, pair, 148, None),               # 62 left of 74: 7 slices would save 1 % of 14 waves
-        (2048, 2048, 262144, pair, 148, (64, 8)),          # 64 tiles on 74 pairs: eighths in 7 rounds -> 0.875 of a tile time
+        (2048, 8192, 8192, pair, 148, (34, 2)),
+        (1024, 8192, 8192, pair, 148, None),               # 54 left of 74: more than half a wave, one round cannot hold two slices each
+        (8192, 8192, 8192, pair, 148, None),               # 62 left of 74
+        (2048, 2048, 262144, pair, 148, None),             # 64 tiles on 74 pairs
+        (256 * 5, 256 * 15, 2048, pair, 148, (1, 8)),      # 75 tiles: one left, eight slices (the cap)
         (128 * 3, 128 * 50, 1024, one, 148, (2, 4)),       # 150 tiles on 148: 2 left, 16 K segments -> at most 4 slices of 4
-        (640, 896, 4096, one, 20, (15, 4)),                # 35 tiles on 20 CTAs: 15 left, quarters in 3 rounds
+        (640, 896, 4096, one, 40, None),                   # 35 tiles on 40 CTAs
+        (640, 1024, 4096, one, 30, (10, 3)),               # 40 tiles on 30 CTAs: 10 left, thirds
         (256 * 74, 256, 4096, pair, 148, None),            # a full wave
-        (300, 520, 2048, dict(one, tile_n=64), 40, (27, 7)),  # 27 tiles on 40 CTAs: sevenths in 5 rounds -> 0.71
+        (300, 520, 2048, dict(one, tile_n=64), 20, (7, 2)),   # 27 tiles on 20 CTAs: 7 left, halves
     ]
     for M, N, K, ov, sms, want in cases:
         p = P(pkg, **dict(ov, num_sms=sms))
@@ -227,7 +230,7 @@ def test_tail_split_schedule_covers_every_k_segment_once(pkg):
             _, units = pkg.schedule(M, N, K, p, sms, g)
             kinds = [u[4] for u in units]
             first_whole = kinds.index(0) if 0 in kinds else len(kinds)
-            assert all(k == 0 for k in kinds[first_whole:]), (g, kinds)                # slice units first, then whole tiles
+            assert all(k == 0 for k in kinds[first_whole:]) and first_whole <= 1, (g, kinds)   # at most one slice unit, first
             longest = max(longest, sum(u[3] - u[2] for u in units) / segs)
         if cut:
             r = len(cut)

@@ -235,7 +235,7 @@ def test_cuda_graph_capture_and_overlapped_launch(pkg, cuda, oracle):
     torch = cuda
     cases = [(16, 1536, 2048, pkg.BF16, dict()), (300, 512, 1024, pkg.F16, dict()), (64, 768, 4096, pkg.BF16, dict(split_k=3)),
              (16, 1024, 8192, pkg.BF16, dict(swap_ab=1, tile_m=16, split_k=4, cluster_reduce=1)), (520, 1024, 512, pkg.F16, dict(tile_m=256, tile_n=256, cta_group=2)),
-             (640, 128 * 30, 1024, pkg.F16, dict(tile_m=128, tile_n=128, tail_split=1, num_sms=40))]     # tail split: replays reuse the flags
+             (640, 128 * 30, 1024, pkg.F16, dict(tile_m=128, tile_n=128, tail_split=1, num_sms=60))]     # tail split: replays reuse the flags
     for overlap in (0, 1):
         prepared = []
         for i, (m, n, k, dtype, ov) in enumerate(cases):
@@ -406,11 +406,11 @@ def test_tail_split(pkg, cuda, oracle):
         (128 * 10, 128 * (sms // 10 + 2), 1024, dict(tile_m=128, tile_n=128)),                         # 1-CTA tiles, a few left over
         (256 * 5, 256 * (sms // 10 + 1), 2048, dict(tile_m=256, tile_n=256, cta_group=2)),             # pairs, one tile left over: eight slices
         (200, 128 * (sms + 3), 2048, dict(tile_m=128, tile_n=128, segment_dim_k=128, num_stages=3)),   # ragged M, 3 tiles left over
-        (1536, 2048, 4096, dict(tile_m=256, tile_n=256, cta_group=2)),                                 # 48 tiles on 74 pairs: every tile is cut in three
+        (1024, 2048, 4096, dict(tile_m=256, tile_n=256, cta_group=2)),                                 # 32 tiles on 74 pairs: every tile is cut in two
         (640, 64 * 50, 1096, dict(tile_m=64, tile_n=64, num_sms=40)),                                  # 64-row atoms, ragged K
         (700, 1000, 2048, dict(tile_m=128, tile_n=224, num_consumer_warps=8, num_sms=28)),             # 8 draining warps, ragged M and N, 16-column last chunk
-        (1024, 128 * 37, 1536, dict(tile_m=128, tile_n=128, epilogue=0, num_sms=110, num_producer_warps=2)),   # plain-store drain
-        (2048, 2048, 2048, dict(tile_m=256, tile_n=128, cta_group=2, num_stages=4)),                   # 128 tiles on 74 pairs: 54 left, quarters
+        (1024, 128 * 37, 1536, dict(tile_m=128, tile_n=128, epilogue=0, num_sms=120, num_producer_warps=2)),   # plain-store drain, 56 left of 120: halves
+        (2048, 1664, 2048, dict(tile_m=256, tile_n=128, cta_group=2, num_stages=4)),                   # 104 tiles on 74 pairs: 30 left, halves
     ]
     for m, n, k, ov in cases:
         p = pkg.default_params(m, n, k, pkg.F16, tail_split=1, **ov)
@@ -425,7 +425,7 @@ def test_tail_split(pkg, cuda, oracle):
         plain = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, 1.5, 1.0, tail_split=0, **ov)
         assert float(np.abs(got - plain).max()) <= 2.0 ** -10 * np.sqrt(k) * 3.0, (m, n, k, ov)   # cut tiles sum K in another order
     # the defaults ask for it wherever it can gain, and a call without a workspace still works (plain schedule)
-    m, n, k = 2048, 4096, 1024
+    m, n, k = 2048, 3328, 1024                                      # 8 x 13 pair tiles: 30 left over
     p = pkg.default_params(m, n, k, pkg.F16)
     assert p.tail_split == 1 and pkg.workspace_bytes(m, n, k, p) > 0
     A, Bt, _ = inputs(pkg, pkg.F16, m, n, k, 199)
@@ -450,7 +450,7 @@ def test_tail_split_wait_for_a_partial_nobody_announces_times_out(pkg, cuda, ora
     flags withheld (diagnostic bit 4: a flag that nothing sets) and a 100 us budget the launch ends by itself with
     a DEVICE_TIMEOUT record naming that wait (800 + draining warp, detail = the partial slot); reading the record
     also clears the flag sets, and the next normal launch with cut tiles is correct."""
-    m, n, k = 1536, 2048, 1024
+    m, n, k = 1024, 2048, 1024
     ov = dict(tile_m=256, tile_n=256, cta_group=2, tail_split=1)
     A, Bt, _ = inputs(pkg, pkg.F16, m, n, k, 198)
     dA, dB = to_device(cuda, A, pkg.F16), to_device(cuda, Bt, pkg.F16)
