@@ -187,8 +187,10 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         // empty still costs a whole tile time. Narrower tiles (224 or 192 columns, the last tile column ragged
         // where they do not divide N) can make the waves come out even - 1024 x 8192: 4 x 37 tiles of 224 columns
         // are exactly two waves, where 4 x 32 tiles of 256 take two waves of which the second is 73 % full -
-        // at the price of more operand traffic per flop. Cost = waves x (columns + a per-tile charge), with the
-        // tail split's single-round saving counted where it applies (it needs the caller's workspace).
+        // at the price of more operand traffic per flop. Cost = waves x (columns + a per-tile charge). The 256-column
+        // tile is credited with the tail split's saving where that applies (measured: 4096^3 and 2048 x 8192 x 8192
+        // run faster with 256 columns and the tail cut in two than with 224 or 192 columns); a narrower tile has to
+        // win by 3 % without it, since the tail split only engages when the caller passes a workspace.
         const int64_t rows = (M + 255) / 256;
         int best_n = 256;
         double best_cost = 0.0;
@@ -198,14 +200,12 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
             double waves = double(full);
             if (r > 0) {
                 const int64_t s = 74 / r > 8 ? 8 : 74 / r;
-                waves += (s >= 2 && K / 64 / s >= 4) ? 1.0 / double(s) + 0.04 : 1.0;
+                waves += (tn == 256 && s >= 2 && K / 64 / s >= 4) ? 1.0 / double(s) + 0.04 : 1.0;
             }
             const double cost = waves * double(tn + 12) * (tn == 256 ? 1.0 : 1.02);
-            if (tn == 256 || cost < best_cost * 0.97) {   // a narrower tile has to win by 3 %
-                if (tn == 256 || cost < best_cost) {
-                    best_cost = cost;
-                    best_n = tn;
-                }
+            if (tn == 256 || cost < best_cost * 0.97) {
+                best_cost = cost;
+                best_n = tn;
             }
         }
         p->tile_n = best_n;
