@@ -520,30 +520,55 @@ def run_ours(args):
     # ---- end to end: the host-buffer call of the C ABI (H2D of A, B^T, launch, D2H of D, sync)
     e2e = None
     if not splitk_ranks and not args.no_e2e and not library:
+        sharded_host = world > 1 and scaling == "strong" and not nshard and N % world == 0 and (N // world) % 256 == 0
         hA = torch.empty((m_loc, k_loc), dtype=tdt).pin_memory()
-        hB = torch.empty((n_loc, k_loc), dtype=tdt).pin_memory()
         hD = torch.empty((m_loc, n_loc), dtype=torch.float32).pin_memory()
         hA.copy_(A)
-        hB.copy_(Bt)
-        sess = pkg.Session(m_loc, n_loc, k_loc)
         e_steps = max(1, min(args.steps, 10))
-        sess.gemm_host(dtype, hA, hB, None, hD, 1.0, 0.0, m_loc, n_loc, k_loc, p if p.split_k == 1 else None)
+        if sharded_host:
+            # M-shard on several GPUs: B^T crosses PCIe once. Every rank uploads its rows of A and only its N / world
+            # rows of B^T, the GPUs exchange the B^T rows over NVLink (peer copies), every rank downloads its rows of D.
+            rows_b = N // world
+            hB = torch.empty((rows_b, k_loc), dtype=tdt).pin_memory()
+            hB.copy_(Bt[rank * rows_b:(rank + 1) * rows_b])
+            hg = shard.HostGemmMShard(pkg, m_loc, N, K)
+            run_e2e = lambda: hg.gemm(dtype, hA, hB, None, hD, 1.0, 0.0)
+            h2d = int(2 * (m_loc * k_loc + rows_b * k_loc))
+            call = ("b200_session_gemm_host_sharded (pinned host rows of A and N / world rows of B^T -> device, B^T rows exchanged "
+                    "between the GPUs over NVLink, one product per column block, rows of D -> pinned host, synchronised)")
+        else:
+            hB = torch.empty((n_loc, k_loc), dtype=tdt).pin_memory()
+            hB.copy_(Bt)
+            sess = pkg.Session(m_loc, n_loc, k_loc)
+            p_host = p if p.split_k == 1 else None
+            run_e2e = lambda: sess.gemm_host(dtype, hA, hB, None, hD, 1.0, 0.0, m_loc, n_loc, k_loc, p_host)
+            h2d = int(2 * (m_loc * k_loc + n_loc * k_loc))
+            call = ("b200_session_gemm_host (pinned host A, B^T -> device, GEMM, D -> pinned host, synchronised; a 4 x 4 grid of D "
+                    "blocks pipelined over upload / compute / download streams)")
+        run_e2e()
         barrier()
         t0 = time.perf_counter()
         for _ in range(e_steps):
-            sess.gemm_host(dtype, hA, hB, None, hD, 1.0, 0.0, m_loc, n_loc, k_loc, p if p.split_k == 1 else None)
+            run_e2e()
         dt = (time.perf_counter() - t0) / e_steps
         tt = torch.tensor([dt], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         dt = float(tt.item())
         ev_ = (job_flops / dt / 1e12) if bound == "tensor" else (job_bytes / dt / 1e9)
-        same = bool(torch.equal(hD.to(dev), D)) if p.split_k == 1 else None
-        e2e = {"value": ev_, "unit": unit, "h2d_bytes_per_step": int(2 * (m_loc * k_loc + n_loc * k_loc)),
-               "d2h_bytes_per_step": int(4 * m_loc * n_loc), "steps": e_steps, "ms_per_step": dt * 1e3,
-               "call": "b200_session_gemm_host (pinned host A, B^T -> device, GEMM, D -> pinned host, synchronised; a 4 x 4 grid of D blocks pipelined over upload / compute / download streams)",
-               "result_equals_device_run": same}
-        sess.close()
+        pkg.gemm(A, Bt, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)     # the device-resident result of the same operands
+        torch.cuda.synchronize()
+        diff = float((hD.to(dev) - D).abs().max())
+        st, info = pkg.device_status()
+        assert st == pkg.OK, f"device status {st} {info}"
+        e2e = {"value": ev_, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(4 * m_loc * n_loc), "steps": e_steps,
+               "ms_per_step": dt * 1e3, "call": call, "result_equals_device_run": diff == 0.0,
+               "result_max_abs_diff_vs_device_run": diff,
+               "note": "differences, if any, are summation order: the tail split cuts other tiles in the block products than in the whole product"}
+        if sharded_host:
+            hg.close()
+        else:
+            sess.close()
         del hA, hB, hD
 
     # ---- optional: per-role cycle counters of CTA 0 from one extra launch (tracing hook of the library)

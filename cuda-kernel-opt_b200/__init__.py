@@ -26,7 +26,7 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 EXPORTS = [
     "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes", "b200_gemm_schedule",
     "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_f16_out_f16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
-    "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host",
+    "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host", "b200_session_buffers", "b200_session_gemm_host_sharded",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_profile_slots", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
     "b200_fill_u16_device", "b200_fill_f32_device", "b200_fill_u16_host", "b200_fill_f32_host",
 ]
@@ -88,6 +88,9 @@ def lib():
         L.b200_session_destroy.argtypes = [vp]
         L.b200_session_destroy.restype = None
         L.b200_session_gemm_host.argtypes = [vp, C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, PP]
+        L.b200_session_buffers.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
+        L.b200_session_gemm_host_sharded.argtypes = [vp, C.c_int, vp, vp, vp, vp, f32, f32, i64, i64, i64, C.c_int, C.c_int,
+                                                     C.POINTER(vp), C.POINTER(vp), C.c_int, PP]
         L.b200_device_status.argtypes = [vp, C.POINTER(C.c_int * 4)]
         L.b200_set_wait_budget_ns.argtypes = [u64]
         L.b200_set_wait_budget_ns.restype = None

@@ -460,6 +460,7 @@ struct b200_session {
     cudaStream_t stream;      // uploads
     cudaStream_t compute;     // launches
     cudaStream_t download;    // results
+    cudaStream_t push;        // copies of this GPU's B^T rows into the other GPUs (sharded call)
     cudaEvent_t up[16], done[16], b_ready;
     void *dW;                 // workspace for the tail split of the block products
     size_t w_bytes;
@@ -669,6 +670,7 @@ int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_sessio
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->compute, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->download, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->push, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->b_ready, cudaEventDisableTiming);
     for (int i = 0; i < 16 && e == cudaSuccess; ++i) {
         e = cudaEventCreateWithFlags(&s->up[i], cudaEventDisableTiming);
@@ -687,6 +689,7 @@ void b200_session_destroy(b200_session *s) {
     if (s->stream) cudaStreamDestroy(s->stream);
     if (s->compute) cudaStreamDestroy(s->compute);
     if (s->download) cudaStreamDestroy(s->download);
+    if (s->push) cudaStreamDestroy(s->push);
     if (s->b_ready) cudaEventDestroy(s->b_ready);
     for (int i = 0; i < 16; ++i) {
         if (s->up[i]) cudaEventDestroy(s->up[i]);
@@ -779,6 +782,101 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
         }
     }
     e = cudaStreamSynchronize(s->download);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+    if (e != cudaSuccess) return drained(fail_cuda(e));
+    return B200_OK;
+}
+
+int b200_session_buffers(b200_session *s, void **dA, void **dBt, void **dC, void **dD) {
+    if (!s) return B200_INVALID_POINTER;
+    if (dA) *dA = s->dA;
+    if (dBt) *dBt = s->dB;
+    if (dC) *dC = s->dC;
+    if (dD) *dD = s->dD;
+    return B200_OK;
+}
+
+int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_rows, const void *hBt_rows, const float *hC_rows,
+                                   float *hD_rows, float alpha, float beta, int64_t m_rows, int64_t N, int64_t K, int world,
+                                   int rank, void *const *peer_bt, void *const *peer_flags, int epoch,
+                                   const b200_gemm_params *p) {
+    if (!s || !hA_rows || !hBt_rows || !hD_rows || !peer_bt || !peer_flags) return B200_INVALID_POINTER;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || epoch < 1) return B200_INVALID_CONFIG;
+    if (m_rows <= 0 || m_rows > s->max_m || N > s->max_n || K > s->max_k || N <= 0 || K <= 0) return B200_INVALID_SHAPE;
+    if (N % world || (N / world) % 256) return B200_INVALID_SHAPE;   // column blocks end on tile edges of every tile shape
+    if (beta != 0.0f && !hC_rows) return B200_INVALID_POINTER;
+    for (int o = 0; o < world; ++o)
+        if (!peer_bt[o] || !peer_flags[o]) return B200_INVALID_POINTER;
+    if (peer_bt[rank] != s->dB) return B200_INVALID_POINTER;         // this rank's entry is the session's own B^T buffer
+    b200_gemm_params local;
+    if (!p) {
+        default_params(m_rows, N / world, K, &local);
+        p = &local;
+    }
+    const int64_t cols = N / world;                       // B^T rows (= columns of D) per rank
+    const size_t slice_bytes = static_cast<size_t>(cols) * K * 2;
+    const long long budget = static_cast<long long>(g_wait_budget_ns.load() * 2ull);
+    int *const my_flags = static_cast<int *>(peer_flags[rank]);
+    char *const dB8 = static_cast<char *>(s->dB);
+    cudaError_t e = cudaSuccess;
+    auto drained = [s](int status) {
+        cudaStreamSynchronize(s->stream);
+        cudaStreamSynchronize(s->push);
+        cudaStreamSynchronize(s->compute);
+        cudaStreamSynchronize(s->download);
+        return status;
+    };
+    auto check = [&](int launch_error) { return launch_error == 0 ? cudaSuccess : static_cast<cudaError_t>(launch_error); };
+
+    // upload stream: this rank's B^T rows, then its A rows (and C rows)
+    e = cudaMemcpyAsync(dB8 + static_cast<size_t>(rank) * slice_bytes, hBt_rows, slice_bytes, cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(s->b_ready, s->stream);
+    if (e == cudaSuccess) e = check(launch_flag_set(my_flags + rank, epoch, s->stream));
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(s->dA, hA_rows, static_cast<size_t>(m_rows) * K * 2, cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess && beta != 0.0f)
+        e = cudaMemcpyAsync(s->dC, hC_rows, static_cast<size_t>(m_rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(s->up[0], s->stream);
+    if (e != cudaSuccess) return drained(fail_cuda(e));
+
+    // push stream: the rows just uploaded go to every other GPU over NVLink (one copy per peer, nearest rank first),
+    // each followed by that peer's "rows of `rank` have arrived" flag. A peer's buffer is overwritten only after
+    // that peer has announced the end of its previous product (its "done" flag here).
+    e = cudaStreamWaitEvent(s->push, s->b_ready, 0);
+    for (int d = 1; d < world && e == cudaSuccess; ++d) {
+        const int o = (rank + d) % world;
+        e = check(launch_flag_wait(my_flags + world + o, epoch - 1, budget, 900 + o, s->push));
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(static_cast<char *>(peer_bt[o]) + static_cast<size_t>(rank) * slice_bytes,
+                                dB8 + static_cast<size_t>(rank) * slice_bytes, slice_bytes, cudaMemcpyDefault, s->push);
+        if (e == cudaSuccess) e = check(launch_flag_set(static_cast<int *>(peer_flags[o]) + rank, epoch, s->push));
+    }
+    if (e != cudaSuccess) return drained(fail_cuda(e));
+
+    // compute stream: one product per column block, own block first, each as soon as its B^T rows are here;
+    // download stream: every finished block goes back while the next one is computed
+    e = cudaStreamWaitEvent(s->compute, s->up[0], 0);
+    for (int d = 0; d < world && e == cudaSuccess; ++d) {
+        const int j = (rank + d) % world;
+        e = check(launch_flag_wait(my_flags + j, epoch, budget, 910 + j, s->compute));
+        if (e != cudaSuccess) break;
+        const size_t off = static_cast<size_t>(j) * cols;
+        const int st = gemm_impl(dtype, s->dA, dB8 + static_cast<size_t>(j) * slice_bytes, beta != 0.0f ? s->dC + off : nullptr,
+                                 s->dD + off, alpha, beta, m_rows, cols, K, p, s->dW, s->w_bytes, s->compute, nullptr, N);
+        if (st != B200_OK) return drained(st);
+        e = cudaEventRecord(s->done[d], s->compute);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[d], 0);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(hD_rows + off, static_cast<size_t>(N) * 4, s->dD + off, static_cast<size_t>(N) * 4,
+                                  static_cast<size_t>(cols) * 4, static_cast<size_t>(m_rows), cudaMemcpyDeviceToHost, s->download);
+    }
+    // tell every GPU that this one no longer reads the B^T rows of this epoch
+    for (int o = 0; o < world && e == cudaSuccess; ++o)
+        if (o != rank) e = check(launch_flag_set(static_cast<int *>(peer_flags[o]) + world + rank, epoch, s->compute));
+    if (e != cudaSuccess) return drained(fail_cuda(e));
+    e = cudaStreamSynchronize(s->download);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->compute);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->push);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
     if (e != cudaSuccess) return drained(fail_cuda(e));
     return B200_OK;

@@ -1303,6 +1303,41 @@ int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int sp
     return static_cast<int>(cudaGetLastError());
 }
 
+// Flags between the GPUs of a box (plain ints in peer-mapped device memory): one thread writes a flag after
+// everything before it in the stream has completed; one thread waits, bounded, until a flag has reached an epoch
+// (epochs only grow). A wait that runs out leaves a DEVICE_TIMEOUT record {block 0, wait id, epoch}.
+__global__ void flag_set_kernel(int *flag, int epoch) {
+    __threadfence_system();
+    *reinterpret_cast<volatile int *>(flag) = epoch;
+    __threadfence_system();
+}
+
+__global__ void flag_wait_kernel(const int *flag, int epoch, long long budget, int wait_id) {
+    const long long t0 = clock64();
+    while (static_cast<int>(*reinterpret_cast<const volatile int *>(flag) - epoch) < 0) {
+        __nanosleep(200);
+        if (clock64() - t0 > budget) {
+            if (atomicCAS(&g_device_status[0], 0, B200_DEVICE_TIMEOUT) == 0) {
+                g_device_status[1] = 0;
+                g_device_status[2] = wait_id;
+                g_device_status[3] = epoch;
+            }
+            break;
+        }
+    }
+    __threadfence_system();
+}
+
+int launch_flag_set(int *flag, int epoch, cudaStream_t stream) {
+    flag_set_kernel<<<1, 1, 0, stream>>>(flag, epoch);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int launch_flag_wait(const int *flag, int epoch, long long budget_cycles, int wait_id, cudaStream_t stream) {
+    flag_wait_kernel<<<1, 1, 0, stream>>>(flag, epoch, budget_cycles, wait_id);
+    return static_cast<int>(cudaGetLastError());
+}
+
 int launch_push_reduce(const float *slots, const int *flags, int world, int epoch, const float *C, float *D, float alpha,
                        float beta, int64_t rows, int64_t n, long long budget_cycles, cudaStream_t stream) {
     const long long n4 = rows * n / 4;

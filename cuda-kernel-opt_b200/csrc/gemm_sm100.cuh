@@ -67,6 +67,9 @@ int read_device_status(int out[4], cudaStream_t stream);
 // D = alpha * sum over sources of slot[src] + beta * C for this GPU's rows.
 int launch_push_reduce(const float *slots, const int *flags, int world, int epoch, const float *C, float *D, float alpha,
                        float beta, int64_t rows, int64_t n, long long budget_cycles, cudaStream_t stream);
+// Stream-ordered flag write / bounded flag wait (flag >= epoch) for exchanges between the GPUs of a box.
+int launch_flag_set(int *flag, int epoch, cudaStream_t stream);
+int launch_flag_wait(const int *flag, int epoch, long long budget_cycles, int wait_id, cudaStream_t stream);
 // Second step of split-K when the rows go to their owner GPUs instead of a local D.
 int launch_splitk_reduce_push(const float *partial, int64_t m, int64_t n, int split_k, float *const *slots, int *const *flags,
                               unsigned int *done, int world, int rank, int epoch, cudaStream_t stream);

@@ -194,7 +194,92 @@ class PushExchange:
         self.slots = self.flags = self.done = None
 
 
-class PeerLeft(RuntimeError):
+class HostGemmMShard:
+    """The host-buffer GEMM of an M-sharded square problem on the GPUs of a box (b200_session_gemm_host_sharded):
+    every rank passes its rows of A, its N / world rows of B^T and a buffer for its rows of D, all in (pinned) host
+    memory. B^T crosses PCIe once: each rank uploads its own rows and copies them to the other GPUs over NVLink,
+    and multiplies column block by column block as the blocks arrive. torch.distributed only carries the IPC
+    handles at set-up."""
+
+    def __init__(self, pkg, m_rows: int, N: int, K: int, group=None):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        self.pkg, self.C, self.dist, self.group = pkg, C, dist, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if N % self.world or (N // self.world) % 256:
+            raise ValueError("columns per GPU must be a multiple of 256")
+        self.m_rows, self.N, self.K = m_rows, N, K
+        lib = pkg.lib()
+        self.session = pkg.Session(m_rows, N, K)
+        dB = C.c_void_p()
+        st = lib.b200_session_buffers(self.session.h, None, C.byref(dB), None, None)
+        if st != pkg.OK:
+            raise pkg.B200Error(st, "b200_session_buffers")
+        self.flags = C.c_void_p()
+        st = lib.b200_peer_alloc(64 * 4, C.byref(self.flags))
+        if st != pkg.OK:
+            raise pkg.B200Error(st, "b200_peer_alloc")
+        handles = []
+        for ptr in (dB, self.flags):
+            buf = C.create_string_buffer(64)
+            st = lib.b200_peer_export(ptr, buf)
+            if st != pkg.OK:
+                raise pkg.B200Error(st, "b200_peer_export")
+            handles.append(bytes(buf.raw))
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=group)
+        self.imported = []
+        self.bt_ptrs = (C.c_void_p * 8)()
+        self.flag_ptrs = (C.c_void_p * 8)()
+        for o in range(self.world):
+            if o == self.rank:
+                self.bt_ptrs[o], self.flag_ptrs[o] = dB.value, self.flags.value
+                continue
+            for which, arr in ((0, self.bt_ptrs), (1, self.flag_ptrs)):
+                out = C.c_void_p()
+                st = lib.b200_peer_import(gathered[o][which], C.byref(out))
+                if st != pkg.OK:
+                    raise pkg.B200Error(st, "b200_peer_import")
+                arr[o] = out.value
+                self.imported.append(out)
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def gemm(self, dtype, hA_rows, hBt_rows, hC_rows, hD_rows, alpha=1.0, beta=0.0, params=None):
+        """hA_rows: m_rows x K, hBt_rows: (N / world) x K (this rank's rows of B^T), hD_rows: m_rows x N, host arrays
+        (numpy or torch CPU tensors, pinned for speed). Every rank calls it once per step. Returns when this rank's
+        rows of D are in host memory."""
+        def addr(x):
+            if x is None:
+                return None
+            return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
+        self.epoch += 1
+        st = self.pkg.lib().b200_session_gemm_host_sharded(
+            self.session.h, dtype, addr(hA_rows), addr(hBt_rows), addr(hC_rows), addr(hD_rows), alpha, beta, self.m_rows, self.N,
+            self.K, self.world, self.rank, self.bt_ptrs, self.flag_ptrs, self.epoch,
+            self.C.byref(params) if params is not None else None)
+        if st != self.pkg.OK:
+            raise self.pkg.B200Error(st, "b200_session_gemm_host_sharded")
+
+    def close(self):
+        import torch
+        torch.cuda.synchronize()
+        self.dist.barrier(group=self.group)
+        lib = self.pkg.lib()
+        for p in self.imported:
+            lib.b200_peer_release(p)
+        self.imported = []
+        self.dist.barrier(group=self.group)
+        if self.flags:
+            lib.b200_peer_free(self.flags)
+            self.flags = None
+        self.session.close()
+
+
+class PeerLeft(RuntimeError):"""
     """Raised by Membership.check() when another rank has announced that it left, or has stopped beating."""
 
     def __init__(self, rank: int, reason: str):

@@ -247,6 +247,25 @@ void b200_session_destroy(b200_session *s);
 int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const void *hBt, const float *hC, float *hD,
                            float alpha, float beta, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p);
 
+/* The host-buffer call on the GPUs of one box, one process and one session per GPU, for D = A * B^T with the rows
+ * of A and D split over the ranks and B^T needed whole on every GPU (the M-shard of a square problem). The
+ * reference's harness is single-GPU (cudaSetDevice(0), matmul_shmem_tc_async_opt_port_2.cu:1503-1510); done naively,
+ * every rank would upload all of B^T over its own PCIe link. Here B^T crosses PCIe once: rank r uploads only rows
+ * [r*N/world, (r+1)*N/world) of B^T (hBt_rows) and its own rows of A (hA_rows, m_rows x K), copies its B^T rows
+ * into the other GPUs' B^T buffers over NVLink (plain peer copies, one per peer), and multiplies column block by
+ * column block as the blocks arrive, own block first, downloading each finished block of D (hD_rows, m_rows x N)
+ * while the next is computed. peer_bt[o] is rank o's session B^T buffer (b200_session_buffers) as mapped into this
+ * process (b200_peer_export / b200_peer_import; peer_bt[rank] is this session's own), peer_flags[o] rank o's array
+ * of 2 * world ints from b200_peer_alloc (zeroed): [src] = rows of src have arrived (epoch), [world + src] = src has
+ * finished its product of that epoch, so its buffer may be overwritten. epoch = 1, 2, 3, ... per call, the same on
+ * every rank. N / world must be a multiple of 256. Waits for peers are on the device and bounded (wait ids 900 + peer
+ * and 910 + block in the DEVICE_TIMEOUT record). Returns when D's rows are in host memory. */
+int b200_session_buffers(b200_session *s, void **dA, void **dBt, void **dC, void **dD);
+int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_rows, const void *hBt_rows, const float *hC_rows,
+                                   float *hD_rows, float alpha, float beta, int64_t m_rows, int64_t N, int64_t K, int world,
+                                   int rank, void *const *peer_bt, void *const *peer_flags, int epoch,
+                                   const b200_gemm_params *p);
+
 /* Synchronises the stream and reports whether any kernel of this library hit a bounded-wait
  * timeout on the current device since the last call. info (may be null) receives
  * {code, block, barrier id, phase}. Clears the record. */

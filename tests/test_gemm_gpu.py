@@ -588,6 +588,33 @@ def test_host_buffer_session(pkg, cuda, oracle):
     s.close()
 
 
+def test_host_buffer_session_sharded_on_one_gpu(pkg, cuda, oracle):
+    """b200_session_gemm_host_sharded with a world of one: the same upload / flag / multiply / download chain as on
+    several GPUs, minus the peer copies (tests/test_multi_gpu.py runs it with peers). Two calls (epochs 1, 2)."""
+    import ctypes as C
+    m, n, k = 384, 1024, 512
+    s = pkg.Session(m, n, k)
+    dB = C.c_void_p()
+    assert pkg.lib().b200_session_buffers(s.h, None, C.byref(dB), None, None) == pkg.OK
+    flags = cuda.zeros(64, dtype=cuda.int32, device="cuda")
+    bt_ptrs, flag_ptrs = (C.c_void_p * 8)(), (C.c_void_p * 8)()
+    bt_ptrs[0], flag_ptrs[0] = dB.value, flags.data_ptr()
+    for epoch in (1, 2):
+        A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 96 + epoch)
+        out = np.full((m, n), np.nan, np.float32)
+        st = pkg.lib().b200_session_gemm_host_sharded(s.h, pkg.F16, A.ctypes.data, Bt.ctypes.data, Cm.ctypes.data, out.ctypes.data,
+                                                      1.0, 1.0, m, n, k, 1, 0, bt_ptrs, flag_ptrs, epoch, None)
+        assert st == pkg.OK, pkg.status_string(st)
+        assert pkg.device_status()[0] == pkg.OK
+        ok, msg = tolerance_ok(out, oracle.gemm(A, Bt, Cm, 1.0, 1.0), k, 2.0)
+        assert ok, msg
+    assert flags[:2].tolist() == [2, 0]
+    bad = pkg.lib().b200_session_gemm_host_sharded(s.h, pkg.F16, A.ctypes.data, Bt.ctypes.data, None, out.ctypes.data,
+                                                   1.0, 0.0, m, 1000, k, 1, 0, bt_ptrs, flag_ptrs, 3, None)
+    assert bad == pkg.INVALID_SHAPE                                     # column blocks must end on tile edges
+    s.close()
+
+
 def test_device_generator_equals_host_generator(pkg, cuda):
     for tdt, code in ((cuda.float16, 0), (cuda.bfloat16, 1)):
         for dist, sigma in ((0, 1.0), (1, 0.02)):

@@ -84,12 +84,27 @@ def _worker(rank, world, port, q):
         ms = shard.m_shard(m3, world, rank, 256)
         got3 = pkg.gemm(to_device(torch, np.ascontiguousarray(A3[ms.begin:ms.end]), pkg.F16), to_device(torch, B3, pkg.F16))
         want3 = oracle.gemm(A3, B3)[ms.begin:ms.end]
+        # (4) the host-buffer call of an M-sharded square: B^T crosses PCIe once (every rank uploads its own rows and
+        # copies them to the other GPUs over NVLink); two steps in a row with different operands
+        m4, n4, k4 = 512, 512 * world, 1024
+        hg = shard.HostGemmMShard(pkg, m4, n4, k4)
+        host_reports = {}
+        for step in range(2):
+            A4 = pkg.fill_u16_host((m4 * world, k4), seed + 10 + step, 1)
+            B4 = pkg.fill_u16_host((n4, k4), seed + 10 + step, 2)
+            mine = np.ascontiguousarray(A4[rank * m4:(rank + 1) * m4])
+            b_rows = np.ascontiguousarray(B4[rank * (n4 // world):(rank + 1) * (n4 // world)])
+            out4 = np.full((m4, n4), np.nan, np.float32)
+            hg.gemm(pkg.F16, mine, b_rows, None, out4, 1.0, 0.0)
+            host_reports[f"host-buffer M-shard, step {step}"] = tolerance_ok(out4, oracle.gemm(mine, B4), k4)
+        hg.close()
         torch.cuda.synchronize()
         st, info = pkg.device_status()
         ex.close()
         report = {name: tolerance_ok(got, want, k) for name, got in results.items()}
         report["N-shard, decode defaults"] = tolerance_ok(got2.cpu().numpy(), want2, k2)
         report["M-shard, defaults"] = tolerance_ok(got3.cpu().numpy(), want3, k3)
+        report.update(host_reports)
         q.put((rank, st, report))
     finally:
         dist.destroy_process_group()
