@@ -279,7 +279,7 @@ class HostGemmMShard:
         self.session.close()
 
 
-class PeerLeft(RuntimeError):"""
+class PeerLeft(RuntimeError):
     """Raised by Membership.check() when another rank has announced that it left, or has stopped beating."""
 
     def __init__(self, rank: int, reason: str):

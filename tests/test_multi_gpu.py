@@ -122,7 +122,15 @@ def test_split_k_over_gpus_nccl_and_fused():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in range(world)]
+    import queue
+    results, deadline = [], time.time() + 300
+    while len(results) < world:
+        try:
+            results.append(q.get(timeout=2))
+        except queue.Empty:
+            dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+            assert not dead, f"a rank exited with {dead} before reporting"       # fail at once, not after the time limit
+            assert time.time() < deadline, "ranks did not report in time"
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
