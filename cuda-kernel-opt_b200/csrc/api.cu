@@ -809,11 +809,14 @@ int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_ro
         if (!peer_bt[o] || !peer_flags[o]) return B200_INVALID_POINTER;
     if (peer_bt[rank] != s->dB) return B200_INVALID_POINTER;         // this rank's entry is the session's own B^T buffer
     b200_gemm_params local;
+    const int64_t cols = N / world;                       // B^T rows (= columns of D) per rank
+    int64_t brows = ((m_rows + 3) / 4 + 255) / 256 * 256; // A is uploaded and multiplied in up to four row blocks
+    if (brows > m_rows) brows = m_rows;
+    const int R = static_cast<int>((m_rows + brows - 1) / brows);
     if (!p) {
-        default_params(m_rows, N / world, K, &local);
+        default_params(brows, cols, K, &local);           // the shape of one block product
         p = &local;
     }
-    const int64_t cols = N / world;                       // B^T rows (= columns of D) per rank
     const size_t slice_bytes = static_cast<size_t>(cols) * K * 2;
     const long long budget = static_cast<long long>(g_wait_budget_ns.load() * 2ull);
     int *const my_flags = static_cast<int *>(peer_flags[rank]);
@@ -828,15 +831,22 @@ int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_ro
     };
     auto check = [&](int launch_error) { return launch_error == 0 ? cudaSuccess : static_cast<cudaError_t>(launch_error); };
 
-    // upload stream: this rank's B^T rows, then its A rows (and C rows)
+    // upload stream: this rank's B^T rows first (every other GPU waits for them), then its A rows in up to four row
+    // blocks (and the matching C rows), so that the first products and their downloads start while later rows are
+    // still on their way up: the two copy directions run on different engines
     e = cudaMemcpyAsync(dB8 + static_cast<size_t>(rank) * slice_bytes, hBt_rows, slice_bytes, cudaMemcpyHostToDevice, s->stream);
     if (e == cudaSuccess) e = cudaEventRecord(s->b_ready, s->stream);
     if (e == cudaSuccess) e = check(launch_flag_set(my_flags + rank, epoch, s->stream));
-    if (e == cudaSuccess)
-        e = cudaMemcpyAsync(s->dA, hA_rows, static_cast<size_t>(m_rows) * K * 2, cudaMemcpyHostToDevice, s->stream);
-    if (e == cudaSuccess && beta != 0.0f)
-        e = cudaMemcpyAsync(s->dC, hC_rows, static_cast<size_t>(m_rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
-    if (e == cudaSuccess) e = cudaEventRecord(s->up[0], s->stream);
+    for (int i = 0; i < R && e == cudaSuccess; ++i) {
+        const int64_t r0 = i * brows, rows = (m_rows - r0 < brows) ? (m_rows - r0) : brows;
+        e = cudaMemcpyAsync(static_cast<char *>(s->dA) + static_cast<size_t>(r0) * K * 2,
+                            static_cast<const char *>(hA_rows) + static_cast<size_t>(r0) * K * 2, static_cast<size_t>(rows) * K * 2,
+                            cudaMemcpyHostToDevice, s->stream);
+        if (e == cudaSuccess && beta != 0.0f)
+            e = cudaMemcpyAsync(s->dC + static_cast<size_t>(r0) * N, hC_rows + static_cast<size_t>(r0) * N,
+                                static_cast<size_t>(rows) * N * 4, cudaMemcpyHostToDevice, s->stream);
+        if (e == cudaSuccess) e = cudaEventRecord(s->up[i], s->stream);
+    }
     if (e != cudaSuccess) return drained(fail_cuda(e));
 
     // push stream: the rows just uploaded go to every other GPU over NVLink (one copy per peer, nearest rank first),
@@ -853,22 +863,29 @@ int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_ro
     }
     if (e != cudaSuccess) return drained(fail_cuda(e));
 
-    // compute stream: one product per column block, own block first, each as soon as its B^T rows are here;
-    // download stream: every finished block goes back while the next one is computed
-    e = cudaStreamWaitEvent(s->compute, s->up[0], 0);
+    // compute stream: column block by column block, own block first, each as soon as its B^T rows are here, and
+    // within a column block one product per row block of A; download stream: every finished block of D goes back
+    // while the next one is computed
+    int n_done = 0;
     for (int d = 0; d < world && e == cudaSuccess; ++d) {
         const int j = (rank + d) % world;
         e = check(launch_flag_wait(my_flags + j, epoch, budget, 910 + j, s->compute));
-        if (e != cudaSuccess) break;
-        const size_t off = static_cast<size_t>(j) * cols;
-        const int st = gemm_impl(dtype, s->dA, dB8 + static_cast<size_t>(j) * slice_bytes, beta != 0.0f ? s->dC + off : nullptr,
-                                 s->dD + off, alpha, beta, m_rows, cols, K, p, s->dW, s->w_bytes, s->compute, nullptr, N);
-        if (st != B200_OK) return drained(st);
-        e = cudaEventRecord(s->done[d], s->compute);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, s->done[d], 0);
-        if (e == cudaSuccess)
-            e = cudaMemcpy2DAsync(hD_rows + off, static_cast<size_t>(N) * 4, s->dD + off, static_cast<size_t>(N) * 4,
-                                  static_cast<size_t>(cols) * 4, static_cast<size_t>(m_rows), cudaMemcpyDeviceToHost, s->download);
+        for (int i = 0; i < R && e == cudaSuccess; ++i) {
+            const int64_t r0 = i * brows, rows = (m_rows - r0 < brows) ? (m_rows - r0) : brows;
+            if (d == 0) e = cudaStreamWaitEvent(s->compute, s->up[i], 0);
+            if (e != cudaSuccess) break;
+            const size_t off = static_cast<size_t>(r0) * N + static_cast<size_t>(j) * cols;
+            const int st = gemm_impl(dtype, static_cast<char *>(s->dA) + static_cast<size_t>(r0) * K * 2,
+                                     dB8 + static_cast<size_t>(j) * slice_bytes, beta != 0.0f ? s->dC + off : nullptr, s->dD + off,
+                                     alpha, beta, rows, cols, K, p, s->dW, s->w_bytes, s->compute, nullptr, N);
+            if (st != B200_OK) return drained(st);
+            cudaEvent_t ev = s->done[n_done++ % 16];     // recorded and waited for at once: safe to record again later
+            e = cudaEventRecord(ev, s->compute);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(s->download, ev, 0);
+            if (e == cudaSuccess)
+                e = cudaMemcpy2DAsync(hD_rows + off, static_cast<size_t>(N) * 4, s->dD + off, static_cast<size_t>(N) * 4,
+                                      static_cast<size_t>(cols) * 4, static_cast<size_t>(rows), cudaMemcpyDeviceToHost, s->download);
+        }
     }
     // tell every GPU that this one no longer reads the B^T rows of this epoch
     for (int o = 0; o < world && e == cudaSuccess; ++o)
