@@ -124,6 +124,25 @@ class ClockSampler(threading.Thread):
                 "reasons": [name for bit, name in self.REASONS.items() if self.bits & bit]}
 
 
+def bind_to_gpu_numa_node(index: int):
+    """Runs this process on the CPUs next to its GPU (NVML's affinity mask), so that the pinned host buffers it
+    allocates afterwards are placed in that socket's memory and host <-> device copies do not cross sockets.
+    Read-only with respect to the GPU; a no-op where NVML or the affinity call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        return sorted(cpus)
+    except Exception:
+        return None
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -252,6 +271,7 @@ def run_ours(args):
         args.gpus = world
     assert torch.cuda.is_available(), "bench.py --impl ours needs a GPU: the library has no CPU path"
     torch.cuda.set_device(local)
+    bind_to_gpu_numa_node(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)

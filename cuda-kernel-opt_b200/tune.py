@@ -41,15 +41,18 @@ def candidates(M: int, N: int, K: int) -> list[dict]:
                         out.append(dict(base, split_k=s, cluster_reduce=1))
                         out.append(dict(base, split_k=s, cluster_reduce=0))
         if M > 32:
-            # the swapped two-CTA pair: 256 weight rows per tile, activation rows in multiples of 32
+            # the swapped two-CTA pair: 256 weight rows per tile, activation rows in multiples of 32 (each CTA stages
+            # half of them); K over a cluster of 2 or 4 pairs when the pair tiles are few
             tm2 = -(-M // 32) * 32
-            per_stage = (128 + tm2 // 2) * 128
-            for stages in sorted({max(2, min(10, 200000 // per_stage)), max(2, min(10, 200000 // per_stage) - 2)}):
-                base = dict(swap_ab=1, cta_group=2, tile_m=tm2, tile_n=256, segment_dim_k=64, num_stages=stages, l2_hint=1,
-                            split_k=1, cluster_reduce=0)
-                out.append(base)
-                if -(-N // 256) < 74 and K >= 2048:
-                    out.append(dict(base, split_k=2, cluster_reduce=1))
+            for seg_k in (64, 128):
+                per_stage = (128 + tm2 // 2) * seg_k * 2
+                for stages in sorted({max(2, min(10, 200000 // per_stage)), max(2, min(10, 200000 // per_stage) - 2)}):
+                    base = dict(swap_ab=1, cta_group=2, tile_m=tm2, tile_n=256, segment_dim_k=seg_k, num_stages=stages, l2_hint=1,
+                                split_k=1, cluster_reduce=0)
+                    out.append(base)
+                    if -(-N // 256) < 74 and K >= 2048 and tm2 <= 128:
+                        for s in (2, 4):
+                            out.append(dict(base, split_k=s, cluster_reduce=1))
     tiles = []
     if M > 128:
         tiles += [dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=256, tile_n=128, cta_group=2)]
@@ -81,12 +84,16 @@ def load(path: str) -> list[dict]:
         return [json.loads(line) for line in f if line.strip()]
 
 
+LIBRARY = {"library": "torch.matmul"}   # the vendor library timed beside the candidates (never the best: it is not this kernel)
+
+
 def best(path: str, M: int, N: int, K: int, dtype: str = "f16") -> dict | None:
-    rows = [r for r in load(path) if r["shape"] == [M, N, K] and r["dtype"] == dtype and r["status"] == 0]
+    rows = [r for r in load(path) if r["shape"] == [M, N, K] and r["dtype"] == dtype and r["status"] == 0 and r["params"] != LIBRARY]
     return min(rows, key=lambda r: r["ms"])["params"] if rows else None
 
 
-def tune(M: int, N: int, K: int, dtype: str = "f16", out: str = "tune.jsonl", rounds: int = 12, inner: int = 3, log=print):
+def tune(M: int, N: int, K: int, dtype: str = "f16", out: str = "tune.jsonl", rounds: int = 12, inner: int = 3, log=print,
+         with_library: bool = False):
     import torch
     sys.path.insert(0, ROOT)
     from __graft_entry__ import load_package
@@ -109,6 +116,8 @@ def tune(M: int, N: int, K: int, dtype: str = "f16", out: str = "tune.jsonl", ro
         need = pkg.workspace_bytes(M, N, K, p)
         ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
         todo.append((ov, p, ws if need else None, []))
+    if with_library and key_of(LIBRARY) not in done:
+        todo.append((LIBRARY, None, None, []))      # torch.matmul in the same round-robin: a number for scale, not a candidate
     log(f"{len(todo)} candidates to time, {len(done)} already in {out}")
     # Operands that fit the L2 are rotated over R copies so every launch streams from HBM, and each
     # candidate's launches are replayed as one CUDA graph: a call from Python costs more host time than
@@ -121,12 +130,18 @@ def tune(M: int, N: int, K: int, dtype: str = "f16", out: str = "tune.jsonl", ro
     graphs = []
     for ov, p, ws, times in todo:
         with torch.cuda.stream(side):
-            pkg.gemm(A, Bs[0], None, D, 1.0, 0.0, p, workspace=ws)
+            if p is None:
+                torch.matmul(A, Bs[0].t())
+            else:
+                pkg.gemm(A, Bs[0], None, D, 1.0, 0.0, p, workspace=ws)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
                 for i in range(reps):
-                    pkg.gemm(A, Bs[i % rot], None, D, 1.0, 0.0, p, workspace=ws)
+                    if p is None:
+                        torch.matmul(A, Bs[i % rot].t())
+                    else:
+                        pkg.gemm(A, Bs[i % rot], None, D, 1.0, 0.0, p, workspace=ws)
         graphs.append(g)
     for _ in range(rounds):
         for (ov, p, ws, times), g in zip(todo, graphs):
@@ -156,6 +171,7 @@ if __name__ == "__main__":
     ap.add_argument("--dtype", choices=["f16", "bf16"], default="f16")
     ap.add_argument("--out", default="tune.jsonl")
     ap.add_argument("--rounds", type=int, default=12)
+    ap.add_argument("--with-library", action="store_true", help="time torch.matmul in the same round-robin, for scale")
     a = ap.parse_args()
-    b = tune(a.M, a.N, a.K, a.dtype, a.out, a.rounds)
+    b = tune(a.M, a.N, a.K, a.dtype, a.out, a.rounds, with_library=a.with_library)
     print(json.dumps({"shape": [a.M, a.N, a.K], "dtype": a.dtype, "best": b}))
