@@ -153,6 +153,20 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         // 4- and 8-GPU shards of the decode shape, 117 and 59 MB of weights; +6 % on the whole one,
         // 470 MB, where all SMs are busy for 70 us).
         p->overlap_launch = (N * K * 2 <= 160000000) ? 1 : 0;
+        if (M > 64 && few_tiles && N >= 256) {
+            // 65 - 128 activation rows and few tiles: the swapped pair (256 weight rows per tile, each CTA stages 128 of
+            // them and half of the activation rows) over a cluster of four pairs, and eight draining warps, which
+            // halve the staging and the reduce of the 128-column accumulator (tuner, interleaved: 128 x 7168: 27.1
+            // against 28.4 us for the 4-CTA form with four warps; 128 x 3584: 18.2 against 18.9 us)
+            p->tile_m = static_cast<int>((M + 31) / 32 * 32);
+            p->tile_n = 256;
+            p->cta_group = 2;
+            p->segment_dim_k = 64;
+            p->num_stages = 6;
+            p->num_consumer_warps = 8;
+            p->bar_step_rows_a = p->tile_m;
+            p->bar_step_rows_b = p->tile_n;
+        }
         return;
     }
     if (allow_swap && M > 64 && M <= 128 && n_tiles128 >= 112) {

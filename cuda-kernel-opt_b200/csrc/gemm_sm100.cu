@@ -795,16 +795,18 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     const int row4 = w.m0 + static_cast<int>(rank) * c.cta_rows_a + lane * 4;
                     const bool rows_ok = row4 < c.M;
                     const uint32_t my_rows = pbuf + static_cast<uint32_t>(lane) * 16u;
-                    // two columns per round: up to eight 16-byte remote loads in flight per lane
-                    for (int col0 = c.cl_rank * per + e; col0 < my_end; col0 += 2 * c.epi_warps) {
-                        float4 sum[2];
+                    // three columns per round: up to twelve 16-byte remote loads in flight per lane (a round trip through
+                    // distributed shared memory takes about a microsecond: the rounds, not the bytes, are the cost)
+                    constexpr int kRC = 3;
+                    for (int col0 = c.cl_rank * per + e; col0 < my_end; col0 += kRC * c.epi_warps) {
+                        float4 sum[kRC];
 #pragma unroll
-                        for (int cc = 0; cc < 2; ++cc) sum[cc] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        for (int cc = 0; cc < kRC; ++cc) sum[cc] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                         // slices are added in ascending order, four at a time
                         for (int base4 = 0; base4 < c.cl_split; base4 += 4) {
-                            float4 v[2][4];
+                            float4 v[kRC][4];
 #pragma unroll
-                            for (int cc = 0; cc < 2; ++cc) {
+                            for (int cc = 0; cc < kRC; ++cc) {
                                 const int col = col0 + cc * c.epi_warps;
                                 const uint32_t src = my_rows + static_cast<uint32_t>(col) * 512u;
 #pragma unroll
@@ -813,7 +815,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                         v[cc][i] = ld_shared_cluster_v4(mapa_shared(src, static_cast<uint32_t>((base4 + i) * CG) + rank));
                             }
 #pragma unroll
-                            for (int cc = 0; cc < 2; ++cc)
+                            for (int cc = 0; cc < kRC; ++cc)
 #pragma unroll
                                 for (int i = 0; i < 4; ++i)
                                     if (base4 + i < c.cl_split && col0 + cc * c.epi_warps < my_end) {
@@ -824,7 +826,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                     }
                         }
 #pragma unroll
-                        for (int cc = 0; cc < 2; ++cc) {
+                        for (int cc = 0; cc < kRC; ++cc) {
                             const int col = col0 + cc * c.epi_warps;
                             const int gcol = w.n0 + col;
                             if (!(rows_ok && col < my_end && gcol < c.N)) continue;

@@ -52,6 +52,12 @@ B200_HD void tile_origin(const Cfg &c, int t, Unit &w) {
         w.n0 = t * c.tile_n;
         return;
     }
+    if (c.tiles_n == 1) {
+        // one column of tiles (the skinny shapes with swapped roles): the grouped order is the plain row order
+        w.m0 = t * c.tile_m;
+        w.n0 = 0;
+        return;
+    }
     const int group_tile_count = c.tile_group_m * c.tiles_n;
     const int group_first_row = (t / group_tile_count) * c.tile_group_m;
     const int group_rows = sched_min(c.tiles_m - group_first_row, c.tile_group_m);

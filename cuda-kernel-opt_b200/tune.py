@@ -40,6 +40,8 @@ def candidates(M: int, N: int, K: int) -> list[dict]:
                     for s in (2, 4, 8):
                         out.append(dict(base, split_k=s, cluster_reduce=1))
                         out.append(dict(base, split_k=s, cluster_reduce=0))
+                        if tm >= 64:      # a wide accumulator: eight draining warps halve the staging and the reduce
+                            out.append(dict(base, split_k=s, cluster_reduce=1, num_consumer_warps=8))
         if M > 32:
             # the swapped two-CTA pair: 256 weight rows per tile, activation rows in multiples of 32 (each CTA stages
             # half of them); K over a cluster of 2 or 4 pairs when the pair tiles are few
@@ -53,6 +55,7 @@ def candidates(M: int, N: int, K: int) -> list[dict]:
                     if -(-N // 256) < 74 and K >= 2048 and tm2 <= 128:
                         for s in (2, 4):
                             out.append(dict(base, split_k=s, cluster_reduce=1))
+                            out.append(dict(base, split_k=s, cluster_reduce=1, num_consumer_warps=8))
     tiles = []
     if M > 128:
         tiles += [dict(tile_m=256, tile_n=256, cta_group=2), dict(tile_m=256, tile_n=128, cta_group=2)]
