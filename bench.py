@@ -607,7 +607,8 @@ def run_ours(args):
                  "mma_wait_data_per_stage": r[6] / it, "mma_wait_accumulator_per_unit": r[7] / tiles,
                  "mma_wait_accumulator_total": r[7], "mma_cycles_total": r[8],
                  "epilogue_cycles_per_unit": r[11] / tiles, "epilogue_wait_per_unit": r[10] / tiles,
-                 "epilogue_cycles_total": r[11], "epilogue_wait_total": r[10], "kernel_ns": r[15] - r[13]}
+                 "epilogue_cycles_total": r[11], "epilogue_wait_total": r[10], "kernel_ns": r[15] - r[13],
+                 "stages_started_before_last_rows_of_a": r[-2]}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only, bounded sample)
     cpu = None

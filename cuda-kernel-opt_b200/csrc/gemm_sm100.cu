@@ -48,11 +48,13 @@ __device__ int g_device_status[4];
 namespace {
 
 #ifdef B200_TIMELINE
-// Diagnostic build: 32 slots per CTA, slots 16.. hold %globaltimer stamps of set-up and role milestones.
-constexpr int kProfSlots = 32;
+// Diagnostic build: slots 16 .. 31 hold %globaltimer stamps of set-up and role milestones.
+constexpr int kProfSlots = 34;
+constexpr int kEarlySlot = 32;
 #define B200_TL(slot) do { if (PROF && prof) prof[slot] = static_cast<long long>(global_timer_ns()); } while (0)
 #else
-constexpr int kProfSlots = 16;
+constexpr int kProfSlots = 18;
+constexpr int kEarlySlot = 16;   // [kEarlySlot] stages whose first MMAs were issued before the last rows of A had landed, [+1] stages
 #define B200_TL(slot) do { } while (0)
 #endif
 constexpr int kMaxThreads = 384;  // (3 producer + 1 MMA + 8 epilogue warps) * 32: up to 168 registers per thread
@@ -178,6 +180,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int push_world = g.push_world, push_rank = g.push_rank, push_rows = g.push_rows;
     const int ld_cd = g.ld_cd;
     const bool swap_ab = g.swap_ab != 0;
+    const int a_halves = g.a_split ? 2 : 1;   // 2: the 128 rows of a tile are two 64-row MMA atoms, issued as their rows of A land
     const bool out_half = g.out_half != 0;   // C and D are fp16 (never with a workspace, tail or push path)
     // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage); bits 2 and 3: the
     // epilogue withholds its "slice staged" / "slice read" arrivals of the cluster reduce, so that those
@@ -593,6 +596,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint64_t a_kb_step = static_cast<uint64_t>((c.cta_rows_a * kSwizzleBytes) >> 4);
             const uint64_t b_box_step = static_cast<uint64_t>((b_box_rows * kSwizzleBytes) >> 4);   // one box of a K block
             const uint64_t b_sub_step = b_box_step * static_cast<uint64_t>(c.kblocks);             // one private sub-tile
+            const uint64_t a_half_step = static_cast<uint64_t>((64 * kSwizzleBytes) >> 4);           // rows 64.. of a K block
+            long long n_early = 0;
             int s = 0;
             uint32_t ph = 0, it = 0, tl = 0;
             uint32_t sb = bars;
@@ -614,38 +619,56 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const uint32_t d_base = tmem_base + acc * static_cast<uint32_t>(c.acc_cols);
                 uint32_t later_seg = 0;
                 for (int seg = w.seg_begin; ok && seg < w.seg_end; ++seg) {
-                    const long long tf = PROF ? clock64() : 0;
-                    for (int j = 0; ok && j < c.a_bars; ++j) ok = wait_all(sb + 8u * j, ph, c.budget, abort_flag, 400 + s * 32 + j);
-                    if (PROF) t_full += clock64() - tf;
-                    if (!ok) break;
-                    uint64_t sub_desc = b_desc;
-                    uint32_t d_addr = d_base;
-                    for (int t = 0; t < c.b_bars; ++t) {
-                        if (!merged) {
-                            const long long tb = PROF ? clock64() : 0;
-                            ok = wait_all(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
-                            if (PROF) t_full += clock64() - tb;
-                            if (!ok) break;
+                    // The A side of the reference's shift synchronisation (port_1.cu:406-433: a consumer waits per
+                    // fragment row and starts on the first rows while later ones are still being loaded): with two
+                    // 64-row atoms per tile (a_halves == 2) the upper atom's MMAs wait only for the barriers of the
+                    // row boxes of rows 0-63 and are issued before the lower rows have landed; the lower atom follows
+                    // when its boxes are there. With one 128-row atom every A barrier is waited first.
+                    int a_waited = 0;     // A barriers of this stage already waited for
+                    for (int mh = 0; ok && mh < a_halves; ++mh) {
+                        const long long tf = PROF ? clock64() : 0;
+                        // barriers that cover this half's row boxes: box b -> barrier min(b, a_priv)
+                        const int last_box = (a_halves == 2) ? ((mh + 1) * c.a_boxes / 2 - 1) : (c.a_boxes - 1);
+                        const int need = min(last_box, c.a_priv) + 1 < c.a_bars ? min(last_box, c.a_priv) + 1 : c.a_bars;
+                        if (PROF && mh == 1 && a_waited < c.a_bars) {
+                            // were the last rows of A still on their way when the upper atom's MMAs went out?
+                            const bool landed = mbar_try_wait(sb + 8u * static_cast<uint32_t>(c.a_bars - 1), ph);
+                            if (!__all_sync(0xffffffffu, landed)) ++n_early;
                         }
-                        tc_fence_after_sync();
-                        const bool priv = t < c.b_priv;
-                        const uint32_t idesc = priv ? c.idesc_chunk : c.idesc_res;
-                        const uint64_t b_kb_step = priv ? b_box_step : b_box_step * static_cast<uint64_t>(c.b_res_chunks);
-                        uint64_t da = a_desc, db = sub_desc;
-                        for (int kb = 0; kb < c.kblocks; ++kb) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                // +32 bytes per 16-element K step inside the 128-byte swizzle row
-                                if (issue)
-                                    umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc,
-                                                 (later_seg | static_cast<uint32_t>(kb) | static_cast<uint32_t>(i)) ? 1u : 0u);
+                        for (; ok && a_waited < need; ++a_waited)
+                            ok = wait_all(sb + 8u * a_waited, ph, c.budget, abort_flag, 400 + s * 32 + a_waited);
+                        if (PROF) t_full += clock64() - tf;
+                        if (!ok) break;
+                        uint64_t sub_desc = b_desc;
+                        uint32_t d_addr = d_base + static_cast<uint32_t>(mh * c.tile_n);
+                        for (int t = 0; t < c.b_bars; ++t) {
+                            if (!merged && mh == 0) {
+                                const long long tb = PROF ? clock64() : 0;
+                                ok = wait_all(sb + full_b_off + 8u * t, ph, c.budget, abort_flag, 500 + s * 32 + t);
+                                if (PROF) t_full += clock64() - tb;
+                                if (!ok) break;
                             }
-                            da += a_kb_step;
-                            db += b_kb_step;
+                            tc_fence_after_sync();
+                            const bool priv = t < c.b_priv;
+                            const uint32_t idesc = priv ? c.idesc_chunk : c.idesc_res;
+                            const uint64_t b_kb_step = priv ? b_box_step : b_box_step * static_cast<uint64_t>(c.b_res_chunks);
+                            uint64_t da = a_desc + static_cast<uint64_t>(mh) * a_half_step, db = sub_desc;
+                            for (int kb = 0; kb < c.kblocks; ++kb) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    // +32 bytes per 16-element K step inside the 128-byte swizzle row
+                                    if (issue)
+                                        umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc,
+                                                     (later_seg | static_cast<uint32_t>(kb) | static_cast<uint32_t>(i)) ? 1u : 0u);
+                                }
+                                da += a_kb_step;
+                                db += b_kb_step;
+                            }
+                            // a B^T sub-tile is free when the last atom has read it
+                            if (!merged && issuer && mh == a_halves - 1) commit_to<CG>(sb + empty_b_off + 8u * t, pair_mask);
+                            sub_desc += b_sub_step;
+                            d_addr += static_cast<uint32_t>(c.chunk_n);
                         }
-                        if (!merged && issuer) commit_to<CG>(sb + empty_b_off + 8u * t, pair_mask);
-                        sub_desc += b_sub_step;
-                        d_addr += static_cast<uint32_t>(c.chunk_n);
                     }
                     if (!ok) break;
                     if (issuer) commit_to<CG>(sb + empty_a_off, pair_mask);
@@ -670,6 +693,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 prof[7] = t_acc;
                 prof[8] = clock64() - t_begin;
                 prof[9] = it;
+                prof[kEarlySlot] = n_early;
+                prof[kEarlySlot + 1] = it;
             }
         }
         __syncwarp();
@@ -900,198 +925,210 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 if (lane < c.cl_split && !(dbg & 8)) mbar_arrive_release_cluster(mapa_shared(part_empty, static_cast<uint32_t>(lane * CG) + rank));
                 continue;
             }
-            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
-                if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
-                uint32_t r[32];
-                const bool wide = (col_end - c0) >= 32;
-                float4 part[8];
-                if (tail_peers > 0) {
-                    // The earlier slices' partials of this chunk, summed in ascending K order (this, the last slice, is
-                    // added below). Eight independent 16-byte loads per lane and slice are in flight at once, and the
-                    // first batch is issued ahead of the tensor-memory load; .cg: other SMs wrote them.
-                    const float4 *src = reinterpret_cast<const float4 *>(g_partial) +
-                                        (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
-                    const uint32_t step4 = static_cast<uint32_t>(tail_step) * tail_slot4;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) part[j] = __ldcg(src + j * 32);
-#pragma unroll 1
-                    for (int i = 1; i < tail_peers; ++i) {
-                        float4 v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + i * step4 + j * 32);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            part[j].x += v[j].x;
-                            part[j].y += v[j].y;
-                            part[j].z += v[j].z;
-                            part[j].w += v[j].w;
+            // With two 64-row atoms per tile the drain below runs once per atom: the lower atom's accumulator sits
+            // tile_n columns further in tensor memory and its rows 64 further in D (the names of the per-row
+            // values are re-declared for the atom, so the drain code is the one-atom code).
+            const int row_atom0 = row;
+            const size_t row_off_atom0 = row_off;
+            const uint32_t t_row_atom0 = t_row;
+            for (int mh = 0; mh < a_halves; ++mh) {
+                const int row = row_atom0 + mh * 64;
+                const bool row_ok = lane_has_row && row < c.M;
+                const size_t row_off = row_off_atom0 + static_cast<size_t>(mh * 64) * static_cast<size_t>(ld_cd);
+                const uint32_t t_row = t_row_atom0 + static_cast<uint32_t>(mh * c.tile_n);
+                for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+                    if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
+                    uint32_t r[32];
+                    const bool wide = (col_end - c0) >= 32;
+                    float4 part[8];
+                    if (tail_peers > 0) {
+                        // The earlier slices' partials of this chunk, summed in ascending K order (this, the last slice, is
+                        // added below). Eight independent 16-byte loads per lane and slice are in flight at once, and the
+                        // first batch is issued ahead of the tensor-memory load; .cg: other SMs wrote them.
+                        const float4 *src = reinterpret_cast<const float4 *>(g_partial) +
+                                            (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
+                        const uint32_t step4 = static_cast<uint32_t>(tail_step) * tail_slot4;
+    #pragma unroll
+                        for (int j = 0; j < 8; ++j) part[j] = __ldcg(src + j * 32);
+    #pragma unroll 1
+                        for (int i = 1; i < tail_peers; ++i) {
+                            float4 v[8];
+    #pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + i * step4 + j * 32);
+    #pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                part[j].x += v[j].x;
+                                part[j].y += v[j].y;
+                                part[j].z += v[j].z;
+                                part[j].w += v[j].w;
+                            }
                         }
                     }
-                }
-                if (wide) {
-                    tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
-                } else {
-                    uint32_t r16[16];
-                    tmem_ld_32x16(t_row + static_cast<uint32_t>(c0), r16);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = r16[j];
-#pragma unroll
-                    for (int j = 16; j < 32; ++j) r[j] = 0;
-                }
-                tmem_ld_wait();
-                if (e == 0 && lane == 0) B200_TL(18);
-                const int nvec = wide ? 8 : 4;
-                if (w.kind == 2) {
-                    // raw partial of this chunk into this unit's slot (a 16-column last chunk stores its zero padding too)
-                    float4 *dst = reinterpret_cast<float4 *>(g_partial) +
-                                  (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        dst[j * 32] = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
-                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                    continue;
-                }
-                if (tail_peers > 0) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        r[4 * j + 0] = __float_as_uint(part[j].x + __uint_as_float(r[4 * j + 0]));
-                        r[4 * j + 1] = __float_as_uint(part[j].y + __uint_as_float(r[4 * j + 1]));
-                        r[4 * j + 2] = __float_as_uint(part[j].z + __uint_as_float(r[4 * j + 2]));
-                        r[4 * j + 3] = __float_as_uint(part[j].w + __uint_as_float(r[4 * j + 3]));
+                    if (wide) {
+                        tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
+                    } else {
+                        uint32_t r16[16];
+                        tmem_ld_32x16(t_row + static_cast<uint32_t>(c0), r16);
+    #pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = r16[j];
+    #pragma unroll
+                        for (int j = 16; j < 32; ++j) r[j] = 0;
                     }
-                }
-                if (swap_ab) {
-                    // Transposed drain: this thread's row is a column of D and register j its row
-                    // w.n0 + c0 + j, so for every j the 32 lanes store 32 consecutive floats. The
-                    // pointers advance by one pitch per register: a handful of instructions per store
-                    // (the epilogue warps run alone on their schedulers, every instruction shows).
-                    if (row_ok) {
-                        const size_t pitch = to_partial ? static_cast<size_t>(c.M) : static_cast<size_t>(ld_cd);
-                        const size_t off0 = static_cast<size_t>(w.n0 + c0) * pitch + static_cast<size_t>(row);
-                        float *dst = out + off0;
-                        const float *csrc = gC + off0;
-                        const int valid = min(4 * nvec, c.N - (w.n0 + c0));
-                        if (out_half) {
-                            __half *dst16 = reinterpret_cast<__half *>(gD) + off0;
-                            const __half *c16 = reinterpret_cast<const __half *>(gC) + off0;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (j < 16 || wide) {
-                                    if (j < valid) {
-                                        float v = a_u * __uint_as_float(r[j]);
-                                        if (b_u != 0.0f) v += b_u * __half2float(*c16);
-                                        *dst16 = __float2half_rn(v);
+                    tmem_ld_wait();
+                    if (e == 0 && lane == 0) B200_TL(18);
+                    const int nvec = wide ? 8 : 4;
+                    if (w.kind == 2) {
+                        // raw partial of this chunk into this unit's slot (a 16-column last chunk stores its zero padding too)
+                        float4 *dst = reinterpret_cast<float4 *>(g_partial) +
+                                      (static_cast<uint32_t>(tail_slot) * tail_slot4 + tail_lane + static_cast<uint32_t>(c0 >> 5) * 256u);
+    #pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            dst[j * 32] = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
+                                                      __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        continue;
+                    }
+                    if (tail_peers > 0) {
+    #pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            r[4 * j + 0] = __float_as_uint(part[j].x + __uint_as_float(r[4 * j + 0]));
+                            r[4 * j + 1] = __float_as_uint(part[j].y + __uint_as_float(r[4 * j + 1]));
+                            r[4 * j + 2] = __float_as_uint(part[j].z + __uint_as_float(r[4 * j + 2]));
+                            r[4 * j + 3] = __float_as_uint(part[j].w + __uint_as_float(r[4 * j + 3]));
+                        }
+                    }
+                    if (swap_ab) {
+                        // Transposed drain: this thread's row is a column of D and register j its row
+                        // w.n0 + c0 + j, so for every j the 32 lanes store 32 consecutive floats. The
+                        // pointers advance by one pitch per register: a handful of instructions per store
+                        // (the epilogue warps run alone on their schedulers, every instruction shows).
+                        if (row_ok) {
+                            const size_t pitch = to_partial ? static_cast<size_t>(c.M) : static_cast<size_t>(ld_cd);
+                            const size_t off0 = static_cast<size_t>(w.n0 + c0) * pitch + static_cast<size_t>(row);
+                            float *dst = out + off0;
+                            const float *csrc = gC + off0;
+                            const int valid = min(4 * nvec, c.N - (w.n0 + c0));
+                            if (out_half) {
+                                __half *dst16 = reinterpret_cast<__half *>(gD) + off0;
+                                const __half *c16 = reinterpret_cast<const __half *>(gC) + off0;
+    #pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (j < 16 || wide) {
+                                        if (j < valid) {
+                                            float v = a_u * __uint_as_float(r[j]);
+                                            if (b_u != 0.0f) v += b_u * __half2float(*c16);
+                                            *dst16 = __float2half_rn(v);
+                                        }
+                                        dst16 += pitch;
+                                        c16 += pitch;
                                     }
-                                    dst16 += pitch;
-                                    c16 += pitch;
                                 }
-                            }
-                        } else if (b_u == 0.0f) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (j < 16 || wide) {
-                                    if (j < valid) *dst = a_u * __uint_as_float(r[j]);
-                                    dst += pitch;
+                            } else if (b_u == 0.0f) {
+    #pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (j < 16 || wide) {
+                                        if (j < valid) *dst = a_u * __uint_as_float(r[j]);
+                                        dst += pitch;
+                                    }
                                 }
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (j < 16 || wide) {
-                                    if (j < valid) *dst = a_u * __uint_as_float(r[j]) + b_u * __ldg(csrc);
-                                    dst += pitch;
-                                    csrc += pitch;
+                            } else {
+    #pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (j < 16 || wide) {
+                                        if (j < valid) *dst = a_u * __uint_as_float(r[j]) + b_u * __ldg(csrc);
+                                        dst += pitch;
+                                        csrc += pitch;
+                                    }
                                 }
                             }
                         }
-                    }
-                } else if (out_half) {
-                    // fp16 C and D: four values per 8-byte store
-                    if (row_ok) {
-                        uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(gD) + row_off + c0);
-                        const uint2 *csrc = reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + row_off + c0);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
-                                float4 v;
-                                v.x = a_u * __uint_as_float(r[4 * j + 0]);
-                                v.y = a_u * __uint_as_float(r[4 * j + 1]);
-                                v.z = a_u * __uint_as_float(r[4 * j + 2]);
-                                v.w = a_u * __uint_as_float(r[4 * j + 3]);
-                                if (b_u != 0.0f) {
-                                    const uint2 cv = __ldg(csrc + j);
-                                    const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
-                                    const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
-                                    v.x += b_u * c01.x;
-                                    v.y += b_u * c01.y;
-                                    v.z += b_u * c23.x;
-                                    v.w += b_u * c23.y;
+                    } else if (out_half) {
+                        // fp16 C and D: four values per 8-byte store
+                        if (row_ok) {
+                            uint2 *dst = reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(gD) + row_off + c0);
+                            const uint2 *csrc = reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + row_off + c0);
+    #pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
+                                    float4 v;
+                                    v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                                    v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                                    v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                                    v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                                    if (b_u != 0.0f) {
+                                        const uint2 cv = __ldg(csrc + j);
+                                        const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
+                                        const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
+                                        v.x += b_u * c01.x;
+                                        v.y += b_u * c01.y;
+                                        v.z += b_u * c23.x;
+                                        v.w += b_u * c23.y;
+                                    }
+                                    const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+                                    uint2 o;
+                                    o.x = *reinterpret_cast<const uint32_t *>(&h01);
+                                    o.y = *reinterpret_cast<const uint32_t *>(&h23);
+                                    dst[j] = o;
                                 }
-                                const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
-                                uint2 o;
-                                o.x = *reinterpret_cast<const uint32_t *>(&h01);
-                                o.y = *reinterpret_cast<const uint32_t *>(&h23);
-                                dst[j] = o;
                             }
                         }
-                    }
-                } else if (c.epi_mode == 0 || !wide) {
-                    if (row_ok) {
-                        float4 *dst = reinterpret_cast<float4 *>(out + row_off + c0);
+                    } else if (c.epi_mode == 0 || !wide) {
+                        if (row_ok) {
+                            float4 *dst = reinterpret_cast<float4 *>(out + row_off + c0);
+                            const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
+    #pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
+                                    float4 v;
+                                    v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                                    v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                                    v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                                    v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                                    if (b_u != 0.0f) {
+                                        const float4 cv = __ldg(csrc + j);
+                                        v.x += b_u * cv.x;
+                                        v.y += b_u * cv.y;
+                                        v.z += b_u * cv.z;
+                                        v.w += b_u * cv.w;
+                                    }
+                                    dst[j] = v;
+                                }
+                            }
+                        }
+                    } else {
+                        // registers -> 128-byte-swizzled shared memory -> one TMA store of 32 x 32 fp32
+                        const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
+                        if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
+                        __syncwarp();
                         const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
-#pragma unroll
+    #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            if (j < nvec && w.n0 + c0 + 4 * j < c.N) {
-                                float4 v;
-                                v.x = a_u * __uint_as_float(r[4 * j + 0]);
-                                v.y = a_u * __uint_as_float(r[4 * j + 1]);
-                                v.z = a_u * __uint_as_float(r[4 * j + 2]);
-                                v.w = a_u * __uint_as_float(r[4 * j + 3]);
-                                if (b_u != 0.0f) {
-                                    const float4 cv = __ldg(csrc + j);
-                                    v.x += b_u * cv.x;
-                                    v.y += b_u * cv.y;
-                                    v.z += b_u * cv.z;
-                                    v.w += b_u * cv.w;
-                                }
-                                dst[j] = v;
+                            float4 v;
+                            v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                            v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                            v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                            v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                            if (b_u != 0.0f && row_ok && w.n0 + c0 + 4 * j < c.N) {
+                                const float4 cv = __ldg(csrc + j);
+                                v.x += b_u * cv.x;
+                                v.y += b_u * cv.y;
+                                v.z += b_u * cv.z;
+                                v.w += b_u * cv.w;
                             }
+                            const uint32_t addr = buf + static_cast<uint32_t>(lane) * 128u + static_cast<uint32_t>((j ^ (lane & 7)) * 16);
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+                                         "f"(v.w)
+                                         : "memory");
                         }
-                    }
-                } else {
-                    // registers -> 128-byte-swizzled shared memory -> one TMA store of 32 x 32 fp32
-                    const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
-                    if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
-                    __syncwarp();
-                    const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float4 v;
-                        v.x = a_u * __uint_as_float(r[4 * j + 0]);
-                        v.y = a_u * __uint_as_float(r[4 * j + 1]);
-                        v.z = a_u * __uint_as_float(r[4 * j + 2]);
-                        v.w = a_u * __uint_as_float(r[4 * j + 3]);
-                        if (b_u != 0.0f && row_ok && w.n0 + c0 + 4 * j < c.N) {
-                            const float4 cv = __ldg(csrc + j);
-                            v.x += b_u * cv.x;
-                            v.y += b_u * cv.y;
-                            v.z += b_u * cv.z;
-                            v.w += b_u * cv.w;
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&g.map_d, buf, w.n0 + c0, w.m0 + static_cast<int>(rank) * c.cta_rows_a + q * 32);
+                            tma_store_commit();
                         }
-                        const uint32_t addr = buf + static_cast<uint32_t>(lane) * 128u + static_cast<uint32_t>((j ^ (lane & 7)) * 16);
-                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
-                                     "f"(v.w)
-                                     : "memory");
+                        ++store_idx;
                     }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&g.map_d, buf, w.n0 + c0, w.m0 + static_cast<int>(rank) * c.cta_rows_a + q * 32);
-                        tma_store_commit();
-                    }
-                    ++store_idx;
                 }
-            }
+            }   // atoms
             if (w.kind == 2) {
                 // this warp's part of the partial is complete: make it visible, then say so
                 __threadfence();

@@ -45,6 +45,9 @@ struct alignas(64) GemmArgs {
     int cl_split;       // > 1: cluster size; the CTAs of a cluster take the K slices of one tile and reduce through
                         // distributed shared memory (split_k is 1 then: no workspace)
     int overlap_launch; // 1: set-up runs before griddepcontrol.wait (launched with programmatic stream serialisation)
+    int a_split;        // 1: a 128-row tile is two 64-row MMA atoms (the A side of the shift synchronisation): the upper
+                        // atom's MMAs are issued when the row boxes of rows 0-63 have landed; accumulators of the two
+                        // atoms sit side by side in tensor memory (acc_cols = 2 * tile_n)
     int out_half;       // 1: C and D hold fp16 (the reference's DT_ACC = half instances); accumulation stays fp32
     int swap_ab;        // 1: M/N above are those of the transposed problem and the tile is stored transposed (D[col][row])
     // split-K across GPUs with the reduce-scatter fused into the epilogue ("push" mode, world > 0):

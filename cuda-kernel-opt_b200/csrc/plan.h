@@ -51,6 +51,8 @@ struct Plan {
     int swap = 0;                         // 1: the kernel computes D^T = B^T * A^T (tile_m spans N, tile_n spans M)
     int cluster_reduce = 0;               // 1: the split_k slices of a tile run in one thread-block cluster and meet
                                           //    in distributed shared memory (no workspace, no second kernel)
+    int a_split = 0;                      // 1: a 128-row tile is issued as two 64-row MMA atoms so that the upper rows'
+                                          //    MMAs start before the lower rows of A have landed (A-side shift)
 };
 
 // Tail split (tail_split = 1): the tiles that do not fill a wave of the persistent grid are cut along K.
@@ -210,9 +212,20 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     }
     if (p.a_bars > kMaxSubBars || p.b_bars > kMaxSubBars) return p;
 
+    // A-side shift synchronisation that starts MMAs early (the reference's per-fragment-row waits, port_1.cu:406-433):
+    // a one-CTA 128-row tile whose A buffer is released in steps of at most 64 rows is issued as two 64-row atoms; the
+    // upper atom waits only for the barriers of rows 0-63. Its accumulators sit side by side in tensor memory, so the
+    // tile may be at most 128 columns wide (2 atoms x 2 slots x 128 = 512 columns); wider tiles, pairs, swapped roles
+    // and K slices keep the one-atom form, where the A steps change the copy granularity only.
+    if (cg == 1 && p.tile_m == 128 && !p.swap && p.a_boxes > 1 && p.a_box_rows <= 64 && 64 % p.a_box_rows == 0 &&
+        p.tile_n <= 128 && p.split_k == 1) {
+        p.a_split = 1;
+        p.mma_m = 64;
+    }
+
     // Tensor memory: two accumulator slots so the drain of tile i overlaps the MMAs of tile i+1.
     // M=64 per CTA keeps the 16-lanes-per-quarter layout of one 64-row atom.
-    p.acc_cols = p.tile_n;
+    p.acc_cols = p.a_split ? 2 * p.tile_n : p.tile_n;
     p.tmem_cols = pow2_at_least(2 * p.acc_cols);
     if (p.tmem_cols > kTmemColumns) return p;
 

@@ -49,7 +49,11 @@ enum { B200_F16 = 0, B200_BF16 = 1 };
  * bar_steps_a/b      number of leading sub-tiles of the A / B^T stage buffer with a private "full"
  *                    barrier; the rest share one residual barrier (port_2.cu:627-630)
  * bar_step_rows_a/b  rows of A / rows of B^T (= columns of the tile) per sub-tile; equal to the
- *                    tile extent = no sub-tiles = shift synchronisation off (port_1.cu:508-509)
+ *                    tile extent = no sub-tiles = shift synchronisation off (port_1.cu:508-509). Every B^T
+ *                    sub-tile has its own MMAs, issued as it lands. A one-CTA 128 x (<= 128) tile with
+ *                    bar_step_rows_a <= 64 is issued as two 64-row MMA atoms, the upper one as soon as the
+ *                    barriers of rows 0-63 are complete (the reference's per-fragment-row start,
+ *                    port_1.cu:406-433); in every other form the A steps set the copy granularity only
  * tile_group_m       tile rows per L2 rasterisation group (port_0.cu:201-210)
  * num_stages         depth of the shared-memory ring
  * num_producer_warps 1 = one warp issues the A and the B^T copies; >= 2 = separate A and B^T
@@ -277,12 +281,14 @@ void b200_set_wait_budget_ns(uint64_t ns);
  * write b200_profile_slots() int64 counters each (clock64 cycles) into it: [0..2] A-producer {cycles waiting for free
  * stages, cycles in loop, stages filled}, [3..5] the same for a separate B^T producer, [6..9] MMA
  * thread {cycles waiting for data, cycles waiting for a free accumulator, cycles in loop, stages},
- * [10..12] first epilogue warp {cycles waiting for a finished tile, cycles in loop, tiles}. The
- * reference only times whole launches with CUDA events (matmul_shmem_tc_async.cu:787-795). */
+ * [10..12] first epilogue warp {cycles waiting for a finished tile, cycles in loop, tiles}, [13..15] %globaltimer
+ * (ns) at kernel entry, after set-up and at exit, [16..17] A-side shift synchronisation {pipeline stages whose first
+ * MMAs were issued before the stage's last rows of A had landed, stages}. The reference only times whole launches
+ * with CUDA events (matmul_shmem_tc_async.cu:787-795). */
 void b200_set_profile_buffer(void *device_ptr, int blocks);
-/* int64 slots per CTA in that buffer: 16, with [13..15] = %globaltimer (ns) at kernel entry, after
- * set-up and at exit. A diagnostic build of the library (-DB200_TIMELINE) has 32: [16..31] are
- * %globaltimer stamps of set-up and role milestones (cuda-kernel-opt_b200/timeline.py prints them). */
+/* int64 slots per CTA in that buffer: 18. A diagnostic build of the library (-DB200_TIMELINE) has 34: there
+ * [16..31] are %globaltimer stamps of set-up and role milestones (cuda-kernel-opt_b200/timeline.py prints them) and
+ * the A-side shift pair sits at [32..33]. */
 int b200_profile_slots(void);
 
 const char *b200_status_string(int status);

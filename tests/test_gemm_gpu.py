@@ -228,6 +228,44 @@ def test_swapped_roles_and_cluster_reduce(pkg, cuda, oracle):
         assert ok, (m, n, k, p.as_dict(), msg)
 
 
+def test_a_side_shift_starts_before_the_last_rows_of_a_have_landed(pkg, cuda, oracle):
+    """The A side of the shift synchronisation (the reference's per-fragment-row waits, port_1.cu:406-433): a one-CTA
+    128 x (<= 128) tile whose A buffer is released in steps of <= 64 rows is issued as two 64-row MMA atoms, the upper
+    one as soon as the barriers of rows 0-63 are complete. Parity against the oracle for the reference's three
+    granularities, and the in-kernel counters must show stages whose first MMAs went out before the stage's last rows
+    of A had landed - when the upper rows have barriers of their own; with every row box on the shared residual
+    barrier (bar_steps_a = 0) there is nothing to start early on, and the counter must say so."""
+    torch = cuda
+    m, n, k = 384, 512, 4096
+    A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 97)
+    want = oracle.gemm(A, Bt, Cm, 1.0, 1.0)
+    dA, dB, dC = to_device(torch, A, pkg.F16), to_device(torch, Bt, pkg.F16), torch.from_numpy(Cm).cuda()
+    slots = pkg.profile_slots()
+    assert slots >= 18
+    for step_a, steps_a, tile_n, extra in ((16, 4, 128, {}), (16, 8, 128, {}), (32, 2, 128, dict(bar_step_rows_b=64, bar_steps_b=1)),
+                                           (64, 1, 64, {}), (64, 2, 128, dict(segment_dim_k=128)), (64, 0, 128, {})):
+        ov = dict(tile_m=128, tile_n=tile_n, num_stages=2, num_producer_warps=2, bar_step_rows_a=step_a, bar_steps_a=steps_a, **extra)
+        got = run_gemm(pkg, torch, pkg.F16, A, Bt, Cm, 1.0, 1.0, **ov)
+        ok, msg = tolerance_ok(got, want, k, 2.0)
+        assert ok, (ov, msg)
+        p = pkg.default_params(m, n, k, pkg.F16, **ov)
+        prof = torch.zeros((4, slots), dtype=torch.int64, device="cuda")
+        D = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        pkg.lib().b200_set_profile_buffer(prof.data_ptr(), 4)
+        try:
+            pkg.gemm(dA, dB, dC, D, 1.0, 1.0, p)
+            torch.cuda.synchronize()
+        finally:
+            pkg.lib().b200_set_profile_buffer(None, 0)
+        assert pkg.device_status()[0] == pkg.OK
+        early, stages = int(prof[0, slots - 2]), int(prof[0, slots - 1])
+        assert stages == (k // ov.get("segment_dim_k", 64)) * len(range(0, (m // 128) * (n // tile_n), pkg.num_sms()))   # CTA 0's tiles x K segments
+        if steps_a * step_a >= 64:
+            assert early >= stages // 4, (ov, early, stages)       # the upper atom really started early
+        else:
+            assert early == 0, (ov, early, stages)                 # rows 0-63 hang on the residual barrier: nothing to start early on
+
+
 def test_cuda_graph_capture_and_overlapped_launch(pkg, cuda, oracle):
     """The call is capture-safe: a chain of GEMMs (plain, split-K with workspace, cluster split-K) recorded
     into one CUDA graph and replayed gives the oracle's results; overlap_launch = 1 (programmatic dependent
