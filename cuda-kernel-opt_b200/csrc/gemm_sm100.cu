@@ -630,15 +630,15 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         // barriers that cover this half's row boxes: box b -> barrier min(b, a_priv)
                         const int last_box = (a_halves == 2) ? ((mh + 1) * c.a_boxes / 2 - 1) : (c.a_boxes - 1);
                         const int need = min(last_box, c.a_priv) + 1 < c.a_bars ? min(last_box, c.a_priv) + 1 : c.a_bars;
-                        if (PROF && mh == 1 && a_waited < c.a_bars) {
-                            // were the last rows of A still on their way when the upper atom's MMAs went out?
-                            const bool landed = mbar_try_wait(sb + 8u * static_cast<uint32_t>(c.a_bars - 1), ph);
-                            if (!__all_sync(0xffffffffu, landed)) ++n_early;
-                        }
                         for (; ok && a_waited < need; ++a_waited)
                             ok = wait_all(sb + 8u * a_waited, ph, c.budget, abort_flag, 400 + s * 32 + a_waited);
                         if (PROF) t_full += clock64() - tf;
                         if (!ok) break;
+                        if (PROF && a_halves == 2 && mh == 0 && a_waited < c.a_bars) {
+                            // are the last rows of A still on their way as the upper atom's first MMA goes out?
+                            const bool landed = mbar_try_wait(sb + 8u * static_cast<uint32_t>(c.a_bars - 1), ph);
+                            if (!__all_sync(0xffffffffu, landed)) ++n_early;
+                        }
                         uint64_t sub_desc = b_desc;
                         uint32_t d_addr = d_base + static_cast<uint32_t>(mh * c.tile_n);
                         for (int t = 0; t < c.b_bars; ++t) {
