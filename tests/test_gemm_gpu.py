@@ -597,11 +597,13 @@ def test_cluster_reduce_waits_time_out_when_arrivals_are_withheld(pkg, cuda, ora
     700: every peer has read this CTA's slice) are bounded too: with the arrivals withheld (diagnostic
     bits 2 / 3: a flag that nothing sets) and a 50 us budget each launch ends by itself with a
     DEVICE_TIMEOUT record naming that barrier, and the next normal launch is correct."""
-    m, n, k = 16, 1024, 4096
+    m, n, k = 16, 512, 4096
     A, Bt, _ = inputs(pkg, pkg.BF16, m, n, k, 91)
     dA, dB = to_device(cuda, A, pkg.BF16), to_device(cuda, Bt, pkg.BF16)
     D = cuda.empty((m, n), dtype=cuda.float32, device="cuda")
-    base = dict(swap_ab=1, tile_m=16, tile_n=128, split_k=4, cluster_reduce=1, num_sms=8)    # 8 tiles on 2 clusters of 4
+    # 4 tiles on 2 clusters of 4: two tiles per CTA, so the two accumulator slots never make the MMA warp wait and
+    # the withheld arrival is the only wait of the launch that can run out
+    base = dict(swap_ab=1, tile_m=16, tile_n=128, split_k=4, cluster_reduce=1, num_sms=8)
     for bit, want_bar in ((4, 701), (8, 700)):
         p = pkg.default_params(m, n, k, pkg.BF16, diagnostic=bit, **base)
         assert pkg.validate(m, n, k, pkg.BF16, p) == pkg.OK
