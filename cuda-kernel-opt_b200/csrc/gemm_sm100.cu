@@ -26,9 +26,8 @@
 // Skinny (decode) shapes: with swapped roles the kernel computes D^T = B^T * A^T, so B^T fills the
 // 128-row side of the MMA and the few rows of A its N side; the epilogue then writes the
 // accumulator transposed. When a shape has few tiles, the K slices of one tile run as the CTAs
-// (or CTA pairs) of a thread-block cluster: every CTA stores its raw accumulator straight into the
-// shared memory of the CTAs that own the columns (one-way remote stores), and every owner sums its
-// share of the columns from its own shared memory (no workspace, no second kernel).
+// (or CTA pairs) of a thread-block cluster and are summed through distributed shared memory in
+// the epilogue (no workspace, no second kernel).
 //
 // Every wait is bounded: when its budget runs out the CTA records {code, block, barrier, phase}
 // in a device status word, raises a block-wide abort flag so all roles leave their loops, frees
@@ -768,14 +767,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint32_t tail_slot4 = tail_chunks * 1024u;                                // float4 per slot (offsets fit 32 bits)
             const uint32_t tail_lane = static_cast<uint32_t>(q) * tail_chunks * 256u + static_cast<uint32_t>(lane);
             if (c.cl_split > 1) {
-                // ---- K slices of this tile live in the CTAs of the cluster (transposed drain only). Every CTA of the
-                // cluster owns a share of the tile's columns (`per` consecutive ones) and has room for that share from
-                // every slice: [slice][column of the share][128 rows] fp32.
-                // A: raw accumulator -> the owners' shared memory, with one-way remote stores (fire and forget: no
-                //    round trip, unlike loads through distributed shared memory); tell every CTA.
+                // ---- K slices of this tile live in the CTAs of the cluster (transposed drain only).
+                // A: raw accumulator -> this CTA's shared memory as [column][row]; tell every CTA.
                 const uint32_t pbuf = base + static_cast<uint32_t>(off_epi);
-                const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
-                ok = wait_all<true>(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the owners have reduced the previous tile
+                ok = wait_all<true>(part_empty, (tl & 1u) ^ 1u, c.budget, abort_flag, 700);  // the peers have read the previous tile
                 if (!ok) break;
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                     uint32_t r[32];
@@ -791,26 +786,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     }
                     tmem_ld_wait();
                     if (lane_has_row) {
-                        // column c0 + j belongs to owner (c0 + j) / per; walking j, owner and column-in-share advance
-                        // without divisions. This CTA's slice of the owner's area starts at cl_rank * per columns.
-                        int owner = c0 / per;
-                        int lcol = c0 - owner * per;
-                        uint32_t dst = mapa_shared(pbuf + static_cast<uint32_t>((c.cl_rank * per + lcol) * 128 + row_in_cta) * 4u,
-                                                   static_cast<uint32_t>(owner * CG) + rank);
+                        // columns beyond the tile are never read back: store the whole 16 or 32 without tests
+                        const uint32_t dst = pbuf + static_cast<uint32_t>(c0 * 128 + row_in_cta) * 4u;
+                        const bool wide32 = col_end - c0 >= 32;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (c0 + j < col_end) st_shared_cluster_b32(dst, r[j]);
-                            dst += 512u;
-                            if (++lcol == per) {           // next owner: same offset in its area, column 0 of this CTA's slice
-                                lcol = 0;
-                                ++owner;
-                                dst = mapa_shared(pbuf + static_cast<uint32_t>(c.cl_rank * per * 128 + row_in_cta) * 4u,
-                                                  static_cast<uint32_t>((owner < c.cl_split ? owner : 0) * CG) + rank);
-                            }
-                        }
+                        for (int j = 0; j < 32; ++j)
+                            if (j < 16 || wide32)
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + static_cast<uint32_t>(j) * 512u), "r"(r[j]) : "memory");
                     }
                 }
-                // The lanes' (remote) shared-memory writes are ordered before the arrivals below by the warp
+                // The lanes' shared-memory writes are ordered before the arrivals below by the warp
                 // barrier, and the arrivals release at cluster scope (cumulative): no fence needed.
                 tc_fence_before_sync();
                 __syncwarp();
@@ -821,57 +806,117 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 // the peers of this CTA: the CTA with the same rank in its pair, in every slice of the cluster
                 if (lane < c.cl_split && !(dbg & 4)) mbar_arrive_release_cluster(mapa_shared(part_full, static_cast<uint32_t>(lane * CG) + rank));
                 if (e == 0 && lane == 0) B200_TL(29);
-                // B: when every slice has arrived, this CTA sums its share of the columns from its own shared memory,
-                // slices in ascending order (the order of the workspace form), and writes D: a warp per column, a
-                // lane per four consecutive rows (the kernel's M is a multiple of 4), 16-byte loads and stores.
+                // B: when all slices are staged, this CTA sums its share of the tile's columns over the
+                // cluster in slice order (the order of the workspace form) and writes D.
                 ok = wait_all<true>(part_full, tl & 1u, c.budget, abort_flag, 701);
                 if (!ok) break;
                 if (e == 0 && lane == 0) B200_TL(30);
-                {
-                    const int my_cols = min(per, c.tile_n - c.cl_rank * per);      // columns of this CTA's share (may be <= 0)
-                    const int rows4 = c.mma_m / 4;                                   // lanes that hold rows: 32 or 16
-                    const int cols_per_pass = 32 / rows4;                            // 64-row tiles: two columns per warp pass
-                    const int sub = lane / rows4, l4 = lane - sub * rows4;
-                    const int row4 = w.m0 + static_cast<int>(rank) * c.cta_rows_a + l4 * 4;
+                const int per = (c.tile_n + c.cl_split - 1) / c.cl_split;
+                const int my_end = min(c.tile_n, (c.cl_rank + 1) * per);
+                if (c.mma_m == 128) {
+                    // 128-row slices: a warp takes whole columns of the tile (column first + e, then every
+                    // epi_warps-th), a lane four consecutive rows, so a column costs one 16-byte remote load
+                    // per slice and one 16-byte store per lane (the kernel's M is a multiple of 4).
+                    const int row4 = w.m0 + static_cast<int>(rank) * c.cta_rows_a + lane * 4;
                     const bool rows_ok = row4 < c.M;
-                    for (int lc = e * cols_per_pass + sub; lc < my_cols; lc += c.epi_warps * cols_per_pass) {
-                        const uint32_t src = pbuf + static_cast<uint32_t>(lc * 128 + l4 * 4) * 4u;
-                        float4 sum = ld_shared_v4(src);
-                        for (int sl = 1; sl < c.cl_split; ++sl) {
-                            const float4 v = ld_shared_v4(src + static_cast<uint32_t>(sl * per) * 512u);
-                            sum.x += v.x;
-                            sum.y += v.y;
-                            sum.z += v.z;
-                            sum.w += v.w;
+                    const uint32_t my_rows = pbuf + static_cast<uint32_t>(lane) * 16u;
+                    // three columns per round: up to twelve 16-byte remote loads in flight per lane (a round trip through
+                    // distributed shared memory takes about a microsecond: the rounds, not the bytes, are the cost)
+                    constexpr int kRC = 3;
+                    for (int col0 = c.cl_rank * per + e; col0 < my_end; col0 += kRC * c.epi_warps) {
+                        float4 sum[kRC];
+#pragma unroll
+                        for (int cc = 0; cc < kRC; ++cc) sum[cc] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        // slices are added in ascending order, four at a time
+                        for (int base4 = 0; base4 < c.cl_split; base4 += 4) {
+                            float4 v[kRC][4];
+#pragma unroll
+                            for (int cc = 0; cc < kRC; ++cc) {
+                                const int col = col0 + cc * c.epi_warps;
+                                const uint32_t src = my_rows + static_cast<uint32_t>(col) * 512u;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    if (base4 + i < c.cl_split && col < my_end)
+                                        v[cc][i] = ld_shared_cluster_v4(mapa_shared(src, static_cast<uint32_t>((base4 + i) * CG) + rank));
+                            }
+#pragma unroll
+                            for (int cc = 0; cc < kRC; ++cc)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    if (base4 + i < c.cl_split && col0 + cc * c.epi_warps < my_end) {
+                                        sum[cc].x += v[cc][i].x;
+                                        sum[cc].y += v[cc][i].y;
+                                        sum[cc].z += v[cc][i].z;
+                                        sum[cc].w += v[cc][i].w;
+                                    }
                         }
-                        const int gcol = w.n0 + c.cl_rank * per + lc;
-                        if (!(rows_ok && gcol < c.N)) continue;
-                        const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row4);
-                        float4 val = make_float4(alpha * sum.x, alpha * sum.y, alpha * sum.z, alpha * sum.w);
-                        if (out_half) {
-                            if (beta != 0.0f) {
-                                const uint2 cv = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + off);
-                                const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
-                                const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
-                                val.x += beta * c01.x;
-                                val.y += beta * c01.y;
-                                val.z += beta * c23.x;
-                                val.w += beta * c23.y;
+#pragma unroll
+                        for (int cc = 0; cc < kRC; ++cc) {
+                            const int col = col0 + cc * c.epi_warps;
+                            const int gcol = w.n0 + col;
+                            if (!(rows_ok && col < my_end && gcol < c.N)) continue;
+                            const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row4);
+                            float4 val = make_float4(alpha * sum[cc].x, alpha * sum[cc].y, alpha * sum[cc].z, alpha * sum[cc].w);
+                            if (out_half) {
+                                if (beta != 0.0f) {
+                                    const uint2 cv = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + off);
+                                    const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
+                                    const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
+                                    val.x += beta * c01.x;
+                                    val.y += beta * c01.y;
+                                    val.z += beta * c23.x;
+                                    val.w += beta * c23.y;
+                                }
+                                const __half2 h01 = __floats2half2_rn(val.x, val.y), h23 = __floats2half2_rn(val.z, val.w);
+                                uint2 o;
+                                o.x = *reinterpret_cast<const uint32_t *>(&h01);
+                                o.y = *reinterpret_cast<const uint32_t *>(&h23);
+                                *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(gD) + off) = o;
+                            } else {
+                                if (beta != 0.0f) {
+                                    const float4 cv = __ldg(reinterpret_cast<const float4 *>(gC + off));
+                                    val.x += beta * cv.x;
+                                    val.y += beta * cv.y;
+                                    val.z += beta * cv.z;
+                                    val.w += beta * cv.w;
+                                }
+                                *reinterpret_cast<float4 *>(gD + off) = val;
                             }
-                            const __half2 h01 = __floats2half2_rn(val.x, val.y), h23 = __floats2half2_rn(val.z, val.w);
-                            uint2 o;
-                            o.x = *reinterpret_cast<const uint32_t *>(&h01);
-                            o.y = *reinterpret_cast<const uint32_t *>(&h23);
-                            *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(gD) + off) = o;
-                        } else {
-                            if (beta != 0.0f) {
-                                const float4 cv = __ldg(reinterpret_cast<const float4 *>(gC + off));
-                                val.x += beta * cv.x;
-                                val.y += beta * cv.y;
-                                val.z += beta * cv.z;
-                                val.w += beta * cv.w;
+                        }
+                    }
+                }
+                // 64-row slices (16 lanes of a quarter hold rows): a thread per row
+                // this thread's row of column 0, as an address in this CTA; mapa turns it into a peer's
+                const uint32_t my_row0 = pbuf + static_cast<uint32_t>(row_in_cta) * 4u;
+                // two columns per round: their 2 x cl_split remote loads are in flight together
+                for (int col0 = c.cl_rank * per + half; c.mma_m != 128 && col0 < my_end; col0 += 2 * halves) {
+                    float v[2][8];
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int col = col0 + cc * halves;
+#pragma unroll
+                        for (int sl = 0; sl < 8; ++sl)
+                            if (sl < c.cl_split && col < my_end)
+                                v[cc][sl] = ld_shared_cluster_f32(mapa_shared(my_row0 + static_cast<uint32_t>(col) * 512u, static_cast<uint32_t>(sl * CG) + rank));
+                    }
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int col = col0 + cc * halves;
+                        const int gcol = w.n0 + col;
+                        if (col < my_end && gcol < c.N && row_ok) {
+                            float sum = v[cc][0];
+#pragma unroll
+                            for (int sl = 1; sl < 8; ++sl)
+                                if (sl < c.cl_split) sum += v[cc][sl];
+                            const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row);
+                            float val = alpha * sum;
+                            if (out_half) {
+                                if (beta != 0.0f) val += beta * __half2float(reinterpret_cast<const __half *>(gC)[off]);
+                                reinterpret_cast<__half *>(gD)[off] = __float2half_rn(val);
+                            } else {
+                                if (beta != 0.0f) val += beta * __ldg(gC + off);
+                                gD[off] = val;
                             }
-                            *reinterpret_cast<float4 *>(gD + off) = val;
                         }
                     }
                 }

@@ -98,15 +98,19 @@ __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-// Store into the shared memory of another CTA of the cluster (address from mapa_shared). One way: the thread does
-// not wait for it; a later release at cluster scope (mbar_arrive_release_cluster) publishes it.
-__device__ __forceinline__ void st_shared_cluster_b32(uint32_t cluster_addr, uint32_t value) {
-    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
+// Load from the shared memory of another CTA of the cluster (address from mapa_shared).
+__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
 }
 
-__device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {  // this CTA's shared memory, 16-byte aligned
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {  // 16-byte aligned
     float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
     return v;
 }
 
