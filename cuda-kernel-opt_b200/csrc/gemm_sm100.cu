@@ -18,10 +18,17 @@
 // stage buffers, one residual barrier for the rest) becomes sub-tile barriers inside a stage:
 // the B^T buffer is split into column sub-tiles, each with its own TMA boxes, full barrier and
 // MMA, issued in load order, so the first sub-tile's MMA starts before the rest of the stage has
-// landed; the A buffer is split into row boxes with their own barriers.
+// landed; the A buffer is split into row boxes with their own barriers, and a one-CTA 128-row tile
+// released in steps of at most 64 rows is issued as two 64-row MMA atoms, the upper one as soon as
+// the barriers of rows 0-63 are complete (the reference's per-fragment-row start, port_1.cu:406-433).
 //
 // Two accumulator slots in tensor memory let the drain of tile i overlap the MMAs of tile i+1,
 // where the reference drains the whole pipeline at every tile (async.cu:339).
+//
+// The schedule (schedule.h) is the reference's persistent tile loop (async.cu:251-252) plus a tail
+// split: the tiles that would leave a last wave partly empty are cut into K slices that run first,
+// one per CTA (pair); the CTA of a tile's last slice adds the other slices' partials from the
+// workspace (flags, bounded waits) before the usual drain, so no second kernel is needed.
 //
 // Skinny (decode) shapes: with swapped roles the kernel computes D^T = B^T * A^T, so B^T fills the
 // 128-row side of the MMA and the few rows of A its N side; the epilogue then writes the
