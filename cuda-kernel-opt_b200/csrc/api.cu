@@ -439,6 +439,8 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.prof_blocks = g_prof_blocks.load();
     a.debug_flags = user->diagnostic;
     a.l2_hint = user->l2_hint;
+    // D larger than half the L2 (126 MB) streams out with evict_first lines; bit 5 of the diagnostic word keeps them normal
+    a.d_stream = (static_cast<int64_t>(M) * N * (out_half ? 2 : 4) >= (int64_t(64) << 20)) && !(user->diagnostic & 32);
     a.k_order = user->k_order;
     a.overlap_launch = user->overlap_launch ? 1 : 0;
 

@@ -728,6 +728,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         const float beta = (to_partial || push_world > 0) ? 0.0f : g_beta;
         uint32_t tl = 0;
         uint32_t store_idx = 0;
+        // D is written once and not read again by this launch: when it is larger than the L2 can keep anyway, its
+        // lines are marked to leave first, so that they do not push out operand panels the next tiles re-read
+        const uint64_t d_policy = l2_policy(g.d_stream ? 1 : 0);
         bool ok = true;
         long long t_tfull = 0;
         const long long t_begin = clock64();
@@ -1129,7 +1132,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&g.map_d, buf, w.n0 + c0, w.m0 + static_cast<int>(rank) * c.cta_rows_a + q * 32);
+                            tma_store_2d_hint(&g.map_d, buf, w.n0 + c0, w.m0 + static_cast<int>(rank) * c.cta_rows_a + q * 32, d_policy);
                             tma_store_commit();
                         }
                         ++store_idx;

@@ -44,6 +44,7 @@ struct alignas(64) GemmArgs {
     int k_order;
     int cl_split;       // > 1: cluster size; the CTAs of a cluster take the K slices of one tile and reduce through
                         // distributed shared memory (split_k is 1 then: no workspace)
+    int d_stream;       // 1: the TMA stores of D carry an evict_first L2 policy (D exceeds what the L2 would keep)
     int overlap_launch; // 1: set-up runs before griddepcontrol.wait (launched with programmatic stream serialisation)
     int a_split;        // 1: a 128-row tile is two 64-row MMA atoms (the A side of the shift synchronisation): the upper
                         // atom's MMAs are issued when the row boxes of rows 0-63 have landed; accumulators of the two

@@ -215,6 +215,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t src,
                  "r"(src), "r"(c0), "r"(c1)
                  : "memory");
 }
+// The same with an L2 eviction-priority policy (from l2_policy) for the lines the store writes.
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap *m, uint32_t src, int c0, int c1, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(src), "r"(c0), "r"(c1), "l"(policy)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

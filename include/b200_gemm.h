@@ -89,7 +89,8 @@ typedef struct b200_gemm_params {
                        bounded waits expire: the launch returns normally with a B200_DEVICE_TIMEOUT
                        record (barrier ids 701 / 700) and an unfinished D; bit 4 (with tail_split) withholds the
                        "partial stored" flags of its fix-up in the same way (wait ids 800 + warp);
-                       for tests of those paths */
+                       for tests of those paths. Bit 5 stores D with normal L2 priority where the library would
+                       mark its lines evict_first (TMA-store epilogue, D of 64 MiB or more): an A/B switch */
     int k_order;    /* 0 = every tile sums K ascending; 1 = serpentine: every other tile of a CTA walks K downwards,
                        so consecutive waves meet their shared operand panels while they are still in L2.
                        Changes the fp32 summation order of those tiles (not the tolerance) */
