@@ -497,15 +497,22 @@ def run_ours(args):
         if library:
             sustained = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
         else:
+            # the vendor library in the same harness, same duration, directly after (or, --sustained-library-first,
+            # directly before: the second leg starts on a warmer GPU): a number for scale (joules per TFLOP side by
+            # side); it is not on this repository's path
+            lib_leg = None
+            with_lib = world == 1 and rank == 0
+            if with_lib and args.sustained_library_first:
+                lib_leg = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
             sustained = sustained_leg(lambda i: pkg.gemm(As[i % rot], Bts[i % rot], None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None),
                                       flops_of(m_loc, n_loc, k_loc))
             st, info = pkg.device_status()
             assert st == pkg.OK, f"device status {st} {info}"
-            if world == 1 and rank == 0:
-                # the vendor library in the same harness, same duration, directly after: a number for scale
-                # (joules per TFLOP side by side); it is not on this repository's path
-                sustained["library_for_scale"] = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()),
-                                                                flops_of(m_loc, n_loc, k_loc))
+            if with_lib and lib_leg is None:
+                lib_leg = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
+            if lib_leg is not None:
+                lib_leg["order"] = "before this kernel's leg" if args.sustained_library_first else "after this kernel's leg"
+                sustained["library_for_scale"] = lib_leg
         sustained["frac_of_sustained_peak"] = sustained["tflops"] / peaks()["bf16_tflops_sustained"]
         sustained["peak_source"] = f"{peaks()['_source']} cuBLAS bf16 8192^3 sustained"
 
@@ -698,6 +705,7 @@ def main():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
                     help="N > 1, square workloads: strong = the workload's M rows split over the GPUs (the baseline's "
                          "configuration), weak = every GPU gets M rows of its own")
+    ap.add_argument("--sustained-library-first", action="store_true", help="run the vendor library's sustained leg before this kernel's instead of after")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="after the timed steps, this many seconds of back-to-back launches with clock, power and energy "
                          "readings (0 = skip)")
