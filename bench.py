@@ -286,6 +286,11 @@ def run_ours(args):
     mshard_alone = args.shard_of > 1 and world == 1 and not nshard and not args.workload.startswith("c5")
     shard_world = args.shard_of if (args.shard_of > 1 and world == 1 and (nshard or mshard_alone)) else world
     library = args.impl == "library"       # torch.matmul (cuBLAS) in the same harness, for scale only
+    # the library's product: fp16/bf16 out by default (torch.matmul); --library-out f32 asks it for this path's fp32 D
+    if args.library_out == "f32":
+        lib_mm = lambda a_, bt_: torch.mm(a_, bt_.t(), out_dtype=torch.float32)
+    else:
+        lib_mm = lambda a_, bt_: torch.matmul(a_, bt_.t())
 
     # ---- placement (see cuda-kernel-opt_b200/shard.py)
     if splitk_ranks:                         # K split over ranks, fp32 partials reduce-scattered by rows
@@ -353,7 +358,7 @@ def run_ours(args):
         if fused:
             return push.gemm_reduce_scatter(a_i, b_i, D_rows, p, workspace=ws if ws_bytes else None)
         if library:
-            return torch.matmul(a_i, b_i.t())
+            return lib_mm(a_i, b_i)
         pkg.gemm(a_i, b_i, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
         if splitk_ranks:
             return shard.reduce_scatter_rows(D)
@@ -405,7 +410,7 @@ def run_ours(args):
                 e1.record()
             else:
                 if library:
-                    torch.matmul(a_i, b_i.t())
+                    lib_mm(a_i, b_i)
                 else:
                     pkg.gemm(a_i, b_i, None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None)
                 e1.record()                                # end of the GEMM kernel(s) of this step
@@ -495,7 +500,7 @@ def run_ours(args):
                     "joules_per_tflop": (joules / (leg_flops * n / 1e12)) if joules is not None else None}
 
         if library:
-            sustained = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
+            sustained = sustained_leg(lambda i: lib_mm(As[i % rot], Bts[i % rot]), flops_of(m_loc, n_loc, k_loc))
         else:
             # the vendor library in the same harness, same duration, directly after (or, --sustained-library-first,
             # directly before: the second leg starts on a warmer GPU): a number for scale (joules per TFLOP side by
@@ -503,13 +508,13 @@ def run_ours(args):
             lib_leg = None
             with_lib = world == 1 and rank == 0
             if with_lib and args.sustained_library_first:
-                lib_leg = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
+                lib_leg = sustained_leg(lambda i: lib_mm(As[i % rot], Bts[i % rot]), flops_of(m_loc, n_loc, k_loc))
             sustained = sustained_leg(lambda i: pkg.gemm(As[i % rot], Bts[i % rot], None, D, 1.0, 0.0, p, workspace=ws if ws_bytes else None),
                                       flops_of(m_loc, n_loc, k_loc))
             st, info = pkg.device_status()
             assert st == pkg.OK, f"device status {st} {info}"
             if with_lib and lib_leg is None:
-                lib_leg = sustained_leg(lambda i: torch.matmul(As[i % rot], Bts[i % rot].t()), flops_of(m_loc, n_loc, k_loc))
+                lib_leg = sustained_leg(lambda i: lib_mm(As[i % rot], Bts[i % rot]), flops_of(m_loc, n_loc, k_loc))
             if lib_leg is not None:
                 lib_leg["order"] = "before this kernel's leg" if args.sustained_library_first else "after this kernel's leg"
                 sustained["library_for_scale"] = lib_leg
@@ -661,6 +666,7 @@ def run_ours(args):
         }
         if library:
             line["impl"] = "library (torch.matmul, for scale: not this repository's kernel)"
+            line["library_out"] = args.library_out
             line["gpu_launches"] = 0
             line["config"].pop("params", None)
         if step_ms is not None:
@@ -705,6 +711,8 @@ def main():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
                     help="N > 1, square workloads: strong = the workload's M rows split over the GPUs (the baseline's "
                          "configuration), weak = every GPU gets M rows of its own")
+    ap.add_argument("--library-out", choices=["half", "f32"], default="half",
+                    help="what the vendor library writes where it is timed for scale: its default 16-bit D, or fp32 like this path (torch.mm out_dtype)")
     ap.add_argument("--sustained-library-first", action="store_true", help="run the vendor library's sustained leg before this kernel's instead of after")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="after the timed steps, this many seconds of back-to-back launches with clock, power and energy "

@@ -310,7 +310,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     st = check_shape(p, M, N, K);
     if (st != B200_OK) return st;
     const bool pushing = push && push->world > 0;
-    if ((p.swap || p.a_split) && pushing) return B200_INVALID_CONFIG;
+    if ((p.swap || p.atoms > 1) && pushing) return B200_INVALID_CONFIG;
     // Swapped roles: the kernel sees the transposed problem (its M operand is B^T, its N operand A)
     // and writes its accumulator transposed, so C and D keep their row-major m x n layout.
     const int64_t kM = p.swap ? N : M, kN = p.swap ? M : N;
@@ -333,7 +333,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     // The tail split is an optimisation of the schedule, taken when the caller's workspace can hold the partials;
     // without it the plain schedule runs and the result is the same to rounding. Its CTAs wait for one another,
     // so all of them must be resident at once: one per SM.
-    TailPlan tail = make_tail_plan(user->tail_split && !p.swap && !p.a_split && p.grid <= dev->num_sms, n_tiles, p.grid / p.cta_group,
+    TailPlan tail = make_tail_plan(user->tail_split && !p.swap && p.atoms == 1 && p.grid <= dev->num_sms, n_tiles, p.grid / p.cta_group,
                                    (K + p.seg_k - 1) / p.seg_k, p.split_k, p.tile_n, p.cta_group);
     if (tail.tiles > 0 && (!workspace || workspace_bytes < static_cast<size_t>(tail.slot_bytes * tail.slots) ||
                            (reinterpret_cast<uintptr_t>(workspace) & 15u)))
@@ -418,10 +418,11 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.off_bars = p.off_bars;
     a.off_tmem_ptr = p.off_tmem_ptr;
     a.epi_mode = epi_mode;
-    const int atom_m = p.a_split ? 64 : p.tile_m;   // M of one MMA (the pair's 256 spans both CTAs)
+    const int atom_m = p.cta_group * p.mma_m;   // M of one MMA (the pair's 256 spans both CTAs)
     a.idesc_chunk = umma_idesc(atom_m, p.chunk_n, dtype == B200_BF16);
     a.idesc_res = umma_idesc(atom_m, p.b_res_chunks * p.chunk_n, dtype == B200_BF16);
     a.a_split = p.a_split;
+    a.atoms = p.atoms;
     a.wait_budget_cycles = static_cast<long long>(g_wait_budget_ns.load() * 2ull);  // SM clock is below 2 GHz
 
     if (pushing && ws_split == 1) {
@@ -555,7 +556,7 @@ int b200_gemm_schedule(int64_t M, int64_t N, int64_t K, const b200_gemm_params *
     const int num_groups = grid / (plan.cta_group * c.cl_split);
     if (num_groups_out) *num_groups_out = num_groups;
     if (group < 0 || group >= num_groups) return -1;
-    const TailPlan tail = make_tail_plan(q.tail_split && !plan.swap && !plan.a_split, c.num_tiles, num_groups, c.num_segs, plan.split_k, plan.tile_n,
+    const TailPlan tail = make_tail_plan(q.tail_split && !plan.swap && plan.atoms == 1, c.num_tiles, num_groups, c.num_segs, plan.split_k, plan.tile_n,
                                          plan.cta_group);
     c.tail_tiles = tail.tiles;
     c.tail_slices = tail.slices;
@@ -586,7 +587,7 @@ int64_t b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, const b200_ge
             cudaGetLastError();
         }
         const Plan plan = make_plan(*p, sms);
-        if (plan.status != B200_OK || plan.swap || plan.a_split) return 0;
+        if (plan.status != B200_OK || plan.swap || plan.atoms > 1) return 0;
         const int64_t n_tiles = ((M + plan.tile_m - 1) / plan.tile_m) * ((N + plan.tile_n - 1) / plan.tile_n);
         const TailPlan t = make_tail_plan(1, n_tiles, plan.grid / plan.cta_group, (K + plan.seg_k - 1) / plan.seg_k, plan.split_k,
                                           plan.tile_n, plan.cta_group);

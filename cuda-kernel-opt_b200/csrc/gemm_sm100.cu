@@ -187,7 +187,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     const int push_world = g.push_world, push_rank = g.push_rank, push_rows = g.push_rows;
     const int ld_cd = g.ld_cd;
     const bool swap_ab = g.swap_ab != 0;
-    const int a_halves = g.a_split ? 2 : 1;   // 2: the 128 rows of a tile are two 64-row MMA atoms, issued as their rows of A land
+    // 2 atoms: a CTA's rows of a tile are two MMA atoms with accumulators side by side: two 64-row atoms issued as
+    // their rows of A land (a_split), or two 128-row atoms of a 256-row CTA share (the tall pair)
+    // (read from the parameter inside each role: the values are not kept live across the others)
     const bool out_half = g.out_half != 0;   // C and D are fp16 (never with a workspace, tail or push path)
     // bit 0: issue no MMA, bit 1: issue no TMA load (pipeline ceilings; results are garbage); bits 2 and 3: the
     // epilogue withholds its "slice staged" / "slice read" arrivals of the cluster reduce, so that those
@@ -402,6 +404,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint64_t a_kb_step = static_cast<uint64_t>((c.cta_rows_a * kSwizzleBytes) >> 4);
             const uint64_t b_kb_step = static_cast<uint64_t>(((c.tile_n / CG) * kSwizzleBytes) >> 4);
             const uint32_t idesc = c.idesc_res;
+            const uint64_t atom_step = static_cast<uint64_t>((c.mma_m * kSwizzleBytes) >> 4);   // second atom: the next rows of the A box
+            const uint32_t atom_cols = static_cast<uint32_t>(c.tile_n);
+            const bool two_atoms = g.atoms == 2;
+            const bool two_slots = 2 * c.acc_cols <= 512;   // else one accumulator slot: the next tile's MMAs wait for the drain
             int s = 0;
             uint32_t ph = 0, it = 0, tl = 0;
             uint32_t sb = bars;
@@ -413,8 +419,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             walk_init(c, walk, group);
             Unit w;
             for (; ok && walk_next(c, walk, num_groups, w); ++tl) {
-                const uint32_t acc = tl & 1u;
-                const uint32_t aph = (tl >> 1) & 1u;
+                const uint32_t acc = two_slots ? (tl & 1u) : 0u;
+                const uint32_t aph = two_slots ? ((tl >> 1) & 1u) : (tl & 1u);
                 const long long ta = PROF ? clock64() : 0;
                 ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
                 if (PROF) t_acc += clock64() - ta;
@@ -430,15 +436,31 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     if (it == 0 && lane == 0) B200_TL(20);
                     tc_fence_after_sync();
                     uint64_t da = a_desc, db = b_desc;
-                    for (int kb = 0; kb < c.kblocks; ++kb) {
+                    if (!two_atoms) {
+                        for (int kb = 0; kb < c.kblocks; ++kb) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            // +32 bytes per 16-element K step inside the 128-byte swizzle row
-                            if (issue) umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, accumulate);
-                            accumulate = 1;
+                            for (int i = 0; i < 4; ++i) {
+                                // +32 bytes per 16-element K step inside the 128-byte swizzle row
+                                if (issue) umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, accumulate);
+                                accumulate = 1;
+                            }
+                            da += a_kb_step;
+                            db += b_kb_step;
                         }
-                        da += a_kb_step;
-                        db += b_kb_step;
+                    } else {
+                        // two 128-row atoms of A against the same B^T rows: accumulators side by side
+                        for (int kb = 0; kb < c.kblocks; ++kb) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                if (issue) {
+                                    umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, accumulate);
+                                    umma_f16<CG>(d_addr + atom_cols, da + atom_step + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, accumulate);
+                                }
+                                accumulate = 1;
+                            }
+                            da += a_kb_step;
+                            db += b_kb_step;
+                        }
                     }
                     if (issuer) commit_to<CG>(sb + empty_a_off, pair_mask);
                     ++it;
@@ -603,7 +625,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const uint64_t a_kb_step = static_cast<uint64_t>((c.cta_rows_a * kSwizzleBytes) >> 4);
             const uint64_t b_box_step = static_cast<uint64_t>((b_box_rows * kSwizzleBytes) >> 4);   // one box of a K block
             const uint64_t b_sub_step = b_box_step * static_cast<uint64_t>(c.kblocks);             // one private sub-tile
-            const uint64_t a_half_step = static_cast<uint64_t>((64 * kSwizzleBytes) >> 4);           // rows 64.. of a K block
+            const uint64_t a_half_step = static_cast<uint64_t>((c.mma_m * kSwizzleBytes) >> 4);  // the second atom's rows of a K block
+            const int a_halves = g.atoms;
+            const bool two_slots = 2 * c.acc_cols <= 512;
             long long n_early = 0;
             int s = 0;
             uint32_t ph = 0, it = 0, tl = 0;
@@ -616,8 +640,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             walk_init(c, walk, group);
             Unit w;
             for (; ok && walk_next(c, walk, num_groups, w); ++tl) {
-                const uint32_t acc = tl & 1u;
-                const uint32_t aph = (tl >> 1) & 1u;
+                const uint32_t acc = two_slots ? (tl & 1u) : 0u;
+                const uint32_t aph = two_slots ? ((tl >> 1) & 1u) : (tl & 1u);
                 const long long ta = PROF ? clock64() : 0;
                 ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
                 if (PROF) t_acc += clock64() - ta;
@@ -708,6 +732,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     } else {
         // ------------------------------------------------------------------ epilogue
         const int e = warp - (P + 1);          // 0 .. epi_warps-1
+        const int a_halves = g.atoms;   // 64-row atoms (a_split) or 128-row atoms (the tall pair): mma_m rows each
         const int q = warp & 3;                // TMEM lane quarter this warp may read
         const int halves = c.epi_warps / 4;    // 1 or 2 warps per quarter
         const int half = e / 4;
@@ -738,8 +763,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
         walk_init(c, walk, group);
         Unit w;
         for (; ok && walk_next(c, walk, num_groups, w); ++tl) {
-            const uint32_t acc = tl & 1u;
-            const uint32_t aph = (tl >> 1) & 1u;
+            const bool two_slots = 2 * c.acc_cols <= 512;
+            const uint32_t acc = two_slots ? (tl & 1u) : 0u;
+            const uint32_t aph = two_slots ? ((tl >> 1) & 1u) : (tl & 1u);
             const long long te = prof ? clock64() : 0;
             ok = wait_all(tmem_full0 + 8u * acc, aph, c.budget, abort_flag, 600 + static_cast<int>(acc));
             if (prof) t_tfull += clock64() - te;
@@ -942,9 +968,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const size_t row_off_atom0 = row_off;
             const uint32_t t_row_atom0 = t_row;
             for (int mh = 0; mh < a_halves; ++mh) {
-                const int row = row_atom0 + mh * 64;
+                const int row = row_atom0 + mh * c.mma_m;
                 const bool row_ok = lane_has_row && row < c.M;
-                const size_t row_off = row_off_atom0 + static_cast<size_t>(mh * 64) * static_cast<size_t>(ld_cd);
+                const size_t row_off = row_off_atom0 + static_cast<size_t>(mh * c.mma_m) * static_cast<size_t>(ld_cd);
                 const uint32_t t_row = t_row_atom0 + static_cast<uint32_t>(mh * c.tile_n);
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                     if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
@@ -1132,7 +1158,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d_hint(&g.map_d, buf, w.n0 + c0, w.m0 + static_cast<int>(rank) * c.cta_rows_a + q * 32, d_policy);
+                            tma_store_2d_hint(&g.map_d, buf, w.n0 + c0, row - lane, d_policy);   // the first of this warp's 32 rows (128-row atoms: row = ... + lane)
                             tma_store_commit();
                         }
                         ++store_idx;

@@ -53,6 +53,9 @@ struct Plan {
                                           //    in distributed shared memory (no workspace, no second kernel)
     int a_split = 0;                      // 1: a 128-row tile is issued as two 64-row MMA atoms so that the upper rows'
                                           //    MMAs start before the lower rows of A have landed (A-side shift)
+    int atoms = 1, atom_rows = 0;         // MMA atoms a CTA's rows of A are issued as (1 or 2) and the rows of one
+    int acc_slots = 2;                    // accumulator slots in tensor memory: 2 (the drain of a tile overlaps the MMAs of
+                                          //    the next), or 1 when one tile's accumulator fills the 512 columns
 };
 
 // Tail split (tail_split = 1): the tiles that do not fill a wave of the persistent grid are cut along K.
@@ -133,12 +136,17 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     const int cg = q.cta_group == 0 ? 1 : q.cta_group;
     if (cg != 1 && cg != 2) return p;
     p.cta_group = cg;
-    // tile_m: 128 or 64 for one CTA; 256 for a pair (each CTA holds 128 rows).
+    // tile_m: 128 or 64 for one CTA; 256 for a pair (each CTA holds 128 rows); 512 for a "tall" pair: each CTA
+    // holds 256 rows of A, issued as two 128-row atoms against the same B^T stage, so a byte of B^T feeds twice the
+    // MMA work (operand bytes per flop drop by a quarter against the 256-row pair).
     if (cg == 1 && q.tile_m != 128 && q.tile_m != 64) return p;
-    if (cg == 2 && q.tile_m != 256) return p;
+    if (cg == 2 && q.tile_m != 256 && q.tile_m != 512) return p;
     p.tile_m = q.tile_m;
     p.cta_rows_a = q.tile_m / cg;
-    p.mma_m = p.cta_rows_a;
+    p.mma_m = p.cta_rows_a > 128 ? 128 : p.cta_rows_a;
+    p.atoms = p.cta_rows_a / p.mma_m;
+    p.atom_rows = p.mma_m;
+    if (p.atoms == 2 && (p.swap || user.cluster_reduce)) return p;
     // tile_n: N of the MMA. M=128 per CTA needs N % 16 == 0, M=64 needs N % 8; a pair splits N.
     const int n_gran = 16 * cg;
     if (q.tile_n < n_gran || q.tile_n > 256 || q.tile_n % n_gran) return p;
@@ -221,12 +229,16 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
         p.tile_n <= 128 && p.split_k == 1) {
         p.a_split = 1;
         p.mma_m = 64;
+        p.atoms = 2;
+        p.atom_rows = 64;
     }
+    if (p.atoms == 2 && !p.a_split && (p.a_boxes > 1 || p.split_k > 1)) return p;   // the tall pair: whole-stage barriers for A, whole tiles
 
     // Tensor memory: two accumulator slots so the drain of tile i overlaps the MMAs of tile i+1.
     // M=64 per CTA keeps the 16-lanes-per-quarter layout of one 64-row atom.
-    p.acc_cols = p.a_split ? 2 * p.tile_n : p.tile_n;
-    p.tmem_cols = pow2_at_least(2 * p.acc_cols);
+    p.acc_cols = p.atoms * p.tile_n;
+    p.acc_slots = (2 * p.acc_cols <= kTmemColumns) ? 2 : 1;
+    p.tmem_cols = pow2_at_least(p.acc_slots * p.acc_cols);
     if (p.tmem_cols > kTmemColumns) return p;
 
     // Shared memory map (offsets from a 1024-byte aligned base).

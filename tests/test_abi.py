@@ -126,6 +126,27 @@ def test_b200_extensions(pkg):
     assert pkg.workspace_bytes(512, 256, 4096, P(pkg)) == 0
 
 
+def test_tall_pair_tile_domain(pkg):
+    """tile_m = 512 with cta_group = 2: each CTA stages 256 rows of A and issues them as two 128-row MMA atoms against one
+    B^T stage; the two accumulators fill the 512 tensor-memory columns at tile_n = 256 (one slot), whole tiles and whole-stage
+    A barriers only."""
+    tall = dict(tile_m=512, tile_n=256, cta_group=2, bar_step_rows_a=512, bar_step_rows_b=256, tail_split=0)
+    ok = lambda M=8192, N=8192, K=8192, **ov: pkg.validate(M, N, K, pkg.F16, P(pkg, **dict(tall, **ov)))
+    assert ok(num_stages=4) == pkg.OK
+    assert ok(num_stages=5) == pkg.INVALID_CONFIG                       # 5 x 48 KiB of stages + drain buffers do not fit
+    assert ok(num_stages=3, num_consumer_warps=8) == pkg.OK
+    assert ok(num_stages=4, tile_n=128, bar_step_rows_b=128) == pkg.OK
+    assert ok(num_stages=4, cta_group=1) == pkg.INVALID_CONFIG
+    assert ok(num_stages=4, split_k=2) == pkg.INVALID_CONFIG
+    assert ok(num_stages=4, bar_step_rows_a=128) == pkg.INVALID_CONFIG  # sub-tile barriers for A belong to the 128-row forms
+    assert ok(num_stages=4, swap_ab=1) == pkg.INVALID_CONFIG
+    assert pkg.smem_bytes(pkg.F16, P(pkg, num_stages=4, epilogue=1, **tall)) == 4 * (256 + 128) * 64 * 2 + 4 * 2 * 4096 + (4 * 4 + 6) * 8 + 16 + 1024
+    # the schedule: 512-row tiles, every tile once, ragged M included
+    p = P(pkg, num_stages=4, **tall)
+    tiles, groups = _coverage(pkg, 1200, 768, 512, p, 8)
+    assert groups == 4 and sorted(tiles) == [(m, n) for m in (0, 512, 1024) for n in (0, 256, 512)]
+
+
 def test_swapped_roles_and_cluster_reduce_domain(pkg):
     """swap_ab: tile_n is the 64/128-row side, tile_m the multiple-of-16 side; cluster_reduce needs
     swap_ab, a portable cluster size and a narrow accumulator, and then no workspace."""
