@@ -194,6 +194,7 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         }
         return;
     }
+    bool tall = false;
     if (pair) {
         p->tile_m = 256;
         p->cta_group = 2;
@@ -226,6 +227,19 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         p->num_stages = 6;   // 6 x (128 + tile_n / 2) rows x 128 B, and 32 KB of TMA-store staging: 224 KB with 256 columns
         p->num_producer_warps = 2;
         p->l2_hint = 3;  // keep operand panels in L2: fewer DRAM re-reads, measured +2.5 % under the power limit
+        // The tall pair (512 x 256 per pair, 256 rows of A per CTA as two MMA atoms against one B^T stage) moves a
+        // quarter fewer operand bytes per flop from L2 to the SMs: the K loop stops waiting for data (1049 against
+        // 1106 cycles per 512 x 256 x 64 block) and a launch costs less energy, which under the power limit is clock.
+        // Its accumulators fill the tensor memory, so the drain of a tile (9.5 k cycles with eight warps) is not
+        // hidden behind the next tile's MMAs: 7 % of a tile at K = 8192, more at smaller K. Measured at 8192^3:
+        // 1491 against 1443 TFLOP/s (0.968 of the time). Taken when its rounds cost less by that model.
+        if (best_n == 256 && K >= 4096) {
+            const int64_t tall_tiles = ((M + 511) / 512) * ((N + 255) / 256);
+            const int64_t tall_rounds = (tall_tiles + 73) / 74;
+            const double tall_factor = 0.968 + 0.071 * (8192.0 / double(K) - 1.0);
+            const double tall_cost = double(tall_rounds) * 2.0 * double(256 + 12) * tall_factor;
+            if (tall_cost < best_cost * 0.995) tall = true;
+        }
     } else {
         // One row of tiles (skinny, HBM-bound: decode shapes) or N not a multiple of 256: a one-CTA
         // tile whose width divides N and fills the last wave of the persistent grid best.
@@ -273,6 +287,13 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         p->tile_group_m = 16;
     }
     p->num_consumer_warps = 4;
+    if (tall) {
+        p->tile_m = 512;
+        p->bar_step_rows_a = 512;
+        p->num_stages = 3;          // 3 x 48 KB of stages + 64 KB of drain buffers for eight warps
+        p->num_consumer_warps = 8;  // the drain is exposed: two warps per tensor-memory lane quarter halve it
+        p->tile_group_m = 8;        // 8 x 512 rows: the same 4096-row groups as 16 x 256
+    }
     p->num_sms = 0;
     p->split_k = 1;
     // drain through swizzled shared memory and TMA stores: 3x shorter per tile than scattered 128-bit
