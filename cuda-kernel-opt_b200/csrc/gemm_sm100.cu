@@ -784,6 +784,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 out = g.push_slot[owner];
                 row_off = (static_cast<size_t>(push_rank) * push_rows + static_cast<size_t>(row - owner * push_rows)) * c.N + w.n0;
             }
+            // alpha * acc + beta * C is evaluated everywhere as fma(beta, C, round(alpha * acc)), written with the intrinsic so
+            // that every drain path (and every tiling) rounds the same way
             const float a_u = alpha;
             const float b_u = beta;
             const uint32_t t_row = tmem_base + acc * static_cast<uint32_t>(c.acc_cols) + (static_cast<uint32_t>(q * 32) << 16);
@@ -898,10 +900,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                     const uint2 cv = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(gC) + off);
                                     const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
                                     const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
-                                    val.x += beta * c01.x;
-                                    val.y += beta * c01.y;
-                                    val.z += beta * c23.x;
-                                    val.w += beta * c23.y;
+                                    val.x = __fmaf_rn(beta, c01.x, val.x);
+                                    val.y = __fmaf_rn(beta, c01.y, val.y);
+                                    val.z = __fmaf_rn(beta, c23.x, val.z);
+                                    val.w = __fmaf_rn(beta, c23.y, val.w);
                                 }
                                 const __half2 h01 = __floats2half2_rn(val.x, val.y), h23 = __floats2half2_rn(val.z, val.w);
                                 uint2 o;
@@ -911,10 +913,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                             } else {
                                 if (beta != 0.0f) {
                                     const float4 cv = __ldg(reinterpret_cast<const float4 *>(gC + off));
-                                    val.x += beta * cv.x;
-                                    val.y += beta * cv.y;
-                                    val.z += beta * cv.z;
-                                    val.w += beta * cv.w;
+                                    val.x = __fmaf_rn(beta, cv.x, val.x);
+                                    val.y = __fmaf_rn(beta, cv.y, val.y);
+                                    val.z = __fmaf_rn(beta, cv.z, val.z);
+                                    val.w = __fmaf_rn(beta, cv.w, val.w);
                                 }
                                 *reinterpret_cast<float4 *>(gD + off) = val;
                             }
@@ -947,10 +949,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                             const size_t off = static_cast<size_t>(gcol) * static_cast<size_t>(ld_cd) + static_cast<size_t>(row);
                             float val = alpha * sum;
                             if (out_half) {
-                                if (beta != 0.0f) val += beta * __half2float(reinterpret_cast<const __half *>(gC)[off]);
+                                if (beta != 0.0f) val = __fmaf_rn(beta, __half2float(reinterpret_cast<const __half *>(gC)[off]), val);
                                 reinterpret_cast<__half *>(gD)[off] = __float2half_rn(val);
                             } else {
-                                if (beta != 0.0f) val += beta * __ldg(gC + off);
+                                if (beta != 0.0f) val = __fmaf_rn(beta, __ldg(gC + off), val);
                                 gD[off] = val;
                             }
                         }
@@ -972,6 +974,45 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const bool row_ok = lane_has_row && row < c.M;
                 const size_t row_off = row_off_atom0 + static_cast<size_t>(mh * c.mma_m) * static_cast<size_t>(ld_cd);
                 const uint32_t t_row = t_row_atom0 + static_cast<uint32_t>(mh * c.tile_n);
+                if (w.kind == 0 && tail_peers == 0 && c.epi_mode == 1 && b_u == 0.0f && ((col_end - col_begin) & 31) == 0 && w.n0 + col_end <= c.N) {
+                    // ---- The common drain: a whole tile, beta = 0, fp32 D through TMA stores, full 32-column boxes. The same steps
+                    // as the general loop below, with the tensor-memory load of the next box issued as soon as this
+                    // box's registers have been staged, so that it overlaps the fence, the warp barrier and the store.
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(col_begin), r);
+                    const uint32_t my_x = static_cast<uint32_t>(lane & 7);
+                    int d_col = w.n0 + col_begin;
+                    for (int c0 = col_begin; c0 < col_end; c0 += 32, d_col += 32) {
+                        tmem_ld_wait();
+                        const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
+                        if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
+                        __syncwarp();
+                        const uint32_t my_row = buf + static_cast<uint32_t>(lane) * 128u;
+                        if (a_u == 1.0f) {
+    #pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((static_cast<uint32_t>(j) ^ my_x) << 4)),
+                                             "r"(r[4 * j + 0]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                                             : "memory");
+                        } else {
+    #pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((static_cast<uint32_t>(j) ^ my_x) << 4)),
+                                             "f"(a_u * __uint_as_float(r[4 * j + 0])), "f"(a_u * __uint_as_float(r[4 * j + 1])),
+                                             "f"(a_u * __uint_as_float(r[4 * j + 2])), "f"(a_u * __uint_as_float(r[4 * j + 3]))
+                                             : "memory");
+                        }
+                        if (c0 + 32 < col_end) tmem_ld_32x32(t_row + static_cast<uint32_t>(c0 + 32), r);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d_hint(&g.map_d, buf, d_col, row - lane, d_policy);   // the first of this warp's 32 rows
+                            tma_store_commit();
+                        }
+                        ++store_idx;
+                    }
+                    continue;
+                }
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                     if (w.n0 + c0 >= c.N) break;  // ragged last tile column: nothing of D beyond N
                     uint32_t r[32];
@@ -1051,7 +1092,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                     if (j < 16 || wide) {
                                         if (j < valid) {
                                             float v = a_u * __uint_as_float(r[j]);
-                                            if (b_u != 0.0f) v += b_u * __half2float(*c16);
+                                            if (b_u != 0.0f) v = __fmaf_rn(b_u, __half2float(*c16), v);
                                             *dst16 = __float2half_rn(v);
                                         }
                                         dst16 += pitch;
@@ -1070,7 +1111,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
     #pragma unroll
                                 for (int j = 0; j < 32; ++j) {
                                     if (j < 16 || wide) {
-                                        if (j < valid) *dst = a_u * __uint_as_float(r[j]) + b_u * __ldg(csrc);
+                                        if (j < valid) *dst = __fmaf_rn(b_u, __ldg(csrc), __fmul_rn(a_u, __uint_as_float(r[j])));
                                         dst += pitch;
                                         csrc += pitch;
                                     }
@@ -1094,10 +1135,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                         const uint2 cv = __ldg(csrc + j);
                                         const float2 c01 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.x));
                                         const float2 c23 = __half22float2(*reinterpret_cast<const __half2 *>(&cv.y));
-                                        v.x += b_u * c01.x;
-                                        v.y += b_u * c01.y;
-                                        v.z += b_u * c23.x;
-                                        v.w += b_u * c23.y;
+                                        v.x = __fmaf_rn(b_u, c01.x, v.x);
+                                        v.y = __fmaf_rn(b_u, c01.y, v.y);
+                                        v.z = __fmaf_rn(b_u, c23.x, v.z);
+                                        v.w = __fmaf_rn(b_u, c23.y, v.w);
                                     }
                                     const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
                                     uint2 o;
@@ -1121,57 +1162,40 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                                     v.w = a_u * __uint_as_float(r[4 * j + 3]);
                                     if (b_u != 0.0f) {
                                         const float4 cv = __ldg(csrc + j);
-                                        v.x += b_u * cv.x;
-                                        v.y += b_u * cv.y;
-                                        v.z += b_u * cv.z;
-                                        v.w += b_u * cv.w;
+                                        v.x = __fmaf_rn(b_u, cv.x, v.x);
+                                        v.y = __fmaf_rn(b_u, cv.y, v.y);
+                                        v.z = __fmaf_rn(b_u, cv.z, v.z);
+                                        v.w = __fmaf_rn(b_u, cv.w, v.w);
                                     }
                                     dst[j] = v;
                                 }
                             }
                         }
                     } else {
-                        // registers -> 128-byte-swizzled shared memory -> one TMA store of 32 x 32 fp32
+                        // registers -> 128-byte-swizzled shared memory -> one TMA store of 32 x 32 fp32 (the boxes the common
+                        // drain above does not take: ragged tile columns, the finishing CTA of a cut tile)
                         const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
                         if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
                         __syncwarp();
-                        // A draining warp has a scheduler to itself, so every instruction here is exposed latency: the
-                        // common cases (beta = 0, and alpha = 1 on top) are loops without the tests and loads of C.
-                        const uint32_t my_row = buf + static_cast<uint32_t>(lane) * 128u;
-                        const uint32_t my_x = static_cast<uint32_t>(lane & 7);
-                        if (b_u == 0.0f && a_u == 1.0f) {
+                        const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
     #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((static_cast<uint32_t>(j) ^ my_x) << 4)),
-                                             "r"(r[4 * j + 0]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
-                                             : "memory");
-                        } else if (b_u == 0.0f) {
-    #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((static_cast<uint32_t>(j) ^ my_x) << 4)),
-                                             "f"(a_u * __uint_as_float(r[4 * j + 0])), "f"(a_u * __uint_as_float(r[4 * j + 1])),
-                                             "f"(a_u * __uint_as_float(r[4 * j + 2])), "f"(a_u * __uint_as_float(r[4 * j + 3]))
-                                             : "memory");
-                        } else {
-                            const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
-    #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                float4 v;
-                                v.x = a_u * __uint_as_float(r[4 * j + 0]);
-                                v.y = a_u * __uint_as_float(r[4 * j + 1]);
-                                v.z = a_u * __uint_as_float(r[4 * j + 2]);
-                                v.w = a_u * __uint_as_float(r[4 * j + 3]);
-                                if (row_ok && w.n0 + c0 + 4 * j < c.N) {
-                                    const float4 cv = __ldg(csrc + j);
-                                    v.x += b_u * cv.x;
-                                    v.y += b_u * cv.y;
-                                    v.z += b_u * cv.z;
-                                    v.w += b_u * cv.w;
-                                }
-                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((static_cast<uint32_t>(j) ^ my_x) << 4)),
-                                             "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                                             : "memory");
+                        for (int j = 0; j < 8; ++j) {
+                            float4 v;
+                            v.x = a_u * __uint_as_float(r[4 * j + 0]);
+                            v.y = a_u * __uint_as_float(r[4 * j + 1]);
+                            v.z = a_u * __uint_as_float(r[4 * j + 2]);
+                            v.w = a_u * __uint_as_float(r[4 * j + 3]);
+                            if (b_u != 0.0f && row_ok && w.n0 + c0 + 4 * j < c.N) {
+                                const float4 cv = __ldg(csrc + j);
+                                v.x = __fmaf_rn(b_u, cv.x, v.x);
+                                v.y = __fmaf_rn(b_u, cv.y, v.y);
+                                v.z = __fmaf_rn(b_u, cv.z, v.z);
+                                v.w = __fmaf_rn(b_u, cv.w, v.w);
                             }
+                            const uint32_t addr = buf + static_cast<uint32_t>(lane) * 128u + static_cast<uint32_t>((j ^ (lane & 7)) * 16);
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+                                         "f"(v.w)
+                                         : "memory");
                         }
                         fence_proxy_async_smem();
                         __syncwarp();
@@ -1269,10 +1293,10 @@ __global__ void splitk_reduce_kernel(const float4 *__restrict__ partial, const f
         o.w = alpha * s.w;
         if (beta != 0.0f) {
             const float4 c = C[i];
-            o.x += beta * c.x;
-            o.y += beta * c.y;
-            o.z += beta * c.z;
-            o.w += beta * c.w;
+            o.x = __fmaf_rn(beta, c.x, o.x);
+            o.y = __fmaf_rn(beta, c.y, o.y);
+            o.z = __fmaf_rn(beta, c.z, o.z);
+            o.w = __fmaf_rn(beta, c.w, o.w);
         }
         D[i] = o;
     }
@@ -1325,10 +1349,10 @@ __global__ void push_reduce_kernel(const float4 *slots, const int *flags, int wo
         o.w = alpha * s.w;
         if (beta != 0.0f) {
             const float4 c = C[i];
-            o.x += beta * c.x;
-            o.y += beta * c.y;
-            o.z += beta * c.z;
-            o.w += beta * c.w;
+            o.x = __fmaf_rn(beta, c.x, o.x);
+            o.y = __fmaf_rn(beta, c.y, o.y);
+            o.z = __fmaf_rn(beta, c.z, o.z);
+            o.w = __fmaf_rn(beta, c.w, o.w);
         }
         D[i] = o;
     }
