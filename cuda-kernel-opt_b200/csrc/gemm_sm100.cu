@@ -23,7 +23,10 @@
 // the barriers of rows 0-63 are complete (the reference's per-fragment-row start, port_1.cu:406-433).
 //
 // Two accumulator slots in tensor memory let the drain of tile i overlap the MMAs of tile i+1,
-// where the reference drains the whole pipeline at every tile (async.cu:339).
+// where the reference drains the whole pipeline at every tile (async.cu:339). The tall pair tile
+// (512 x 256 per CTA pair: each CTA's 256 rows of A are two 128-row MMA atoms against one B^T stage)
+// trades that for a quarter fewer operand bytes per flop: its two accumulators fill the tensor
+// memory, one slot, and the drain (eight warps) is exposed.
 //
 // The schedule (schedule.h) is the reference's persistent tile loop (async.cu:251-252) plus a tail
 // split: the tiles that would leave a last wave partly empty are cut into K slices that run first,

@@ -43,7 +43,12 @@ enum { B200_F16 = 0, B200_BF16 = 1 };
 /* Tunables. The first twelve are the reference launcher's own (matmul_shmem_tc_async_opt_port_2.cu
  * :1088-1109); tile_dim is split into tile_m/tile_n and cta_group/split_k are added for the B200.
  *
- * tile_m             output-tile rows: 128 (one CTA), 256 (two-CTA pair, cta_group = 2) or 64
+ * tile_m             output-tile rows: 128 (one CTA), 256 (two-CTA pair, cta_group = 2) or 64; 512 with
+ *                    cta_group = 2 is the tall pair: each CTA stages 256 rows of A and issues them as two
+ *                    128-row MMA atoms against one B^T stage (a quarter fewer operand bytes per flop); its
+ *                    two accumulators fill the tensor memory at tile_n = 256, so a tile's drain is not hidden
+ *                    behind the next tile's MMAs. Whole tiles only (split_k = 1, no tail split, no swap),
+ *                    bar_step_rows_a = 512
  * tile_n             output-tile columns: multiple of 16 in [16, 256]
  * segment_dim_k      K extent staged per pipeline stage; multiple of 64
  * bar_steps_a/b      number of leading sub-tiles of the A / B^T stage buffer with a private "full"
@@ -60,7 +65,7 @@ enum { B200_F16 = 0, B200_BF16 = 1 };
  *                    issuing warps (the reference's split, port_1.cu:197); further warps idle
  * num_consumer_warps 4 or 8 warps draining the accumulator (one or two per 32 TMEM lanes)
  * num_sms            size of the persistent grid (CTAs); 0 = all SMs of the device
- * cta_group          1, or 2 for the two-CTA tcgen05 pair (tile_m = 256)
+ * cta_group          1, or 2 for the two-CTA tcgen05 pair (tile_m = 256 or 512)
  * split_k            K slices computed by different CTAs into the workspace and summed; 1 = off
  * epilogue, l2_hint  see the fields
  */
