@@ -422,6 +422,31 @@ def test_ragged_n_and_k(pkg, cuda, oracle):
     assert pkg.validate(256, 1002, 1000, pkg.F16, pkg.default_params(256, 1000, 1000, pkg.F16)) == pkg.INVALID_SHAPE
 
 
+def test_tall_pair_tile(pkg, cuda, oracle):
+    """tile_m = 512, cta_group = 2: two 128-row MMA atoms per CTA against one B^T stage, one accumulator slot. Against the
+    oracle (tile multiples, ragged M / N / K, fewer tiles than CTA pairs, several tiles per pair so that the one
+    slot is handed back and forth, alpha and beta through the three drain paths), and bit for bit against the
+    256 x 256 pair tile: with plain K order both add the same products in the same order."""
+    tall = dict(tile_m=512, tile_n=256, cta_group=2, bar_step_rows_a=512, bar_step_rows_b=256, k_order=0, tail_split=0)
+    pair = dict(tile_m=256, tile_n=256, cta_group=2, bar_step_rows_a=256, bar_step_rows_b=256, k_order=0, tail_split=0, num_stages=6)
+    cases = ((1024, 768, 512, dict(num_stages=4), 0),
+             (1536, 1280, 384, dict(num_stages=3, num_consumer_warps=8), 0),
+             (520, 264, 136, dict(num_stages=4), 0),                                 # ragged in every dimension
+             (2048, 1024, 256, dict(num_stages=3, num_consumer_warps=8, num_sms=4), 4),   # 16 tiles on 2 pairs: 8 per pair
+             (1024, 512, 320, dict(num_stages=4, tile_n=128, bar_step_rows_b=128, num_sms=2), 2),   # two accumulator slots again
+             (1000, 516, 200, dict(num_stages=4, epilogue=0), 0))
+    for m, n, k, ov, sms in cases:
+        A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 300 + m)
+        for alpha, beta in ((1.0, 0.0), (1.5, 0.0), (-0.75, 1.25)):
+            got = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, alpha, beta, **dict(tall, **ov))
+            want = oracle.gemm(A, Bt, Cm, alpha, beta)
+            ok, msg = tolerance_ok(got, want, k, scale=max(1.0, abs(alpha)) + abs(beta))
+            assert ok, (m, n, k, ov, alpha, beta, msg)
+            if ov.get("tile_n", 256) == 256:
+                other = run_gemm(pkg, cuda, pkg.F16, A, Bt, Cm, alpha, beta, **dict(pair, num_sms=sms))
+                assert np.array_equal(got, other), (m, n, k, ov, alpha, beta, float(np.abs(got - other).max()))
+
+
 def test_split_k(pkg, cuda, oracle):
     for m, n, k, s, ov in ((256, 256, 2048, 4, dict()), (256, 512, 64 * 7, 3, dict()), (512, 512, 1024, 8, dict(tile_m=256, tile_n=256, cta_group=2))):
         A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 80 + s)
