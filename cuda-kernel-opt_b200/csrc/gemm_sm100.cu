@@ -431,7 +431,78 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 tc_fence_after_sync();
                 const uint32_t d_addr = tmem_base + acc * static_cast<uint32_t>(c.acc_cols);
                 uint32_t accumulate = 0;
-                for (int seg = w.seg_begin; seg < w.seg_end; ++seg) {
+                int seg = w.seg_begin;
+                if (two_atoms && !two_slots) {
+                    // One accumulator slot, two atoms: the draining warps hand back the upper atom's columns first. Its
+                    // MMAs for as many stages as the ring holds are issued while the lower atom is still being drained;
+                    // the lower atom's MMAs for those stages follow when its columns are free, and release the stages.
+                    const int ahead = min(c.stages, w.seg_end - w.seg_begin);
+                    {
+                        int s1 = s;
+                        uint32_t ph1 = ph, sb1 = sb, first = 0;
+                        uint64_t a1 = a_desc, b1 = b_desc;
+                        for (int j = 0; j < ahead; ++j) {
+                            const long long tf = PROF ? clock64() : 0;
+                            ok = wait_all(sb1, ph1, c.budget, abort_flag, 400 + s1);
+                            if (PROF) t_full += clock64() - tf;
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            uint64_t da = a1, db = b1;
+                            for (int kb = 0; kb < c.kblocks; ++kb) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    if (issue) umma_f16<CG>(d_addr, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, first);
+                                    first = 1;
+                                }
+                                da += a_kb_step;
+                                db += b_kb_step;
+                            }
+                            a1 += stage_step;
+                            b1 += stage_step;
+                            sb1 += stage_bar_bytes;
+                            if (++s1 == c.stages) {
+                                s1 = 0;
+                                ph1 ^= 1u;
+                                a1 = a_desc0;
+                                b1 = b_desc0;
+                                sb1 = bars;
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    const long long ta1 = PROF ? clock64() : 0;
+                    ok = wait_all(tmem_empty0 + 8u, aph ^ 1u, c.budget, abort_flag, 301);   // the lower atom's columns
+                    if (PROF) t_acc += clock64() - ta1;
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    uint32_t first = 0;
+                    for (int j = 0; j < ahead; ++j, ++seg) {
+                        uint64_t da = a_desc + atom_step, db = b_desc;
+                        for (int kb = 0; kb < c.kblocks; ++kb) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                if (issue) umma_f16<CG>(d_addr + atom_cols, da + static_cast<uint64_t>(2 * i), db + static_cast<uint64_t>(2 * i), idesc, first);
+                                first = 1;
+                            }
+                            da += a_kb_step;
+                            db += b_kb_step;
+                        }
+                        if (issuer) commit_to<CG>(sb + empty_a_off, pair_mask);
+                        ++it;
+                        a_desc += stage_step;
+                        b_desc += stage_step;
+                        sb += stage_bar_bytes;
+                        if (++s == c.stages) {
+                            s = 0;
+                            ph ^= 1u;
+                            a_desc = a_desc0;
+                            b_desc = b_desc0;
+                            sb = bars;
+                        }
+                    }
+                    accumulate = 1;
+                }
+                for (; seg < w.seg_end; ++seg) {
                     const long long tf = PROF ? clock64() : 0;
                     ok = wait_all(sb, ph, c.budget, abort_flag, 400 + s);
                     if (PROF) t_full += clock64() - tf;
@@ -647,6 +718,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const uint32_t aph = two_slots ? ((tl >> 1) & 1u) : (tl & 1u);
                 const long long ta = PROF ? clock64() : 0;
                 ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
+                // one slot shared by two 128-row atoms: the lower atom's columns come back on the second barrier
+                if (ok && a_halves == 2 && !two_slots) ok = wait_all(tmem_empty0 + 8u, aph ^ 1u, c.budget, abort_flag, 301);
                 if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -972,6 +1045,17 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             const int row_atom0 = row;
             const size_t row_off_atom0 = row_off;
             const uint32_t t_row_atom0 = t_row;
+            // One accumulator slot shared by two atoms: the upper atom's columns go back to the MMA thread as soon as
+            // they are drained (barrier 0), the lower atom's at the end of the tile (barrier 1).
+            const bool atom_release = a_halves == 2 && !two_slots;
+            auto upper_atom_drained = [&]() {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_leader);
+                    else mbar_arrive(tmem_empty0);
+                }
+            };
             for (int mh = 0; mh < a_halves; ++mh) {
                 const int row = row_atom0 + mh * c.mma_m;
                 const bool row_ok = lane_has_row && row < c.M;
@@ -1014,6 +1098,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         }
                         ++store_idx;
                     }
+                    if (atom_release && mh == 0) upper_atom_drained();
                     continue;
                 }
                 for (int c0 = col_begin; c0 < col_end; c0 += 32) {
@@ -1209,6 +1294,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                         ++store_idx;
                     }
                 }
+                if (atom_release && mh == 0) upper_atom_drained();
             }   // atoms
             if (w.kind == 2) {
                 // this warp's part of the partial is complete: make it visible, then say so
@@ -1224,8 +1310,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-                if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_leader + 8u * acc);
-                else mbar_arrive(tmem_empty0 + 8u * acc);
+                if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_leader + 8u * (atom_release ? 1u : acc));
+                else mbar_arrive(tmem_empty0 + 8u * (atom_release ? 1u : acc));
             }
         }
         if (e == 0 && lane == 0) B200_TL(24);

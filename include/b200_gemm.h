@@ -278,7 +278,10 @@ int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_ro
 
 /* Synchronises the stream and reports whether any kernel of this library hit a bounded-wait
  * timeout on the current device since the last call. info (may be null) receives
- * {code, block, barrier id, phase}. Clears the record. */
+ * {code, block, barrier id, phase}. Clears the record. Barrier ids of the GEMM kernel: 100 + stage a producer's
+ * wait for a free stage, 300 + slot the MMA thread's wait for a drained accumulator (301 with the tall pair: the
+ * lower atom's columns), 400 / 500 + stage its waits for operand data, 600 + slot a draining warp's wait for a
+ * finished accumulator, 700 - 703 the cluster reduce, 800 + warp the tail split's fix-up. */
 int b200_device_status(void *stream, int info[4]);
 /* Test hook: the budget of every in-kernel wait, in nanoseconds (default 2e9). */
 void b200_set_wait_budget_ns(uint64_t ns);
