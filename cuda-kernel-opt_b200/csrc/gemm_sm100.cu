@@ -718,8 +718,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                 const uint32_t aph = two_slots ? ((tl >> 1) & 1u) : (tl & 1u);
                 const long long ta = PROF ? clock64() : 0;
                 ok = wait_all(tmem_empty0 + 8u * acc, aph ^ 1u, c.budget, abort_flag, 300 + static_cast<int>(acc));
-                // one slot shared by two 128-row atoms: the lower atom's columns come back on the second barrier
-                if (ok && a_halves == 2 && !two_slots) ok = wait_all(tmem_empty0 + 8u, aph ^ 1u, c.budget, abort_flag, 301);
                 if (PROF) t_acc += clock64() - ta;
                 if (!ok) break;
                 tc_fence_after_sync();

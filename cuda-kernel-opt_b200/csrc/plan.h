@@ -232,7 +232,8 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
         p.atoms = 2;
         p.atom_rows = 64;
     }
-    if (p.atoms == 2 && !p.a_split && (p.a_boxes > 1 || p.split_k > 1)) return p;   // the tall pair: whole-stage barriers for A, whole tiles
+    // the tall pair: whole-stage barriers (it runs in the lean producer / MMA loops only), whole tiles
+    if (p.atoms == 2 && !p.a_split && (p.a_boxes > 1 || p.b_bars > 1 || p.b_priv != 0 || p.b_res_chunks != 1 || p.split_k > 1)) return p;
 
     // Tensor memory: two accumulator slots so the drain of tile i overlaps the MMAs of tile i+1.
     // M=64 per CTA keeps the 16-lanes-per-quarter layout of one 64-row atom.

@@ -139,6 +139,8 @@ def test_tall_pair_tile_domain(pkg):
     assert ok(num_stages=4, cta_group=1) == pkg.INVALID_CONFIG
     assert ok(num_stages=4, split_k=2) == pkg.INVALID_CONFIG
     assert ok(num_stages=4, bar_step_rows_a=128) == pkg.INVALID_CONFIG  # sub-tile barriers for A belong to the 128-row forms
+    assert ok(num_stages=4, bar_step_rows_b=64, bar_steps_b=2) == pkg.INVALID_CONFIG   # ... and so do those for B^T
+    assert ok(num_stages=4, bar_step_rows_b=64, bar_steps_b=0) == pkg.INVALID_CONFIG
     assert ok(num_stages=4, swap_ab=1) == pkg.INVALID_CONFIG
     assert pkg.smem_bytes(pkg.F16, P(pkg, num_stages=4, epilogue=1, **tall)) == 4 * (256 + 128) * 64 * 2 + 4 * 2 * 4096 + (4 * 4 + 6) * 8 + 16 + 1024
     # the schedule: 512-row tiles, every tile once, ragged M included

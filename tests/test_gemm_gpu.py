@@ -447,6 +447,37 @@ def test_tall_pair_tile(pkg, cuda, oracle):
                 assert np.array_equal(got, other), (m, n, k, ov, alpha, beta, float(np.abs(got - other).max()))
 
 
+def test_tall_pair_tile_randomised(pkg, cuda, oracle):
+    """Seeded random walk over what the tall pair accepts: tile widths, ring depths, four or eight draining warps, both
+    epilogues, hints, K order, partial grids, ragged shapes, both dtypes, the three alpha / beta cases."""
+    import random
+    rnd = random.Random(512256)
+    ran = 0
+    for it in range(200):
+        if ran >= 30:
+            break
+        tile_n = rnd.choice([32, 64, 96, 128, 192, 224, 256])
+        ov = dict(tile_m=512, tile_n=tile_n, cta_group=2, bar_step_rows_a=512, bar_step_rows_b=tile_n, segment_dim_k=rnd.choice([64, 64, 128]),
+                  num_stages=rnd.randint(1, 5), tile_group_m=rnd.randint(1, 5), num_producer_warps=rnd.choice([1, 2, 4]),
+                  num_consumer_warps=rnd.choice([4, 8]), epilogue=rnd.choice([0, 1, 1]), l2_hint=rnd.randint(0, 3), k_order=rnd.choice([0, 1]),
+                  num_sms=rnd.choice([0, 0, 2, 6, 74]), tail_split=rnd.choice([0, 1]))
+        dtype = rnd.choice([pkg.F16, pkg.BF16])
+        m = rnd.choice([1, 100, 256, 512, 520, 1024, 1500, 2048, 2100])
+        n = 4 * rnd.randint(4, 300)
+        k = 8 * rnd.randint(1, 160)
+        alpha, beta = rnd.choice([(1.0, 0.0), (1.0, 1.0), (0.5, -2.0), (2.0, 0.0)])
+        p = pkg.default_params(m, n, k, dtype, **ov)
+        if pkg.validate(m, n, k, dtype, p) != pkg.OK:
+            continue
+        ran += 1
+        A, Bt, Cm = inputs(pkg, dtype, m, n, k, 5000 + it)
+        got = run_gemm(pkg, cuda, dtype, A, Bt, Cm, alpha, beta, **ov)
+        want = oracle.gemm(A, Bt, Cm if beta else None, alpha, beta, dtype)
+        ok, msg = tolerance_ok(got, want, k, abs(alpha) + abs(beta) + 1.0)
+        assert ok, (m, n, k, dtype, alpha, beta, p.as_dict(), msg)
+    assert ran >= 25
+
+
 def test_split_k(pkg, cuda, oracle):
     for m, n, k, s, ov in ((256, 256, 2048, 4, dict()), (256, 512, 64 * 7, 3, dict()), (512, 512, 1024, 8, dict(tile_m=256, tile_n=256, cta_group=2))):
         A, Bt, Cm = inputs(pkg, pkg.F16, m, n, k, 80 + s)
