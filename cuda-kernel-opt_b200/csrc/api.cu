@@ -232,13 +232,23 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         // 1106 cycles per 512 x 256 x 64 block) and a launch costs less energy, which under the power limit is clock.
         // Its accumulators fill the tensor memory, so the drain of a tile (9.5 k cycles with eight warps) is not
         // hidden behind the next tile's MMAs: 7 % of a tile at K = 8192, more at smaller K. Measured at 8192^3:
-        // 1491 against 1443 TFLOP/s (0.968 of the time). Taken when its rounds cost less by that model.
-        if (best_n == 256 && K >= 4096) {
-            const int64_t tall_tiles = ((M + 511) / 512) * ((N + 255) / 256);
-            const int64_t tall_rounds = (tall_tiles + 73) / 74;
+        // 1491 against 1443 TFLOP/s (0.968 of the time). Taken when its rounds cost less by that model, in the width
+        // that makes its rounds come out even: 224 columns for the row shards of 8192^3 (1024 x 8192: 2 x 37 tiles are
+        // exactly one round, +4.4 % over two waves of 256 x 224 pairs; 2048 and 4096 rows: two and four rounds, +3.8 %
+        // and +1.4 %), 256 for the whole of it (7 rounds of 74).
+        if (K >= 4096) {
             const double tall_factor = 0.968 + 0.071 * (8192.0 / double(K) - 1.0);
-            const double tall_cost = double(tall_rounds) * 2.0 * double(256 + 12) * tall_factor;
-            if (tall_cost < best_cost * 0.995) tall = true;
+            for (int tn = 256; tn >= 192; tn -= 32) {
+                const int64_t tall_tiles = ((M + 511) / 512) * ((N + tn - 1) / tn);
+                const int64_t tall_rounds = (tall_tiles + 73) / 74;
+                const double tall_cost = double(tall_rounds) * 2.0 * double(tn + 12) * tall_factor * (tn == 256 ? 1.0 : 1.01);
+                if (tall_cost < best_cost * 0.995) {
+                    best_cost = tall_cost / 0.995;   // a narrower tall tile has to beat this one in turn
+                    best_n = tn;
+                    tall = true;
+                }
+            }
+            if (tall) p->tile_n = best_n;
         }
     } else {
         // One row of tiles (skinny, HBM-bound: decode shapes) or N not a multiple of 256: a one-CTA
@@ -290,7 +300,10 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
     if (tall) {
         p->tile_m = 512;
         p->bar_step_rows_a = 512;
-        p->num_stages = 3;          // 3 x 48 KB of stages + 64 KB of drain buffers for eight warps
+        p->bar_step_rows_b = p->tile_n;
+        // 256 columns: 3 x 48 KB of stages + 64 KB of drain buffers (two boxes for each of eight warps); narrower: a
+        // fourth stage pays (919 against 1009 cycles per K block at 224 columns) and the warps stage through one box each
+        p->num_stages = p->tile_n == 256 ? 3 : 4;
         p->num_consumer_warps = 8;  // the drain is exposed: two warps per tensor-memory lane quarter halve it
         p->tile_group_m = 8;        // 8 x 512 rows: the same 4096-row groups as 16 x 256
     }
@@ -444,6 +457,7 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     a.idesc_res = umma_idesc(atom_m, p.b_res_chunks * p.chunk_n, dtype == B200_BF16);
     a.a_split = p.a_split;
     a.atoms = p.atoms;
+    a.epi_bufs = p.epi_bufs;
     a.wait_budget_cycles = static_cast<long long>(g_wait_budget_ns.load() * 2ull);  // SM clock is below 2 GHz
 
     if (pushing && ws_split == 1) {

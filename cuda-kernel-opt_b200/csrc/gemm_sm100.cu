@@ -817,7 +817,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
             col_end = half ? c.tile_n : min(mid, c.tile_n);
         }
         const uint32_t tmem_empty_leader = (CG == 2) ? mapa_shared(tmem_empty0, leader_cta) : tmem_empty0;
-        const uint32_t epi_buf = base + static_cast<uint32_t>(off_epi) + static_cast<uint32_t>(e) * 2u * 4096u;
+        const uint32_t two_bufs = g.epi_bufs == 2 ? 1u : 0u;   // 1: two staging boxes per warp, alternating; 0: one
+        const uint32_t epi_buf = base + static_cast<uint32_t>(off_epi) + static_cast<uint32_t>(e) * (4096u << two_bufs);
         // row of the tile this thread drains: 128-row atoms map row r to lane r; 64-row atoms use
         // lanes 0-15 of each quarter (row 16 * quarter + lane).
         const int row_in_cta = (c.mma_m == 128) ? (q * 32 + lane) : (q * 16 + (lane & 15));
@@ -1069,8 +1070,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     int d_col = w.n0 + col_begin;
                     for (int c0 = col_begin; c0 < col_end; c0 += 32, d_col += 32) {
                         tmem_ld_wait();
-                        const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
-                        if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
+                        const uint32_t buf = epi_buf + (store_idx & two_bufs) * 4096u;
+                        if (lane == 0) {   // the box stored two steps ago (one step ago with a single box) has been read
+                            if (two_bufs) tma_store_wait_read<1>();
+                            else tma_store_wait_read<0>();
+                        }
                         __syncwarp();
                         const uint32_t my_row = buf + static_cast<uint32_t>(lane) * 128u;
                         if (a_u == 1.0f) {
@@ -1260,8 +1264,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) gemm_sm100_kernel(const __grid
                     } else {
                         // registers -> 128-byte-swizzled shared memory -> one TMA store of 32 x 32 fp32 (the boxes the common
                         // drain above does not take: ragged tile columns, the finishing CTA of a cut tile)
-                        const uint32_t buf = epi_buf + (store_idx & 1u) * 4096u;
-                        if (lane == 0) tma_store_wait_read<1>();  // the box stored two steps ago has been read
+                        const uint32_t buf = epi_buf + (store_idx & two_bufs) * 4096u;
+                        if (lane == 0) {   // the box stored two steps ago (one step ago with a single box) has been read
+                            if (two_bufs) tma_store_wait_read<1>();
+                            else tma_store_wait_read<0>();
+                        }
                         __syncwarp();
                         const float4 *csrc = reinterpret_cast<const float4 *>(gC + row_off + c0);
     #pragma unroll

@@ -46,6 +46,7 @@ struct alignas(64) GemmArgs {
                         // distributed shared memory (split_k is 1 then: no workspace)
     int d_stream;       // 1: the TMA stores of D carry an evict_first L2 policy (D exceeds what the L2 would keep)
     int overlap_launch; // 1: set-up runs before griddepcontrol.wait (launched with programmatic stream serialisation)
+    int epi_bufs;       // staging boxes per draining warp of the TMA-store drain (2 or 1)
     int atoms;          // MMA atoms per CTA and tile (1 or 2), mma_m rows of A each; their accumulators sit side by side in
                         // tensor memory (acc_cols = atoms * tile_n; two accumulator slots while 2 * acc_cols fits the 512 columns)
     int a_split;        // 1: a 128-row tile is two 64-row MMA atoms (the A side of the shift synchronisation): the upper

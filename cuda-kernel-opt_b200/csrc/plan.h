@@ -42,6 +42,7 @@ struct Plan {
     int tmem_cols = 0, acc_cols = 0;      // allocation; columns per accumulator slot (2 slots)
     int stage_bytes = 0, a_stage_bytes = 0, b_stage_bytes = 0;
     int epi_mode = 0, epi_bytes = 0;
+    int epi_bufs = 2;                     // 32x32 fp32 staging boxes per draining warp of the TMA-store drain: 2, or 1 when 2 do not fit
     int num_barriers = 0;
     int off_epi = 0, off_bars = 0, off_tmem_ptr = 0;
     int smem_bytes = 0;                   // dynamic shared memory requested (includes alignment slack)
@@ -250,14 +251,20 @@ inline Plan make_plan(const b200_gemm_params &user, int num_sms_device) {
     // every sub-tile base must stay 1024-byte aligned (8 rows of 128 bytes)
     if ((p.a_box_rows % 8) || ((p.chunk_n / cg) % 8)) return p;
     p.off_epi = p.stages * p.stage_bytes;
-    p.epi_bytes = p.epi_mode ? p.epi_warps * 2 * 32 * kEpiBoxCols * 4 : 0;  // two 32x32 fp32 boxes per warp
-    if (p.cluster_reduce) p.epi_bytes = p.tile_n * 128 * 4;                 // this CTA's partial tile, [column][row]
     p.num_barriers = p.stages * 2 * (p.a_bars + p.b_bars) /* full + empty */ + 4 /* tmem full/empty x2 */ +
                      2 /* partial tile full / empty (cluster reduce) */;
-    p.off_bars = p.off_epi + p.epi_bytes;
-    p.off_tmem_ptr = p.off_bars + p.num_barriers * 8;
-    const int used = p.off_tmem_ptr + 16;
-    p.smem_bytes = used + 1024;  // slack to align the dynamic base to 1024 bytes
+    // The TMA-store drain stages two 32x32 fp32 boxes per warp (one being read by the copy engine while the next is
+    // written); where two do not fit beside the ring (eight draining warps next to four 48 KB stages of the tall pair)
+    // one does: the read of a box has long finished when the warp comes round to it again.
+    for (p.epi_bufs = 2; p.epi_bufs >= 1; --p.epi_bufs) {
+        p.epi_bytes = p.epi_mode ? p.epi_warps * p.epi_bufs * 32 * kEpiBoxCols * 4 : 0;
+        if (p.cluster_reduce) p.epi_bytes = p.tile_n * 128 * 4;                 // this CTA's partial tile, [column][row]
+        p.off_bars = p.off_epi + p.epi_bytes;
+        p.off_tmem_ptr = p.off_bars + p.num_barriers * 8;
+        p.smem_bytes = p.off_tmem_ptr + 16 + 1024;  // slack to align the dynamic base to 1024 bytes
+        if (p.smem_bytes <= kSmemLimit || !p.epi_mode || p.cluster_reduce) break;
+    }
+    if (p.epi_bufs < 1) p.epi_bufs = 1;
     if (p.smem_bytes > kSmemLimit) return p;  // the harness's filter, port_2.cu:1229-1231
     if (p.smem_bytes < kMinSmemRequest) p.smem_bytes = kMinSmemRequest;
 
