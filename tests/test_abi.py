@@ -135,6 +135,10 @@ def test_tall_pair_tile_domain(pkg):
     assert ok(num_stages=4) == pkg.OK
     assert ok(num_stages=5) == pkg.INVALID_CONFIG                       # 5 x 48 KiB of stages + drain buffers do not fit
     assert ok(num_stages=3, num_consumer_warps=8) == pkg.OK
+    # four stages beside eight draining warps: two staging boxes per warp do not fit, one does
+    assert ok(num_stages=4, num_consumer_warps=8) == pkg.OK
+    assert pkg.smem_bytes(pkg.F16, P(pkg, num_stages=4, num_consumer_warps=8, epilogue=1, **tall)) == 4 * (256 + 128) * 64 * 2 + 8 * 4096 + (4 * 4 + 6) * 8 + 16 + 1024
+    assert pkg.smem_bytes(pkg.F16, P(pkg, num_stages=3, num_consumer_warps=8, epilogue=1, **tall)) == 3 * (256 + 128) * 64 * 2 + 8 * 2 * 4096 + (3 * 4 + 6) * 8 + 16 + 1024
     assert ok(num_stages=4, tile_n=128, bar_step_rows_b=128) == pkg.OK
     assert ok(num_stages=4, cta_group=1) == pkg.INVALID_CONFIG
     assert ok(num_stages=4, split_k=2) == pkg.INVALID_CONFIG
