@@ -45,7 +45,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM traffic of one launch of the dominant kernel from an ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum); see profiles/. None where no capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"c3_8192_f16": 942209536, "c2_4096_f16": 125809152, "c4_m16_bf16": 472698283, "c4_m128_bf16": 473866240}
+NCU_TRAFFIC_BYTES = {"c3_8192_f16": 939570688, "c2_4096_f16": 125323264, "c4_m16_bf16": 472698283, "c4_m128_bf16": 473866240}
 
 WORKLOADS = {
     # name: (M, N, K, dtype, seed, dist_a, dist_b, bound)
