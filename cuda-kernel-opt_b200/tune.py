@@ -62,10 +62,13 @@ def candidates(M: int, N: int, K: int) -> list[dict]:
     tiles += [dict(tile_m=128, tile_n=tn, cta_group=1) for tn in (256, 224, 192, 128, 64) if N % tn == 0 or tn == 128]
     if M >= 1024 and K >= 4096:
         # the tall pair: 256 rows of A per CTA as two MMA atoms; one accumulator slot, so the drain counts: eight warps
-        for stages, cw in ((3, 8), (4, 4)):
-            for group in (4, 8, 16):
-                out.append(dict(tile_m=512, tile_n=256, cta_group=2, bar_step_rows_a=512, num_stages=stages, num_consumer_warps=cw,
-                                num_producer_warps=2, l2_hint=3, tile_group_m=group, k_order=1, tail_split=0))
+        # (256 columns, or narrower where that makes the rounds of the 74 pairs come out even; four stages beside eight
+        # draining warps make them stage through one box each)
+        for tn in (256, 224, 192):
+            for stages, cw in ((3, 8), (4, 8), (4, 4)):
+                for group in ((4, 8, 16) if tn == 256 else (8,)):
+                    out.append(dict(tile_m=512, tile_n=tn, cta_group=2, bar_step_rows_a=512, bar_step_rows_b=tn, num_stages=stages,
+                                    num_consumer_warps=cw, num_producer_warps=2, l2_hint=3, tile_group_m=group, k_order=1, tail_split=0))
     for t in tiles:
         per_stage = (t["tile_m"] // t["cta_group"] + t["tile_n"] // t["cta_group"]) * 128
         deepest = min(8, 200000 // per_stage)
