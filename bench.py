@@ -575,8 +575,9 @@ def run_ours(args):
             p_host = p if p.split_k == 1 else None
             run_e2e = lambda: sess.gemm_host(dtype, hA, hB, None, hD, 1.0, 0.0, m_loc, n_loc, k_loc, p_host)
             h2d = int(2 * (m_loc * k_loc + n_loc * k_loc))
-            call = ("b200_session_gemm_host (pinned host A, B^T -> device, GEMM, D -> pinned host, synchronised; a 4 x 4 grid of D "
-                    "blocks pipelined over upload / compute / download streams)")
+            call = ("b200_session_gemm_host (pinned host A, B^T -> device, GEMM, D -> pinned host, synchronised; A and B^T uploaded in "
+                    "eight row blocks each, the band of D every block completes multiplied and downloaded at once: upload / compute / "
+                    "download streams)")
         run_e2e()
         barrier()
         t0 = time.perf_counter()

@@ -249,8 +249,10 @@ int b200_peer_release(void *imported);
  * (and C when beta != 0) to the device, the launch, cudaMemcpy of D back, which is also the
  * synchronisation (port_2.cu:1210-1212, :1238-1242). Device buffers come from a session created
  * once at the maximal dimensions, as the harness cudaMallocs once (port_2.cu:1200-1203). Host
- * pointers may be pageable or pinned (with pinned memory D is produced in a grid of up to 4 x 4 blocks
- * whose uploads, products and downloads are pipelined over three streams). Returns after D is in host memory. */
+ * pointers may be pageable or pinned (with pinned memory A and B^T go up in up to eight row blocks each and the
+ * band of D every block completes is multiplied and downloaded while later uploads run, three streams; every band is
+ * its own launch, so the result equals one launch over the whole problem up to fp32 summation order). Returns after
+ * D is in host memory. */
 typedef struct b200_session b200_session;
 int b200_session_create(int64_t max_m, int64_t max_n, int64_t max_k, b200_session **out);
 void b200_session_destroy(b200_session *s);
