@@ -300,6 +300,24 @@ def test_default_params_are_valid(pkg):
             assert pkg.validate(m, n, k, dt, p) == pkg.OK, (m, n, k, p.as_dict())
 
 
+def test_defaults_for_large_squares_and_their_row_shards(pkg):
+    """b200_gemm_default_params weighs the tall pair (512-row tiles, 256 / 224 / 192 columns) against the 256-row pair
+    family by rounds of the 74 CTA pairs: 8192^3 takes 512 x 256 (seven rounds), its row shards 512 x 224 (37 tile
+    columns: one, two and four whole rounds) with a fourth stage; 4096^3, a short K and a shape whose 256-wide tiles
+    already fill a wave keep the 256-row pair."""
+    pick = lambda m, n, k: {f: getattr(pkg.default_params(m, n, k, pkg.F16), f) for f in
+                            ("tile_m", "tile_n", "cta_group", "num_stages", "num_consumer_warps", "tile_group_m", "bar_step_rows_a", "bar_step_rows_b")}
+    assert pick(8192, 8192, 8192) == dict(tile_m=512, tile_n=256, cta_group=2, num_stages=3, num_consumer_warps=8, tile_group_m=8,
+                                          bar_step_rows_a=512, bar_step_rows_b=256)
+    for m in (1024, 2048, 4096):
+        assert pick(m, 8192, 8192) == dict(tile_m=512, tile_n=224, cta_group=2, num_stages=4, num_consumer_warps=8, tile_group_m=8,
+                                           bar_step_rows_a=512, bar_step_rows_b=224), m
+    for shape in ((4096, 4096, 4096), (8192, 8192, 4096), (8192, 4096, 8192), (2048, 2048, 262144)):
+        d = pick(*shape)
+        assert (d["tile_m"], d["tile_n"], d["num_stages"], d["num_consumer_warps"]) == (256, 256, 6, 4), (shape, d)
+    assert pick(512, 8192, 8192)["tile_m"] == 256 and pick(512, 8192, 8192)["tile_n"] == 224     # 2 x 37 tiles: one wave of 256 x 224 pairs
+
+
 def test_status_strings(pkg):
     seen = {pkg.status_string(i) for i in range(8)}
     assert len(seen) == 8 and "unknown status" not in seen
