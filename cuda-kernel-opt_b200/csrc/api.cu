@@ -115,7 +115,7 @@ int encode_2d(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const 
 // Tuned defaults. Large problems use the two-CTA pair (256 x 256 tile, each CTA stages 128 rows of
 // A and 128 rows of B^T per K block: half the L2-to-shared traffic per flop of a one-CTA
 // 128 x 256 tile); small or skinny ones a one-CTA tile with the widest N that divides.
-void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool allow_swap = true) {
+void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool allow_swap = true, bool allow_tall = true) {
     std::memset(p, 0, sizeof(*p));
     // The two-CTA 256 x 256 tile needs enough tiles to occupy the GPU: below half of the 74 pairs
     // (1024^2 has 16) narrower one-CTA tiles finish sooner (1024^3: 7.3 against 11.3 us).
@@ -236,7 +236,7 @@ void default_params(int64_t M, int64_t N, int64_t K, b200_gemm_params *p, bool a
         // that makes its rounds come out even: 224 columns for the row shards of 8192^3 (1024 x 8192: 2 x 37 tiles are
         // exactly one round, +4.4 % over two waves of 256 x 224 pairs; 2048 and 4096 rows: two and four rounds, +3.8 %
         // and +1.4 %), 256 for the whole of it (7 rounds of 74).
-        if (K >= 4096) {
+        if (K >= 4096 && allow_tall) {
             const double tall_factor = 0.968 + 0.071 * (8192.0 / double(K) - 1.0);
             for (int tn = 256; tn >= 192; tn -= 32) {
                 const int64_t tall_tiles = ((M + 511) / 512) * ((N + tn - 1) / tn);
@@ -333,7 +333,9 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
     b200_gemm_params local;
     if (!user) {
-        default_params(M, N, K, &local);
+        // The tall pair's drain is exposed; it pays only through the TMA-store drain, which fp16 output, a push target
+        // and a ragged leading dimension do not have: those keep the 256-row pair.
+        default_params(M, N, K, &local, true, !(out_half || (push && push->world > 0)));
         user = &local;
     }
     const DeviceInfo *dev = nullptr;

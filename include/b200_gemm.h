@@ -231,7 +231,9 @@ int b200_gemm_splitk_noalloc(int dtype, const void *A, const void *Bt, const flo
  * order. Use a new epoch (> 0, increasing) for every GEMM; slots of epoch e may be overwritten
  * only after every rank has finished b200_push_reduce of epoch e (a barrier per step, or two
  * alternating slot areas). After a DEVICE_TIMEOUT read the record with b200_device_status before
- * the next push: while a record is pending a push raises no flags. */
+ * the next push: while a record is pending a push raises no flags. Swapped roles and the tall pair
+ * (tile_m = 512, which b200_gemm_default_params returns for large squares) are refused with
+ * B200_INVALID_CONFIG: pass p = NULL for the defaults of this call, or set tile_m = 256. */
 int b200_gemm_push(int dtype, const void *A, const void *Bt, int64_t M, int64_t N, int64_t K, const b200_gemm_params *p,
                    int world, int rank, void *const *slot_ptrs, void *const *flag_ptrs, void *done_counter, int epoch,
                    void *workspace, size_t workspace_bytes, void *stream);
