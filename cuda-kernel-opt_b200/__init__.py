@@ -24,7 +24,7 @@ TENSOR_A, TENSOR_B, TENSOR_C = 1, 2, 3
 
 # every symbol include/b200_gemm.h declares
 EXPORTS = [
-    "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes", "b200_gemm_schedule",
+    "b200_gemm_default_params", "b200_gemm_default_params_plain", "b200_gemm_default_params_for_call", "b200_gemm_validate", "b200_gemm_smem_bytes", "b200_gemm_workspace_bytes", "b200_gemm_schedule",
     "b200_gemm_f16", "b200_gemm_bf16", "b200_gemm_f16_out_f16", "b200_gemm_splitk_noalloc", "b200_gemm_push", "b200_push_reduce",
     "b200_peer_alloc", "b200_peer_free", "b200_peer_export", "b200_peer_import", "b200_peer_release", "b200_session_create", "b200_session_destroy", "b200_session_gemm_host", "b200_session_buffers", "b200_session_gemm_host_sharded",
     "b200_device_status", "b200_set_wait_budget_ns", "b200_set_profile_buffer", "b200_profile_slots", "b200_status_string", "b200_last_cuda_error", "b200_num_sms",
@@ -63,6 +63,8 @@ def lib():
         PP = C.POINTER(Params)
         L.b200_gemm_default_params.argtypes = [i64, i64, i64, C.c_int, PP]
         L.b200_gemm_default_params_plain.argtypes = [i64, i64, i64, C.c_int, PP]
+        L.b200_gemm_default_params_for_call.argtypes = [i64, i64, i64, C.c_int, C.c_float, C.c_int, PP]
+        L.b200_gemm_default_params_for_call.restype = C.c_int
         L.b200_gemm_validate.argtypes = [i64, i64, i64, C.c_int, PP]
         L.b200_gemm_smem_bytes.argtypes = [C.c_int, PP]
         L.b200_gemm_smem_bytes.restype = i64
@@ -213,7 +215,14 @@ def gemm(A, Bt, Cm=None, D=None, alpha=1.0, beta=0.0, params: Params | None = No
     assert D.dtype in (torch.float32, torch.float16) and D.is_contiguous() and D.shape == (M, N)
     if Cm is not None:
         assert Cm.dtype == D.dtype and Cm.is_contiguous() and Cm.shape == (M, N)
-    p = params if params is not None else default_params(M, N, K, dtype)
+    if params is not None:
+        p = params
+    else:
+        # the defaults of this call: the library keeps large squares off the tall pair when there is a C to read or D is fp16
+        p = Params()
+        st = lib().b200_gemm_default_params_for_call(M, N, K, dtype, float(beta), 1 if D.dtype == torch.float16 else 0, C.byref(p))
+        if st != OK:
+            raise B200Error(st, "b200_gemm_default_params_for_call")
     if D.dtype == torch.float16:
         # fp16 C and D (the reference's DT = DT_ACC = half instances): b200_gemm_f16_out_f16, no workspace forms
         assert dtype == F16, "fp16 output goes with fp16 operands"
@@ -222,7 +231,7 @@ def gemm(A, Bt, Cm=None, D=None, alpha=1.0, beta=0.0, params: Params | None = No
             # no tunables given: the library picks (it keeps large squares off the tall pair here, whose exposed drain only
             # pays with the TMA-store epilogue that fp16 output does not have)
             st = lib().b200_gemm_f16_out_f16(A.data_ptr(), Bt.data_ptr(), Cm.data_ptr() if Cm is not None else None, D.data_ptr(),
-                                             alpha, beta, M, N, K, C.byref(params) if params is not None else None, sptr)
+                                             alpha, beta, M, N, K, C.byref(p), sptr)
         if st != OK:
             raise B200Error(st, "b200_gemm_f16_out_f16")
         return D

@@ -333,9 +333,11 @@ int gemm_impl(int dtype, const void *A, const void *Bt, const float *C, float *D
     if (dtype != B200_F16 && dtype != B200_BF16) return B200_INVALID_CONFIG;
     b200_gemm_params local;
     if (!user) {
-        // The tall pair's drain is exposed; it pays only through the TMA-store drain, which fp16 output, a push target
-        // and a ragged leading dimension do not have: those keep the 256-row pair.
-        default_params(M, N, K, &local, true, !(out_half || (push && push->world > 0)));
+        // The tall pair's drain is exposed; it pays only through the lean TMA-store drain of beta = 0 (with C to read the
+        // drain takes half as long again: 8192^3 at beta = 1 1.0 - 1.26 against 1.23 - 1.41 PFLOP/s for the 256-row pair,
+        // whose drain hides behind the next tile), which fp16 output and a push target do not have either: those keep
+        // the 256-row pair.
+        default_params(M, N, K, &local, true, !(out_half || beta != 0.0f || (push && push->world > 0)));
         user = &local;
     }
     const DeviceInfo *dev = nullptr;
@@ -540,6 +542,13 @@ int b200_gemm_default_params(int64_t M, int64_t N, int64_t K, int dtype, b200_ge
     if (!p) return B200_INVALID_POINTER;
     (void)dtype;
     default_params(M, N, K, p);
+    return B200_OK;
+}
+
+int b200_gemm_default_params_for_call(int64_t M, int64_t N, int64_t K, int dtype, float beta, int fp16_out, b200_gemm_params *p) {
+    if (!p) return B200_INVALID_POINTER;
+    (void)dtype;
+    default_params(M, N, K, p, true, !(fp16_out || beta != 0.0f));
     return B200_OK;
 }
 

@@ -133,11 +133,17 @@ typedef struct b200_gemm_params {
 } b200_gemm_params;
 
 /* Fills *p with the tuned default for the shape (what the reference's harness hard-codes per
- * sweep, port_2.cu:1518-1564). dtype is B200_F16 or B200_BF16. */
+ * sweep, port_2.cu:1518-1564). dtype is B200_F16 or B200_BF16. Tuned for alpha * A * B^T with beta = 0 and
+ * fp32 D: for 8192^3-sized squares and their row shards that is the tall pair (tile_m = 512), whose exposed
+ * drain is slower with C to read; a call with p = NULL knows beta and the output type and keeps the 256-row
+ * pair for beta != 0, fp16 output and b200_gemm_push. */
 int b200_gemm_default_params(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p);
 /* The same without the swapped forms (swap_ab = 0): the tuned plain tile for the shape, the starting point
  * for callers that set tile_m / tile_n / epilogue themselves in the reference's meaning. */
 int b200_gemm_default_params_plain(int64_t M, int64_t N, int64_t K, int dtype, b200_gemm_params *p);
+/* The defaults a call with p = NULL would take, given what such a call knows beyond the shape: beta and
+ * whether C and D are fp16 (b200_gemm_f16_out_f16). No reference counterpart. */
+int b200_gemm_default_params_for_call(int64_t M, int64_t N, int64_t K, int dtype, float beta, int fp16_out, b200_gemm_params *p);
 
 /* Host-only validation: the reference's asserts (port_2.cu:1112-1123) and its harness's
  * shared-memory filter (port_2.cu:1229-1232) as a status. Touches no GPU. */
