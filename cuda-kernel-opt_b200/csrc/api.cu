@@ -825,7 +825,7 @@ int b200_session_gemm_host(b200_session *s, int dtype, const void *hA, const voi
         b200_gemm_params local;
         const b200_gemm_params *bp = user_p;
         if (!bp) {
-            default_params(rows, cols, K, &local);
+            default_params(rows, cols, K, &local, true, beta == 0.0f);   // as a call without tunables picks them
             bp = &local;
         }
         const size_t off = static_cast<size_t>(r0) * N + c0;
@@ -898,7 +898,7 @@ int b200_session_gemm_host_sharded(b200_session *s, int dtype, const void *hA_ro
     if (brows > m_rows) brows = m_rows;
     const int R = static_cast<int>((m_rows + brows - 1) / brows);
     if (!p) {
-        default_params(brows, cols, K, &local);           // the shape of one block product
+        default_params(brows, cols, K, &local, true, beta == 0.0f);   // the shape of one block product
         p = &local;
     }
     const size_t slice_bytes = static_cast<size_t>(cols) * K * 2;
