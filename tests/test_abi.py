@@ -316,6 +316,14 @@ def test_defaults_for_large_squares_and_their_row_shards(pkg):
         d = pick(*shape)
         assert (d["tile_m"], d["tile_n"], d["num_stages"], d["num_consumer_warps"]) == (256, 256, 6, 4), (shape, d)
     assert pick(512, 8192, 8192)["tile_m"] == 256 and pick(512, 8192, 8192)["tile_n"] == 224     # 2 x 37 tiles: one wave of 256 x 224 pairs
+    # what a call without tunables takes when it has a C to read or writes fp16: the 256-row pair (the tall pair's exposed
+    # drain only pays through the lean TMA-store path of beta = 0 and fp32 D)
+    import ctypes as C
+    for beta, f16_out, tile_m in ((0.0, 0, 512), (1.0, 0, 256), (0.0, 1, 256), (-0.5, 1, 256)):
+        p = pkg.Params()
+        assert pkg.lib().b200_gemm_default_params_for_call(8192, 8192, 8192, pkg.F16, beta, f16_out, C.byref(p)) == pkg.OK
+        assert p.tile_m == tile_m and p.cta_group == 2 and pkg.validate(8192, 8192, 8192, pkg.F16, p) == pkg.OK, (beta, f16_out, p.as_dict())
+    assert pkg.lib().b200_gemm_default_params_for_call(8192, 8192, 8192, pkg.F16, 0.0, 0, None) == pkg.INVALID_POINTER
 
 
 def test_status_strings(pkg):
